@@ -1,0 +1,84 @@
+// dispatch.cu - the extern "C" contraction and attention-core entry points: argument checks
+// and the choice between the tcgen05 kernels and the CUDA-core kernels.  The choice is by
+// shape only - an explicit tensor-core request that the shape cannot satisfy is an error,
+// never a silent change of arithmetic.
+#include "common.cuh"
+
+using namespace boatcu;
+
+namespace boatcu {
+bool attn_tc_supported(int mma, int64_t units, int64_t S, int64_t hs, int io_type);
+int attn_fwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q,
+                const void* K, const void* V, int io_type, void* O, float* lse);
+size_t attn_bwd_tc_scratch_bytes(int mma, int64_t units, int64_t S, int64_t hs);
+int attn_bwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q,
+                const void* K, const void* V, const void* dO, const float* lse, const float* delta,
+                int io_type, void* dQ, void* dK, void* dV, void* scratch, size_t scratch_bytes);
+}
+
+static int check_types(const char* who, int mma, int in_type) {
+    if (mma < BOAT_MMA_FP32 || mma > BOAT_MMA_BF16) return set_error(10, "%s: unknown arithmetic %d", who, mma);
+    if (in_type != BOAT_CUDA_F32 && in_type != BOAT_CUDA_BF16) return set_error(10, "%s: unknown storage type %d", who, in_type);
+    if (mma == BOAT_MMA_BF16 && in_type != BOAT_CUDA_BF16) return set_error(10, "%s: BF16 arithmetic needs BF16 storage", who);
+    if (mma == BOAT_MMA_TF32 && in_type != BOAT_CUDA_F32) return set_error(10, "%s: TF32 arithmetic needs FP32 storage", who);
+    return 0;
+}
+
+extern "C" {
+
+int boat_cuda_gemm(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                   const void* B, int64_t ldb, int in_type, void* C, int64_t ldc, int out_type, const float* bias) {
+    if (int rc = check_types("boat_cuda_gemm", mma, in_type)) return rc;
+    if (M < 0 || N < 0 || K < 0) return set_error(11, "boat_cuda_gemm: negative size");
+    if (M == 0 || N == 0) return 0;
+    if (!A || !B || !C) return set_error(11, "boat_cuda_gemm: NULL operand");
+    if (mma != BOAT_MMA_FP32) {
+        if (gemm_tc_supported(mma, ta, tb, M, N, K, A, lda, B, ldb, in_type, C, ldc, out_type))
+            return gemm_tc(mma, ta, tb, M, N, K, A, lda, B, ldb, in_type, C, ldc, out_type, bias);
+        // Small or unaligned problems: same storage types, FP32 FMA arithmetic (more
+        // accurate than the requested tensor-core format, never less).
+    }
+    return gemm_simt(ta, tb, M, N, K, A, lda, B, ldb, in_type, C, ldc, out_type, bias);
+}
+
+int boat_cuda_attn_fwd(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q,
+                       const void* K, const void* V, int io_type, void* O, float* lse) {
+    if (int rc = check_types("boat_cuda_attn_fwd", mma, io_type)) return rc;
+    if (units < 0 || S < 0 || hs < 0) return set_error(11, "boat_cuda_attn_fwd: negative size");
+    if (units == 0 || S == 0 || hs == 0) return 0;
+    if (!Q || !K || !V || !O || !lse) return set_error(11, "boat_cuda_attn_fwd: NULL operand");
+    if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type))
+        return attn_fwd_tc(mma, units, S, hs, causal, scale, Q, K, V, io_type, O, lse);
+    return attn_fwd_simt(units, S, hs, causal, scale, Q, K, V, io_type, O, lse);
+}
+
+size_t boat_cuda_attn_bwd_scratch_bytes(int mma, int64_t units, int64_t S, int64_t hs) {
+    size_t delta = (size_t)units * (size_t)S * sizeof(float);
+    delta = (delta + 255) & ~(size_t)255;
+    size_t extra = 0;
+    if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, mma == BOAT_MMA_BF16 ? BOAT_CUDA_BF16 : BOAT_CUDA_F32))
+        extra = attn_bwd_tc_scratch_bytes(mma, units, S, hs);
+    return delta + extra;
+}
+
+int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q,
+                       const void* K, const void* V, const void* O, const void* dO, const float* lse,
+                       int io_type, void* dQ, void* dK, void* dV, void* scratch, size_t scratch_bytes) {
+    if (int rc = check_types("boat_cuda_attn_bwd", mma, io_type)) return rc;
+    if (units < 0 || S < 0 || hs < 0) return set_error(11, "boat_cuda_attn_bwd: negative size");
+    if (units == 0 || S == 0 || hs == 0) return 0;
+    if (!Q || !K || !V || !O || !dO || !lse || !dQ || !dK || !dV) return set_error(11, "boat_cuda_attn_bwd: NULL operand");
+    size_t need = boat_cuda_attn_bwd_scratch_bytes(mma, units, S, hs);
+    if (!scratch || scratch_bytes < need)
+        return set_error(12, "boat_cuda_attn_bwd: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+    if (((uintptr_t)scratch & 255) != 0) return set_error(12, "boat_cuda_attn_bwd: scratch must be 256-byte aligned");
+    float* delta = (float*)scratch;
+    size_t delta_bytes = ((size_t)units * (size_t)S * sizeof(float) + 255) & ~(size_t)255;
+    if (int rc = rowdot(dO, O, io_type, units * S, hs, delta)) return rc;
+    if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type))
+        return attn_bwd_tc(mma, units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV,
+                           (char*)scratch + delta_bytes, scratch_bytes - delta_bytes);
+    return attn_bwd_simt(units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV);
+}
+
+}  // extern "C"

@@ -1,0 +1,186 @@
+// runtime.cu - device selection, the library stream, stream-ordered HBM allocation and
+// host<->HBM copies.  Stands in for the device stubs of the reference's memory layer
+// (src/core/memory.c:174-186 allocate_device/free_device and :230-247 copy/set, which were
+// malloc/memcpy/memset regardless of the device argument).
+#include "common.cuh"
+#include <stdarg.h>
+#include <stdlib.h>
+#include <string.h>
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+
+namespace boatcu {
+
+static thread_local char g_err[512] = "";
+static std::mutex g_mu;
+static bool g_ready = false;
+static int g_device = -1;
+static cudaStream_t g_stream = 0;
+static std::atomic<uint64_t> g_launches{0};
+static std::unordered_map<void*, size_t>* g_live = nullptr;
+static size_t g_live_bytes = 0;
+
+int set_error(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+cudaStream_t stream() { return g_stream; }
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+static int pick_device(int requested) {
+    if (requested >= 0) return requested;
+    const char* e = getenv("BOAT_CUDA_DEVICE");
+    if (e && *e) return atoi(e);
+    e = getenv("LOCAL_RANK");
+    if (e && *e) return atoi(e);
+    return 0;
+}
+
+static int init_locked(int device) {
+    if (g_ready) return 0;
+    int n = 0;
+    cudaError_t err = cudaGetDeviceCount(&n);
+    if (err != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return set_error(2, "no CUDA device available: %s",
+                         err == cudaSuccess ? "device count is 0" : cudaGetErrorString(err));
+    }
+    int dev = pick_device(device);
+    if (dev >= n) dev = dev % n;
+    BOATCU_CHECK(cudaSetDevice(dev));
+    cudaDeviceProp prop;
+    BOATCU_CHECK(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10) {
+        return set_error(3, "device %d is sm_%d%d; this library contains sm_100a code only",
+                         dev, prop.major, prop.minor);
+    }
+    // Keep freed blocks in the pool instead of returning them to the driver: a training
+    // step allocates and frees the same sizes every iteration.
+    cudaMemPool_t pool;
+    BOATCU_CHECK(cudaDeviceGetDefaultMemPool(&pool, dev));
+    uint64_t keep = UINT64_MAX;
+    BOATCU_CHECK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+    if (!g_live) g_live = new std::unordered_map<void*, size_t>();
+    g_device = dev;
+    g_ready = true;
+    return 0;
+}
+
+int ensure_init() {
+    if (g_ready) return 0;
+    std::lock_guard<std::mutex> lk(g_mu);
+    return init_locked(-1);
+}
+
+}  // namespace boatcu
+
+using namespace boatcu;
+
+extern "C" {
+
+int boat_cuda_init(int device) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    return init_locked(device);
+}
+
+int boat_cuda_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+const char* boat_cuda_last_error(void) { return g_err; }
+
+void* boat_cuda_stream(void) { return (void*)g_stream; }
+
+int boat_cuda_set_stream(void* s) {
+    g_stream = (cudaStream_t)s;
+    return 0;
+}
+
+int boat_cuda_sync(void) {
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaStreamSynchronize(g_stream));
+    return 0;
+}
+
+int boat_cuda_malloc(void** ptr, size_t bytes) {
+    if (!ptr) return set_error(4, "boat_cuda_malloc: NULL out pointer");
+    *ptr = nullptr;
+    if (bytes == 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaMallocAsync(ptr, bytes, g_stream));
+    std::lock_guard<std::mutex> lk(g_mu);
+    (*g_live)[*ptr] = bytes;
+    g_live_bytes += bytes;
+    return 0;
+}
+
+int boat_cuda_free(void* ptr) {
+    if (!ptr) return 0;
+    if (int rc = ensure_init()) return rc;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_live->find(ptr);
+        if (it == g_live->end()) return set_error(5, "boat_cuda_free: %p was not allocated here", ptr);
+        g_live_bytes -= it->second;
+        g_live->erase(it);
+    }
+    BOATCU_CHECK(cudaFreeAsync(ptr, g_stream));
+    return 0;
+}
+
+size_t boat_cuda_bytes_in_use(void) { return g_live_bytes; }
+uint64_t boat_cuda_launch_count(void) { return g_launches.load(); }
+
+int boat_cuda_memcpy_h2d(void* dst, const void* src, size_t bytes) {
+    if (bytes == 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g_stream));
+    BOATCU_CHECK(cudaStreamSynchronize(g_stream));
+    return 0;
+}
+
+int boat_cuda_memcpy_d2h(void* dst, const void* src, size_t bytes) {
+    if (bytes == 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g_stream));
+    BOATCU_CHECK(cudaStreamSynchronize(g_stream));
+    return 0;
+}
+
+int boat_cuda_memcpy_d2d(void* dst, const void* src, size_t bytes) {
+    if (bytes == 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, g_stream));
+    return 0;
+}
+
+int boat_cuda_memset(void* dst, int value, size_t bytes) {
+    if (bytes == 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaMemsetAsync(dst, value, bytes, g_stream));
+    return 0;
+}
+
+int boat_cuda_host_register(void* host, size_t bytes) {
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaHostRegister(host, bytes, cudaHostRegisterDefault));
+    return 0;
+}
+
+int boat_cuda_host_unregister(void* host) {
+    if (int rc = ensure_init()) return rc;
+    BOATCU_CHECK(cudaHostUnregister(host));
+    return 0;
+}
+
+}  // extern "C"

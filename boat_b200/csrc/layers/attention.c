@@ -1,0 +1,658 @@
+/* attention.c - host orchestration of the multi-head attention layer on the GPU.
+ *
+ * Same public behaviour as the reference layer (src/layers/attention.c): create/free
+ * (:126-244), forward (:310-466), backward (:468-732), SGD update (:734-815), the
+ * functional wrappers (:830-879, :1082-1117), the generic-layer adapter (:1119-1175) and
+ * the accessors (:1537-1631).  The arithmetic is not here: every contraction, softmax and
+ * reduction is a kernel behind boat_cuda.h.  This file decides what lives where:
+ *
+ *   - Parameters are FP32 tensors on the layer's device (host after create, HBM after
+ *     boat_attention_to_device).  Host parameters may be edited by the caller through
+ *     boat_tensor_data() at any time without notice (the reference's finite-difference
+ *     test does), so they are uploaded for every call; device parameters are used in place.
+ *   - Activations kept for backward are device buffers in the storage type of the chosen
+ *     arithmetic: the three projections, the pre-projection attention output and one
+ *     log-sum-exp per (unit,row).  The reference's [B,nh,S,S] probability cache
+ *     (:941-949) does not exist.
+ *   - The eight parameter gradients are windows into one flat FP32 bucket so that the
+ *     multi-GPU path reduces them with a single collective; each backward overwrites it
+ *     (the reference replaces the tensors, :653-654, :702-703 - same "no accumulation").
+ */
+#include "../core/boat_internal.h"
+#include <boat/layers.h>
+#include <boat_b200.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <strings.h>
+
+enum { WQ, WK, WV, WO, BQ, BK, BV, BO, NPARAM };
+
+struct boat_attention_t {
+    boat_attention_config_t config;
+    boat_tensor_t* param[NPARAM];       /* biases NULL without use_bias            */
+    boat_tensor_t* grad[NPARAM];        /* windows into grad_bucket                */
+    boat_tensor_t* grad_bucket;         /* FP32, on `device`                       */
+    boat_device_t  device;              /* where the parameters live               */
+    int            precision;           /* -1 automatic, else BOAT_MMA_*           */
+
+    /* state of the last forward, consumed by backward */
+    boat_tensor_t* cache_in[3];         /* query, key, value - referenced          */
+    bool           cached;
+    int            mma, type;           /* arithmetic and storage type it used     */
+    int64_t        B, S;
+    void*          d_in[3];             /* inputs on device in `type`              */
+    bool           d_in_owned[3];
+    void*          d_proj[3];           /* Qp, Kp, Vp [B*S, H]                     */
+    void*          d_ctx;               /* attention output before Wo              */
+    float*         d_lse;               /* [B*nh*S]                                */
+};
+
+/* ---- small helpers ---------------------------------------------------------------------- */
+
+static int storage_of(boat_dtype_t dt) { return dt == BOAT_DTYPE_BFLOAT16 ? BOAT_CUDA_BF16 : BOAT_CUDA_F32; }
+static size_t storage_size(int type) { return type == BOAT_CUDA_BF16 ? 2 : 4; }
+static bool dtype_ok(boat_dtype_t dt) { return dt == BOAT_DTYPE_FLOAT32 || dt == BOAT_DTYPE_BFLOAT16; }
+
+static void* dev_alloc(size_t bytes) {
+    void* p = NULL;
+    if (boat_report("device allocation", boat_cuda_malloc(&p, bytes)) != 0) return NULL;
+    return p;
+}
+
+static void dev_free(void* p) {
+    if (p) boat_report("device free", boat_cuda_free(p));
+}
+
+/* Device buffer holding tensor `t` in storage type `type`.  *owned says whether the caller
+ * must release it (false: it is the tensor's own HBM). */
+static void* stage_in(const boat_tensor_t* t, int type, bool* owned) {
+    int have = storage_of(t->dtype);
+    size_t n = t->nelements;
+    *owned = false;
+    if (t->device == BOAT_DEVICE_CUDA && have == type) return t->data;
+    *owned = true;
+    void* raw = t->data;
+    void* tmp = NULL;
+    if (t->device != BOAT_DEVICE_CUDA) {
+        tmp = dev_alloc(n * storage_size(have));
+        if (!tmp) return NULL;
+        if (boat_report("upload", boat_cuda_memcpy_h2d(tmp, t->data, n * storage_size(have))) != 0) {
+            dev_free(tmp);
+            return NULL;
+        }
+        if (have == type) return tmp;
+        raw = tmp;
+    }
+    void* out = dev_alloc(n * storage_size(type));
+    if (out && boat_report("cast", boat_cuda_cast(out, type, raw, have, (int64_t)n)) != 0) {
+        dev_free(out);
+        out = NULL;
+    }
+    dev_free(tmp);
+    return out;
+}
+
+/* New tensor with the dtype/device of `like`, filled from device buffer `src` (storage
+ * `type`, n elements).  `src` may be adopted as the tensor's memory when it already has the
+ * right type and place; *adopted tells the caller not to free it then. */
+static boat_tensor_t* emit_out(const int64_t* shape, size_t ndim, const boat_tensor_t* like, void* src,
+                               int type) {
+    boat_tensor_t* out = boat_tensor_create_uninit(shape, ndim, like->dtype, like->device);
+    if (!out) return NULL;
+    int want = storage_of(like->dtype);
+    size_t n = out->nelements;
+    int rc = 0;
+    if (like->device == BOAT_DEVICE_CUDA) {
+        rc = boat_cuda_cast(out->data, want, src, type, (int64_t)n);
+    } else if (want == type) {
+        rc = boat_cuda_memcpy_d2h(out->data, src, n * storage_size(type));
+    } else {
+        void* tmp = dev_alloc(n * storage_size(want));
+        rc = tmp ? boat_cuda_cast(tmp, want, src, type, (int64_t)n) : 1;
+        if (rc == 0) rc = boat_cuda_memcpy_d2h(out->data, tmp, n * storage_size(want));
+        dev_free(tmp);
+    }
+    if (boat_report("result transfer", rc) != 0) {
+        boat_tensor_free(out);
+        return NULL;
+    }
+    return out;
+}
+
+static int env_precision(void) {
+    const char* e = getenv("BOAT_MMA");
+    if (!e) return -1;
+    if (!strcasecmp(e, "fp32")) return BOAT_MMA_FP32;
+    if (!strcasecmp(e, "tf32")) return BOAT_MMA_TF32;
+    if (!strcasecmp(e, "bf16")) return BOAT_MMA_BF16;
+    return -1;
+}
+
+/* Arithmetic for a call: the explicit setting, else by input type and shape. */
+static int pick_mma(const boat_attention_t* a, const boat_tensor_t* q, int64_t S, int64_t hs) {
+    if (a->precision >= 0) return a->precision;
+    if (q->dtype == BOAT_DTYPE_BFLOAT16) return BOAT_MMA_BF16;
+    if (S >= 128 && S % 128 == 0 && (hs == 64 || hs == 128)) return BOAT_MMA_TF32;
+    return BOAT_MMA_FP32;
+}
+
+static void drop_forward_state(boat_attention_t* a) {
+    for (int i = 0; i < 3; ++i) {
+        if (a->d_in_owned[i]) {
+            /* the same staged buffer may serve several inputs (self-attention) */
+            for (int j = i + 1; j < 3; ++j)
+                if (a->d_in[j] == a->d_in[i]) a->d_in_owned[j] = false;
+            dev_free(a->d_in[i]);
+        }
+        a->d_in[i] = NULL;
+        a->d_in_owned[i] = false;
+        dev_free(a->d_proj[i]);
+        a->d_proj[i] = NULL;
+        if (a->cache_in[i]) boat_tensor_unref(a->cache_in[i]);
+        a->cache_in[i] = NULL;
+    }
+    dev_free(a->d_ctx);
+    a->d_ctx = NULL;
+    dev_free(a->d_lse);
+    a->d_lse = NULL;
+    a->cached = false;
+}
+
+/* Device copies of the parameters for one call: weights in storage `type`, biases FP32. */
+typedef struct {
+    void* w[4];
+    float* b[4];
+    bool w_owned[4], b_owned[4];
+} staged_params_t;
+
+static void release_params(staged_params_t* p) {
+    for (int i = 0; i < 4; ++i) {
+        if (p->w_owned[i]) dev_free(p->w[i]);
+        if (p->b_owned[i]) dev_free(p->b[i]);
+    }
+    memset(p, 0, sizeof *p);
+}
+
+static bool stage_params(const boat_attention_t* a, int type, staged_params_t* p) {
+    memset(p, 0, sizeof *p);
+    for (int i = 0; i < 4; ++i) {
+        p->w[i] = stage_in(a->param[WQ + i], type, &p->w_owned[i]);
+        if (!p->w[i]) goto fail;
+        if (a->param[BQ + i]) {
+            p->b[i] = (float*)stage_in(a->param[BQ + i], BOAT_CUDA_F32, &p->b_owned[i]);
+            if (!p->b[i]) goto fail;
+        }
+    }
+    return true;
+fail:
+    release_params(p);
+    return false;
+}
+
+/* ---- create / free ------------------------------------------------------------------------ */
+
+static boat_tensor_t* new_weight(size_t in, size_t out) {
+    const int64_t shape[2] = {(int64_t)in, (int64_t)out};
+    boat_tensor_t* w = boat_tensor_create(shape, 2, BOAT_DTYPE_FLOAT32, BOAT_DEVICE_CPU);
+    if (!w) return NULL;
+    /* Xavier/Glorot uniform from rand(), element order and formula of the reference
+     * (attention.c:100-104), so a seeded caller sees the same initial weights. */
+    float* v = (float*)w->data;
+    float bound = sqrtf(2.0f / (float)(in + out));
+    for (size_t i = 0; i < w->nelements; ++i) v[i] = ((float)rand() / RAND_MAX) * 2.0f * bound - bound;
+    return w;
+}
+
+boat_attention_t* boat_attention_create(const boat_attention_config_t* config) {
+    if (!config || config->hidden_size == 0 || config->num_heads == 0) return NULL;
+    if (config->hidden_size % config->num_heads != 0) return NULL;
+    boat_attention_t* a = (boat_attention_t*)boat_calloc(sizeof *a, BOAT_DEVICE_CPU);
+    if (!a) return NULL;
+    a->config = *config;
+    if (config->head_size == 0) a->config.head_size = config->hidden_size / config->num_heads;
+    a->device = BOAT_DEVICE_CPU;
+    a->precision = env_precision();
+    size_t H = config->hidden_size;
+    for (int i = 0; i < 4; ++i) {
+        a->param[WQ + i] = new_weight(H, H);
+        if (!a->param[WQ + i]) goto fail;
+    }
+    if (config->use_bias) {
+        const int64_t shape[1] = {(int64_t)H};
+        for (int i = 0; i < 4; ++i) {
+            a->param[BQ + i] = boat_tensor_create(shape, 1, BOAT_DTYPE_FLOAT32, BOAT_DEVICE_CPU);
+            if (!a->param[BQ + i]) goto fail;
+        }
+    }
+    return a;
+fail:
+    boat_attention_free(a);
+    return NULL;
+}
+
+void boat_attention_free(boat_attention_t* a) {
+    if (!a) return;
+    drop_forward_state(a);
+    for (int i = 0; i < NPARAM; ++i) {
+        if (a->param[i]) boat_tensor_free(a->param[i]);
+        if (a->grad[i]) boat_tensor_free(a->grad[i]);
+    }
+    if (a->grad_bucket) boat_tensor_free(a->grad_bucket);
+    boat_free(a);
+}
+
+/* ---- forward ------------------------------------------------------------------------------- */
+
+boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* query, const boat_tensor_t* key,
+                                      const boat_tensor_t* value, const boat_tensor_t* attention_mask) {
+    (void)attention_mask;                       /* ignored, as in the reference (attention.c:1022-1025) */
+    if (!a || !query || !key || !value) return NULL;
+    const boat_tensor_t* in[3] = {query, key, value};
+    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
+    const int64_t hs = (int64_t)a->config.head_size;
+    if (query->ndim != 3 || nh * hs != H) return NULL;
+    const int64_t B = query->shape[0], S = query->shape[1];
+    for (int i = 0; i < 3; ++i) {
+        if (!dtype_ok(in[i]->dtype) || in[i]->ndim != 3 || in[i]->shape[0] != B || in[i]->shape[1] != S ||
+            in[i]->shape[2] != H)
+            return NULL;
+    }
+    if (boat_report("CUDA start-up", boat_cuda_init(-1)) != 0) return NULL;
+
+    /* Take the new inputs before releasing the old ones: they may be the same tensors. */
+    for (int i = 0; i < 3; ++i) boat_tensor_ref((boat_tensor_t*)in[i]);
+    drop_forward_state(a);
+    for (int i = 0; i < 3; ++i) a->cache_in[i] = (boat_tensor_t*)in[i];
+
+    const int mma = pick_mma(a, query, S, hs);
+    const int type = mma == BOAT_MMA_BF16 ? BOAT_CUDA_BF16 : BOAT_CUDA_F32;
+    const int64_t T = B * S;
+    const size_t act_bytes = (size_t)T * (size_t)H * storage_size(type);
+    a->mma = mma;
+    a->type = type;
+    a->B = B;
+    a->S = S;
+
+    staged_params_t p;
+    void* d_out = NULL;
+    boat_tensor_t* result = NULL;
+    if (!stage_params(a, type, &p)) goto done;
+
+    for (int i = 0; i < 3; ++i) {
+        int same = -1;
+        for (int j = 0; j < i; ++j)
+            if (in[j] == in[i]) same = j;
+        if (same >= 0) {
+            a->d_in[i] = a->d_in[same];
+            a->d_in_owned[i] = false;
+        } else {
+            a->d_in[i] = stage_in(in[i], type, &a->d_in_owned[i]);
+            if (!a->d_in[i]) goto done;
+        }
+    }
+    for (int i = 0; i < 3; ++i) {
+        a->d_proj[i] = dev_alloc(act_bytes);
+        if (!a->d_proj[i]) goto done;
+        if (boat_report("projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_in[i], H, p.w[i], H, type,
+                                                     a->d_proj[i], H, type, p.b[i])) != 0)
+            goto done;
+    }
+    a->d_ctx = dev_alloc(act_bytes);
+    a->d_lse = (float*)dev_alloc((size_t)B * nh * S * sizeof(float));
+    if (!a->d_ctx || !a->d_lse) goto done;
+    /* [B,S,H] viewed as [B*nh, S, hs]: the head split is a reshape (attention.c:393-397). */
+    if (boat_report("attention core", boat_cuda_attn_fwd(mma, B * nh, S, hs, a->config.causal_mask,
+                                                         1.0f / sqrtf((float)hs), a->d_proj[0], a->d_proj[1],
+                                                         a->d_proj[2], type, a->d_ctx, a->d_lse)) != 0)
+        goto done;
+    /* The output projection writes the caller's dtype directly when that is a device
+     * storage type the GEMM can emit. */
+    {
+        int out_type = storage_of(query->dtype);
+        d_out = dev_alloc((size_t)T * H * storage_size(out_type));
+        if (!d_out) goto done;
+        if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_ctx, H, p.w[WO], H, type,
+                                                            d_out, H, out_type, p.b[WO])) != 0)
+            goto done;
+        result = emit_out(query->shape, 3, query, d_out, out_type);
+    }
+    if (result) a->cached = true;
+done:
+    dev_free(d_out);
+    release_params(&p);
+    if (!result) {
+        /* keep the input references (the reference does, attention.c:355-372) but no
+         * half-built device state */
+        boat_tensor_t* keep[3] = {a->cache_in[0], a->cache_in[1], a->cache_in[2]};
+        for (int i = 0; i < 3; ++i) a->cache_in[i] = NULL;
+        drop_forward_state(a);
+        for (int i = 0; i < 3; ++i) a->cache_in[i] = keep[i];
+    }
+    return result;
+}
+
+/* ---- backward ------------------------------------------------------------------------------ */
+
+static bool ensure_grads(boat_attention_t* a) {
+    if (a->grad_bucket && a->grad_bucket->device == a->device) return true;
+    for (int i = 0; i < NPARAM; ++i) {
+        if (a->grad[i]) boat_tensor_free(a->grad[i]);
+        a->grad[i] = NULL;
+    }
+    if (a->grad_bucket) boat_tensor_free(a->grad_bucket);
+    const int64_t H = (int64_t)a->config.hidden_size;
+    const bool bias = a->param[BQ] != NULL;
+    const int64_t total[1] = {4 * H * H + (bias ? 4 * H : 0)};
+    a->grad_bucket = boat_tensor_create(total, 1, BOAT_DTYPE_FLOAT32, a->device);
+    if (!a->grad_bucket) return false;
+    const int64_t wshape[2] = {H, H}, bshape[1] = {H};
+    for (int i = 0; i < 4; ++i) {
+        a->grad[WQ + i] = boat_tensor_window(a->grad_bucket, (size_t)i * H * H * 4, wshape, 2);
+        if (!a->grad[WQ + i]) return false;
+        if (bias) {
+            a->grad[BQ + i] = boat_tensor_window(a->grad_bucket, (size_t)(4 * H * H + i * H) * 4, bshape, 1);
+            if (!a->grad[BQ + i]) return false;
+        }
+    }
+    return true;
+}
+
+bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_output, boat_tensor_t** grad_query,
+                             boat_tensor_t** grad_key, boat_tensor_t** grad_value) {
+    if (!a || !grad_output) {
+        printf("[ERROR] boat_attention_backward: invalid arguments\n");
+        return false;
+    }
+    if (!a->cached) {
+        printf("[ERROR] boat_attention_backward: missing cached tensors\n");
+        return false;
+    }
+    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
+    const int64_t hs = (int64_t)a->config.head_size, B = a->B, S = a->S, T = B * S;
+    if (!dtype_ok(grad_output->dtype) || (int64_t)grad_output->nelements != T * H) {
+        printf("[ERROR] boat_attention_backward: grad_output does not match the cached forward\n");
+        return false;
+    }
+    const int mma = a->mma, type = a->type;
+    const size_t act_bytes = (size_t)T * (size_t)H * storage_size(type);
+    const bool bias = a->param[BQ] != NULL;
+    bool ok = false, go_owned = false;
+    staged_params_t p;
+    memset(&p, 0, sizeof p);
+    void *d_go = NULL, *d_dctx = NULL, *d_dproj[3] = {NULL, NULL, NULL}, *scratch = NULL, *d_dx = NULL;
+    float* d_bucket = NULL;
+    boat_tensor_t* gin[3] = {NULL, NULL, NULL};
+    size_t scratch_bytes;
+
+    if (!ensure_grads(a)) goto done;
+    if (!stage_params(a, type, &p)) goto done;
+    d_go = stage_in(grad_output, type, &go_owned);
+    if (!d_go) goto done;
+    /* gradients are produced in HBM; a host layer receives them with one copy at the end */
+    d_bucket = a->device == BOAT_DEVICE_CUDA ? (float*)a->grad_bucket->data
+                                             : (float*)dev_alloc(a->grad_bucket->nbytes);
+    if (!d_bucket) goto done;
+    float* d_dw[4];
+    float* d_db[4];
+    for (int i = 0; i < 4; ++i) {
+        d_dw[i] = d_bucket + (size_t)i * H * H;
+        d_db[i] = bias ? d_bucket + (size_t)4 * H * H + (size_t)i * H : NULL;
+    }
+
+    /* output projection: d(ctx) = dOut . Wo^T,  dWo = ctx^T . dOut,  dbo = colsum(dOut) */
+    d_dctx = dev_alloc(act_bytes);
+    if (!d_dctx) goto done;
+    if (boat_report("dOut.Wo^T", boat_cuda_gemm(mma, 0, 1, T, H, H, d_go, H, p.w[WO], H, type, d_dctx, H, type, NULL)) != 0) goto done;
+    if (boat_report("dWo", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_ctx, H, d_go, H, type, d_dw[WO], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
+    if (bias && boat_report("dbo", boat_cuda_colsum(d_go, type, T, H, d_db[WO])) != 0) goto done;
+
+    /* attention core */
+    for (int i = 0; i < 3; ++i) {
+        d_dproj[i] = dev_alloc(act_bytes);
+        if (!d_dproj[i]) goto done;
+    }
+    scratch_bytes = boat_cuda_attn_bwd_scratch_bytes(mma, B * nh, S, hs);
+    scratch = dev_alloc(scratch_bytes);
+    if (!scratch) goto done;
+    if (boat_report("attention core backward",
+                    boat_cuda_attn_bwd(mma, B * nh, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
+                                       a->d_proj[0], a->d_proj[1], a->d_proj[2], a->d_ctx, d_dctx, a->d_lse, type,
+                                       d_dproj[0], d_dproj[1], d_dproj[2], scratch, scratch_bytes)) != 0)
+        goto done;
+
+    /* input projections: dX = dP . W^T,  dW = X^T . dP,  db = colsum(dP) */
+    for (int i = 0; i < 3; ++i) {
+        const boat_tensor_t* x = a->cache_in[i];
+        int out_type = storage_of(x->dtype);
+        d_dx = dev_alloc((size_t)T * H * storage_size(out_type));
+        if (!d_dx) goto done;
+        if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, T, H, H, d_dproj[i], H, p.w[i], H, type, d_dx, H, out_type, NULL)) != 0) goto done;
+        if (boat_report("dW", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_in[i], H, d_dproj[i], H, type, d_dw[i], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
+        if (bias && boat_report("db", boat_cuda_colsum(d_dproj[i], type, T, H, d_db[i])) != 0) goto done;
+        gin[i] = emit_out(x->shape, 3, x, d_dx, out_type);
+        dev_free(d_dx);
+        d_dx = NULL;
+        if (!gin[i]) goto done;
+    }
+    if (a->device != BOAT_DEVICE_CUDA &&
+        boat_report("gradient download", boat_cuda_memcpy_d2h(a->grad_bucket->data, d_bucket, a->grad_bucket->nbytes)) != 0)
+        goto done;
+    ok = true;
+done:
+    dev_free(d_dx);
+    dev_free(scratch);
+    for (int i = 0; i < 3; ++i) dev_free(d_dproj[i]);
+    dev_free(d_dctx);
+    if (a->device != BOAT_DEVICE_CUDA) dev_free(d_bucket);
+    if (go_owned) dev_free(d_go);
+    release_params(&p);
+    if (!ok) {
+        for (int i = 0; i < 3; ++i)
+            if (gin[i]) boat_tensor_free(gin[i]);
+        return false;
+    }
+    boat_tensor_t** outp[3] = {grad_query, grad_key, grad_value};
+    for (int i = 0; i < 3; ++i) {
+        if (outp[i]) *outp[i] = gin[i];
+        else boat_tensor_free(gin[i]);
+    }
+    return true;
+}
+
+/* ---- update / setters ------------------------------------------------------------------------ */
+
+void boat_attention_update(boat_attention_t* a, float learning_rate) {
+    if (!a || !a->grad_bucket) return;
+    for (int i = 0; i < NPARAM; ++i) {
+        boat_tensor_t *w = a->param[i], *g = a->grad[i];
+        if (!w || !g) continue;
+        int64_t n = (int64_t)w->nelements;
+        if (a->device == BOAT_DEVICE_CUDA) {
+            boat_report("SGD step", boat_cuda_axpy((float*)w->data, (const float*)g->data, -learning_rate, n));
+            continue;
+        }
+        bool wo, go;
+        float* dw = (float*)stage_in(w, BOAT_CUDA_F32, &wo);
+        float* dg = (float*)stage_in(g, BOAT_CUDA_F32, &go);
+        if (dw && dg && boat_report("SGD step", boat_cuda_axpy(dw, dg, -learning_rate, n)) == 0)
+            boat_report("parameter download", boat_cuda_memcpy_d2h(w->data, dw, w->nbytes));
+        if (wo) dev_free(dw);
+        if (go) dev_free(dg);
+    }
+}
+
+BOAT_NOINLINE void boat_attention_set_dropout(boat_attention_t* a, float dropout_prob) {
+    if (a) a->config.dropout_prob = dropout_prob;
+}
+
+BOAT_NOINLINE void boat_attention_set_causal(boat_attention_t* a, bool causal) {
+    if (a) a->config.causal_mask = causal;
+}
+
+/* ---- functional wrappers ----------------------------------------------------------------------- */
+
+boat_tensor_t* boat_multihead_attention(const boat_tensor_t* input, size_t num_heads, float dropout_prob,
+                                        bool causal_mask, const boat_tensor_t* attention_mask) {
+    if (!input || input->ndim != 3 || num_heads == 0) return NULL;
+    size_t H = (size_t)input->shape[2];
+    if (H % num_heads != 0) return NULL;
+    boat_attention_config_t cfg = {H, num_heads, H / num_heads, dropout_prob, causal_mask, true, false, 10000.0f};
+    boat_attention_t* a = boat_attention_create(&cfg);
+    if (!a) return NULL;
+    boat_tensor_t* out = boat_attention_forward(a, input, input, input, attention_mask);
+    boat_attention_free(a);
+    return out;
+}
+
+boat_tensor_t* boat_scaled_dot_product_attention(const boat_tensor_t* query, const boat_tensor_t* key,
+                                                 const boat_tensor_t* value, float scale_factor,
+                                                 const boat_tensor_t* attention_mask, bool causal_mask,
+                                                 float dropout_prob) {
+    (void)attention_mask;
+    (void)dropout_prob;
+    if (!query || !key || !value) return NULL;
+    if (query->ndim < 3 || key->ndim < 3 || value->ndim < 3) return NULL;
+    if (query->ndim != 4 || key->ndim != 4 || value->ndim != 4) {
+        /* the reference answers anything but 4-D with a copy of `value` (attention.c:905-917) */
+        boat_tensor_t* copy = boat_tensor_create_uninit(value->shape, value->ndim, value->dtype, value->device);
+        if (copy) boat_memory_copy(copy->data, value->data, value->nbytes, copy->device, value->device);
+        return copy;
+    }
+    for (int d = 0; d < 4; ++d)
+        if (key->shape[d] != query->shape[d] || value->shape[d] != query->shape[d]) return NULL;
+    if (query->dtype != BOAT_DTYPE_FLOAT32 || key->dtype != BOAT_DTYPE_FLOAT32 || value->dtype != BOAT_DTYPE_FLOAT32)
+        return NULL;                                 /* FP32 only (attention.c:934-938) */
+    if (boat_report("CUDA start-up", boat_cuda_init(-1)) != 0) return NULL;
+    const int64_t units = query->shape[0] * query->shape[1], S = query->shape[2], hs = query->shape[3];
+    const boat_tensor_t* in[3] = {query, key, value};
+    void* d[3] = {NULL, NULL, NULL};
+    bool owned[3] = {false, false, false};
+    boat_tensor_t* out = NULL;
+    void* d_o = NULL;
+    float* d_lse = NULL;
+    for (int i = 0; i < 3; ++i) {
+        d[i] = stage_in(in[i], BOAT_CUDA_F32, &owned[i]);
+        if (!d[i]) goto done;
+    }
+    d_o = dev_alloc(query->nbytes);
+    d_lse = (float*)dev_alloc((size_t)units * S * sizeof(float));
+    if (!d_o || !d_lse) goto done;
+    if (boat_report("attention core", boat_cuda_attn_fwd(BOAT_MMA_FP32, units, S, hs, causal_mask, scale_factor,
+                                                         d[0], d[1], d[2], BOAT_CUDA_F32, d_o, d_lse)) != 0)
+        goto done;
+    out = emit_out(value->shape, 4, value, d_o, BOAT_CUDA_F32);
+done:
+    for (int i = 0; i < 3; ++i)
+        if (owned[i]) dev_free(d[i]);
+    dev_free(d_o);
+    dev_free(d_lse);
+    return out;
+}
+
+boat_tensor_t* boat_rotary_position_encoding(const boat_tensor_t* tensor, size_t seq_len, size_t head_size, float theta) {
+    (void)tensor; (void)seq_len; (void)head_size; (void)theta;
+    return NULL;
+}
+
+void boat_apply_rotary_embedding(boat_tensor_t* query, boat_tensor_t* key, size_t seq_len, size_t head_size, float theta) {
+    (void)query; (void)key; (void)seq_len; (void)head_size; (void)theta;
+}
+
+/* ---- generic-layer adapter ---------------------------------------------------------------------- */
+
+boat_attention_layer_t* boat_attention_layer_create(size_t hidden_size, size_t num_heads, float dropout_prob,
+                                                    bool causal_mask) {
+    if (num_heads == 0) return NULL;
+    boat_attention_config_t cfg = {hidden_size, num_heads, hidden_size / num_heads, dropout_prob, causal_mask,
+                                   true, false, 10000.0f};
+    return boat_attention_create(&cfg);   /* rejects hidden_size % num_heads != 0 */
+}
+
+void boat_attention_layer_free(boat_attention_layer_t* layer) { boat_attention_free(layer); }
+
+BOAT_NOINLINE boat_tensor_t* boat_attention_layer_forward(boat_attention_layer_t* layer, const boat_tensor_t* query,
+                                                          const boat_tensor_t* key, const boat_tensor_t* value,
+                                                          const boat_tensor_t* attention_mask) {
+    return boat_attention_forward(layer, query, key, value, attention_mask);
+}
+
+BOAT_NOINLINE boat_tensor_t* boat_attention_layer_backward(boat_attention_layer_t* layer,
+                                                           const boat_tensor_t* grad_output) {
+    boat_tensor_t *gq = NULL, *gk = NULL, *gv = NULL;
+    if (!boat_attention_backward(layer, grad_output, &gq, &gk, &gv)) return NULL;
+    if (gk) boat_tensor_free(gk);
+    if (gv) boat_tensor_free(gv);
+    return gq;
+}
+
+BOAT_NOINLINE void boat_attention_layer_update(boat_attention_layer_t* layer, float learning_rate) {
+    boat_attention_update(layer, learning_rate);
+}
+
+/* ---- accessors ------------------------------------------------------------------------------------ */
+
+#define ACCESSOR(name, field, idx) \
+    BOAT_NOINLINE boat_tensor_t* boat_attention_get_##name(const boat_attention_t* a) { return a ? a->field[idx] : NULL; }
+ACCESSOR(weight_q, param, WQ) ACCESSOR(weight_k, param, WK) ACCESSOR(weight_v, param, WV) ACCESSOR(weight_o, param, WO)
+ACCESSOR(bias_q, param, BQ) ACCESSOR(bias_k, param, BK) ACCESSOR(bias_v, param, BV) ACCESSOR(bias_o, param, BO)
+ACCESSOR(grad_weight_q, grad, WQ) ACCESSOR(grad_weight_k, grad, WK) ACCESSOR(grad_weight_v, grad, WV)
+ACCESSOR(grad_weight_o, grad, WO) ACCESSOR(grad_bias_q, grad, BQ) ACCESSOR(grad_bias_k, grad, BK)
+ACCESSOR(grad_bias_v, grad, BV) ACCESSOR(grad_bias_o, grad, BO)
+
+/* ---- GPU-only additions ------------------------------------------------------------------------------ */
+
+int boat_attention_to_device(boat_attention_t* a, boat_device_t device) {
+    if (!a || (device != BOAT_DEVICE_CPU && device != BOAT_DEVICE_CUDA)) return 1;
+    if (a->device == device) return 0;
+    boat_tensor_t* moved[NPARAM] = {0};
+    for (int i = 0; i < NPARAM; ++i) {
+        if (!a->param[i]) continue;
+        moved[i] = boat_tensor_to_device(a->param[i], device);
+        if (!moved[i]) {
+            for (int j = 0; j < i; ++j)
+                if (moved[j]) boat_tensor_free(moved[j]);
+            return 2;
+        }
+    }
+    boat_tensor_t* old_bucket = a->grad_bucket;
+    for (int i = 0; i < NPARAM; ++i) {
+        if (a->param[i]) boat_tensor_free(a->param[i]);
+        a->param[i] = moved[i];
+    }
+    a->device = device;
+    if (old_bucket) {
+        /* carry the gradient values over to the new place */
+        boat_tensor_ref(old_bucket);
+        if (ensure_grads(a))
+            boat_memory_copy(a->grad_bucket->data, old_bucket->data, old_bucket->nbytes, device, old_bucket->device);
+        boat_tensor_free(old_bucket);
+    }
+    return 0;
+}
+
+int boat_attention_set_precision(boat_attention_t* a, int mma) {
+    if (!a || mma < -1 || mma > BOAT_MMA_BF16) return 1;
+    a->precision = mma;
+    return 0;
+}
+
+int boat_attention_get_precision(const boat_attention_t* a) { return a ? a->precision : -1; }
+
+int boat_attention_grad_bucket(const boat_attention_t* a, float** data, size_t* nelements) {
+    if (!a) return 1;
+    if (data) *data = a->grad_bucket ? (float*)a->grad_bucket->data : NULL;
+    if (nelements) *nelements = a->grad_bucket ? a->grad_bucket->nelements : 0;
+    return 0;
+}
+
+int boat_attention_allreduce_grads(boat_attention_t* a) {
+    if (!a || !a->grad_bucket) return 1;
+    if (boat_cuda_comm_world() <= 1) return 0;
+    if (a->device != BOAT_DEVICE_CUDA) {
+        fprintf(stderr, "boat: gradient all-reduce needs the layer on BOAT_DEVICE_CUDA\n");
+        return 2;
+    }
+    return boat_report("gradient all-reduce",
+                       boat_cuda_allreduce_sum_f32((float*)a->grad_bucket->data, (int64_t)a->grad_bucket->nelements));
+}

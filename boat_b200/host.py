@@ -1,0 +1,222 @@
+"""Thin Python mirror of Boat's C interface for the attention path.
+
+Every method is one call into ``libboat_b200.so`` through the C ABI; numpy is used only to
+hand host bytes in and out.  The class and method names follow the C functions they wrap
+(``boat_tensor_*`` -> ``Tensor``, ``boat_attention_*`` -> ``Attention``, ``boat_variable_*``
+-> ``Variable``) so that tests read like the reference's own C tests.
+"""
+import ctypes as C
+import numpy as np
+
+from . import capi
+from .rng import to_bf16_bits, from_bf16_bits
+
+_NP_OF = {capi.DTYPE_FLOAT32: np.float32, capi.DTYPE_FLOAT64: np.float64}
+
+
+class BoatError(RuntimeError):
+    pass
+
+
+def _shape_arg(shape):
+    return (C.c_int64 * len(shape))(*shape), len(shape)
+
+
+class Tensor:
+    """Owns one reference of a ``boat_tensor_t``."""
+
+    def __init__(self, handle, own=True):
+        if not handle:
+            raise BoatError("NULL tensor: " + (capi.load().boat_cuda_last_error() or b"").decode())
+        self.h = C.c_void_p(handle) if not isinstance(handle, C.c_void_p) else handle
+        self.own = own
+
+    # ---- construction -------------------------------------------------------------------
+    @classmethod
+    def create(cls, shape, dtype=capi.DTYPE_FLOAT32, device=capi.DEVICE_CPU):
+        arr, n = _shape_arg(shape)
+        return cls(capi.load().boat_tensor_create(arr, n, dtype, device))
+
+    @classmethod
+    def from_numpy(cls, a, device=capi.DEVICE_CPU, bf16=False):
+        """Host FP32 array -> tensor on `device`; with bf16 the values are rounded to BF16
+        storage (dtype BOAT_DTYPE_BFLOAT16)."""
+        lib = capi.load()
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        payload = to_bf16_bits(a) if bf16 else a
+        dtype = capi.DTYPE_BFLOAT16 if bf16 else capi.DTYPE_FLOAT32
+        arr, n = _shape_arg(a.shape)
+        if device == capi.DEVICE_CPU:
+            return cls(lib.boat_tensor_from_data(arr, n, dtype, payload.ctypes.data_as(C.c_void_p)))
+        t = cls(lib.boat_tensor_create(arr, n, dtype, device))
+        lib.boat_memory_copy(lib.boat_tensor_data(t.h), payload.ctypes.data_as(C.c_void_p), payload.nbytes,
+                             capi.DEVICE_CUDA, capi.DEVICE_CPU)
+        return t
+
+    # ---- properties -----------------------------------------------------------------------
+    @property
+    def shape(self):
+        lib = capi.load()
+        p = lib.boat_tensor_shape(self.h)
+        return tuple(p[i] for i in range(lib.boat_tensor_ndim(self.h)))
+
+    @property
+    def dtype(self):
+        return capi.load().boat_tensor_dtype(self.h)
+
+    @property
+    def device(self):
+        return capi.load().boat_tensor_device(self.h)
+
+    @property
+    def data_ptr(self):
+        return capi.load().boat_tensor_data(self.h)
+
+    @property
+    def nbytes(self):
+        return capi.load().boat_tensor_nbytes(self.h)
+
+    def numpy(self):
+        """Copy out as a host FP32 (or FP64) array, whatever the device and storage type."""
+        lib = capi.load()
+        dt = self.dtype
+        raw = np.empty(self.nbytes, dtype=np.uint8)
+        lib.boat_memory_copy(raw.ctypes.data_as(C.c_void_p), lib.boat_tensor_data(self.h), self.nbytes,
+                             capi.DEVICE_CPU, self.device)
+        if dt == capi.DTYPE_BFLOAT16:
+            return from_bf16_bits(raw.view(np.uint16)).reshape(self.shape)
+        return raw.view(_NP_OF[dt]).reshape(self.shape).copy()
+
+    def host_view(self):
+        """Writable numpy view of a CPU tensor's own memory (the boat_tensor_data() pointer)."""
+        if self.device != capi.DEVICE_CPU:
+            raise BoatError("host_view needs a CPU tensor")
+        n = int(np.prod(self.shape))
+        buf = (C.c_float * n).from_address(self.data_ptr)
+        return np.frombuffer(buf, dtype=np.float32).reshape(self.shape)
+
+    def set(self, a):
+        """Overwrite the contents from a host FP32 array (H2D copy for CUDA tensors)."""
+        lib = capi.load()
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        payload = to_bf16_bits(a) if self.dtype == capi.DTYPE_BFLOAT16 else a
+        assert payload.nbytes == self.nbytes, (payload.nbytes, self.nbytes)
+        lib.boat_memory_copy(lib.boat_tensor_data(self.h), payload.ctypes.data_as(C.c_void_p), payload.nbytes,
+                             self.device, capi.DEVICE_CPU)
+
+    def free(self):
+        if self.own and self.h:
+            capi.load().boat_tensor_unref(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Attention:
+    """boat_attention_t."""
+
+    PARAMS = ("weight_q", "weight_k", "weight_v", "weight_o", "bias_q", "bias_k", "bias_v", "bias_o")
+
+    def __init__(self, hidden_size, num_heads, causal=False, use_bias=True, head_size=0, dropout=0.0):
+        cfg = capi.AttentionConfig(hidden_size, num_heads, head_size, dropout, causal, use_bias, False, 10000.0)
+        self.h = capi.load().boat_attention_create(C.byref(cfg))
+        if not self.h:
+            raise BoatError("boat_attention_create returned NULL")
+        self.h = C.c_void_p(self.h)
+
+    def param(self, name):
+        """Borrowed Tensor for "weight_q" ... "grad_bias_o" (None when the layer has none)."""
+        h = getattr(capi.load(), "boat_attention_get_" + name)(self.h)
+        return Tensor(h, own=False) if h else None
+
+    def set_params(self, **arrays):
+        for name, a in arrays.items():
+            self.param(name).set(a)
+
+    def to_device(self, device):
+        rc = capi.load().boat_attention_to_device(self.h, device)
+        if rc:
+            raise BoatError("boat_attention_to_device failed (%d)" % rc)
+
+    def set_precision(self, mma):
+        if capi.load().boat_attention_set_precision(self.h, mma):
+            raise BoatError("boat_attention_set_precision failed")
+
+    def forward(self, q, k=None, v=None):
+        k = q if k is None else k
+        v = q if v is None else v
+        out = capi.load().boat_attention_forward(self.h, q.h, k.h, v.h, None)
+        if not out:
+            raise BoatError("boat_attention_forward returned NULL: " +
+                            (capi.load().boat_cuda_last_error() or b"").decode())
+        return Tensor(out)
+
+    def backward(self, grad_output):
+        gq, gk, gv = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        ok = capi.load().boat_attention_backward(self.h, grad_output.h, C.byref(gq), C.byref(gk), C.byref(gv))
+        if not ok:
+            raise BoatError("boat_attention_backward failed: " +
+                            (capi.load().boat_cuda_last_error() or b"").decode())
+        return Tensor(gq.value), Tensor(gk.value), Tensor(gv.value)
+
+    def update(self, lr):
+        capi.load().boat_attention_update(self.h, lr)
+
+    def allreduce_grads(self):
+        rc = capi.load().boat_attention_allreduce_grads(self.h)
+        if rc:
+            raise BoatError("boat_attention_allreduce_grads failed (%d)" % rc)
+
+    def free(self):
+        if self.h:
+            capi.load().boat_attention_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def check(rc, what="boat_cuda call"):
+    if rc != 0:
+        raise BoatError("%s failed (%d): %s" % (what, rc, (capi.load().boat_cuda_last_error() or b"").decode()))
+
+
+class DeviceBuffer:
+    """Raw HBM block from boat_cuda_malloc, for tests that call the kernel ABI directly."""
+
+    def __init__(self, nbytes):
+        self.p = C.c_void_p()
+        self.nbytes = int(nbytes)
+        check(capi.load().boat_cuda_malloc(C.byref(self.p), self.nbytes), "boat_cuda_malloc")
+
+    @classmethod
+    def from_numpy(cls, a, bf16=False):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        payload = to_bf16_bits(a) if bf16 else a
+        b = cls(payload.nbytes)
+        check(capi.load().boat_cuda_memcpy_h2d(b.p, payload.ctypes.data_as(C.c_void_p), payload.nbytes), "h2d")
+        return b
+
+    def numpy(self, shape, bf16=False):
+        n = int(np.prod(shape))
+        raw = np.empty(n, dtype=np.uint16 if bf16 else np.float32)
+        check(capi.load().boat_cuda_memcpy_d2h(raw.ctypes.data_as(C.c_void_p), self.p, raw.nbytes), "d2h")
+        return (from_bf16_bits(raw) if bf16 else raw).reshape(shape)
+
+    def free(self):
+        if self.p:
+            capi.load().boat_cuda_free(self.p)
+        self.p = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

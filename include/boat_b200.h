@@ -1,0 +1,45 @@
+/* boat_b200.h - additions to Boat's C API that only make sense with a GPU behind it.
+ *
+ * None of these has a counterpart in the reference (its layer is host-only and FP32-only);
+ * they add capability and never change the meaning of a reference entry point.  A program
+ * that ignores this header gets the reference's behaviour with the arithmetic done on the
+ * GPU: host tensors in, host tensors out. */
+#ifndef BOAT_B200_H
+#define BOAT_B200_H
+
+#include "boat/tensor.h"
+#include "boat/layers/attention.h"
+#include "boat_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Move the layer's eight parameters (and from then on its gradients) to `device`.
+ * With BOAT_DEVICE_CUDA the accessors hand out CUDA tensors, nothing is uploaded per call
+ * and forward/backward accept CUDA inputs without host traffic.  Returns 0 on success. */
+BOAT_API int boat_attention_to_device(boat_attention_t* attention, boat_device_t device);
+
+/* Choose the arithmetic: BOAT_MMA_FP32 (exact CUDA-core path, any shape), BOAT_MMA_TF32
+ * or BOAT_MMA_BF16 (tcgen05 tensor-core paths; need seq_len % 128 == 0 and head size 64 or
+ * 128), or -1 for automatic: BF16 inputs -> BF16, FP32 inputs -> TF32 when the shape
+ * allows it and FP32 otherwise.  The default is taken from the environment variable
+ * BOAT_MMA (fp32 | tf32 | bf16 | auto), else automatic.  Returns 0 on success. */
+BOAT_API int boat_attention_set_precision(boat_attention_t* attention, int mma);
+BOAT_API int boat_attention_get_precision(const boat_attention_t* attention);
+
+/* The layer keeps its eight gradients back to back in one FP32 buffer, in the order
+ * dWq dWk dWv dWo dbq dbk dbv dbo; the accessor tensors are windows into it.  Gives its
+ * address (device memory for a CUDA layer, host memory otherwise) and element count;
+ * NULL / 0 before the first backward. */
+BOAT_API int boat_attention_grad_bucket(const boat_attention_t* attention, float** data, size_t* nelements);
+
+/* Sum the gradient bucket over all ranks of the communicator made with
+ * boat_cuda_comm_init (data-parallel training: every rank holds the same weights and a
+ * different slice of the batch).  No-op with a single rank.  Returns 0 on success. */
+BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BOAT_B200_H */

@@ -1,0 +1,122 @@
+/* boat_cuda.h - the extern "C" surface between the C host layer and the sm_100a kernels.
+ *
+ * Plain pointers and sizes only; every function returns 0 on success and a non-zero
+ * status otherwise (boat_cuda_last_error() has the text), never exits, and launches on the
+ * library stream (boat_cuda_stream()).  All pointers are DEVICE pointers unless a
+ * parameter says "host".
+ *
+ * Each entry names the piece of the reference it stands in for; paths are relative to the
+ * reference tree (xiaoshaoning/boat).
+ */
+#ifndef BOAT_CUDA_H
+#define BOAT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#pragma GCC visibility push(default)
+
+/* Storage type of a device buffer. */
+enum { BOAT_CUDA_F32 = 0, BOAT_CUDA_BF16 = 1 };
+
+/* Arithmetic used by the contraction kernels.
+ *   FP32: CUDA-core FMA, any shape (the exact path; reference numerics are IEEE FP32).
+ *   TF32: tcgen05 kind::tf32 on FP32 storage, FP32 accumulate in tensor memory.
+ *   BF16: tcgen05 kind::f16 on BF16 storage, FP32 accumulate in tensor memory. */
+enum { BOAT_MMA_FP32 = 0, BOAT_MMA_TF32 = 1, BOAT_MMA_BF16 = 2 };
+
+/* ---- runtime: replaces the host-only device stubs of src/core/memory.c:174-186,
+ *      :230-247 (allocate / copy / set "on device" were malloc/memcpy/memset) ---------- */
+int         boat_cuda_init(int device);          /* idempotent; device < 0: env BOAT_CUDA_DEVICE or LOCAL_RANK or 0 */
+int         boat_cuda_device_count(void);        /* 0 when no usable GPU / driver */
+const char* boat_cuda_last_error(void);
+void*       boat_cuda_stream(void);              /* cudaStream_t the library launches on */
+int         boat_cuda_set_stream(void* stream);
+int         boat_cuda_sync(void);                /* wait for the library stream */
+int         boat_cuda_malloc(void** ptr, size_t bytes);   /* stream-ordered pool allocation */
+int         boat_cuda_free(void* ptr);
+int         boat_cuda_memcpy_h2d(void* dst, const void* src_host, size_t bytes);  /* returns after arrival */
+int         boat_cuda_memcpy_d2h(void* dst_host, const void* src, size_t bytes);  /* returns after arrival */
+int         boat_cuda_memcpy_d2d(void* dst, const void* src, size_t bytes);       /* asynchronous on the stream */
+int         boat_cuda_memset(void* dst, int value, size_t bytes);
+int         boat_cuda_host_register(void* host, size_t bytes);   /* pin a caller buffer for fast copies */
+int         boat_cuda_host_unregister(void* host);
+size_t      boat_cuda_bytes_in_use(void);        /* bytes handed out by boat_cuda_malloc and not yet freed */
+uint64_t    boat_cuda_launch_count(void);        /* kernels of this library launched so far */
+
+/* ---- contraction: replaces boat_matmul (src/ops/linear.c:12-170) as used by
+ *      linear_projection (src/layers/attention.c:247-308) and
+ *      linear_projection_backward (attention.c:1186-1293), including the materialised
+ *      boat_transpose calls (linear.c:238-406) that those make --------------------------
+ * C[M,N] = op(A) . op(B) (+ bias[N] broadcast over rows), row-major, leading dimensions in
+ * elements.  trans_a: A is stored [K,M];  trans_b: B is stored [N,K].
+ *   forward projection   Y  = X . W + b      trans_a=0 trans_b=0
+ *   input gradient       dX = dY . W^T       trans_a=0 trans_b=1
+ *   weight gradient      dW = X^T . dY       trans_a=1 trans_b=0
+ * in_type is the storage type of A and B (F32 for mma FP32/TF32, BF16 for mma BF16);
+ * out_type the storage type of C; bias is FP32 or NULL. */
+int boat_cuda_gemm(int mma, int trans_a, int trans_b, int64_t M, int64_t N, int64_t K,
+                   const void* A, int64_t lda, const void* B, int64_t ldb, int in_type,
+                   void* C, int64_t ldc, int out_type, const float* bias);
+
+/* ---- attention core: replaces scaled_dot_product_attention_impl
+ *      (src/layers/attention.c:882-1079) ------------------------------------------------
+ * Q,K,V,O are [units, S, hs] contiguous: unit u = (b*nh + h) is the block at element
+ * u*S*hs - the reference's reshape-only head split (attention.c:393-397).
+ * O = softmax(scale * Q K^T, causal: j>i masked) V.  The S x S probabilities are never
+ * stored; lse[units*S] (FP32) receives max + log(sum exp) of the scaled scores per row,
+ * which is all the backward needs. */
+int boat_cuda_attn_fwd(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale,
+                       const void* Q, const void* K, const void* V, int io_type,
+                       void* O, float* lse);
+
+/* ---- attention core backward: replaces attention_backward
+ *      (src/layers/attention.c:1388-1534) -----------------------------------------------
+ * Recomputes P = exp(scale*QK^T - lse) tile by tile and produces
+ *   dV = P^T dO, dP = dO V^T, dS = P * (dP - delta) * scale, dQ = dS K, dK = dS^T Q
+ * with delta_i = sum_d dO[i,d]*O[i,d] (equal to the reference's sum_j dP_ij P_ij,
+ * attention.c:1472-1488).  `scratch` is device memory the kernels may use freely:
+ * boat_cuda_attn_bwd_scratch_bytes() gives the size needed for a problem. */
+size_t boat_cuda_attn_bwd_scratch_bytes(int mma, int64_t units, int64_t S, int64_t hs);
+int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale,
+                       const void* Q, const void* K, const void* V, const void* O,
+                       const void* dO, const float* lse, int io_type,
+                       void* dQ, void* dK, void* dV, void* scratch, size_t scratch_bytes);
+
+/* ---- element-wise / reduction tail ----------------------------------------------------
+ * colsum:  out[j] = sum_i X[i,j]     bias gradient loop, attention.c:1271-1284
+ * axpy:    y += alpha * x            boat_add_ (arithmetic.c:362-391) with alpha = 1 for
+ *                                    gradient accumulation (autodiff.c:2495-2525);
+ *                                    alpha = -lr for the SGD step, i.e. boat_mul_scalar +
+ *                                    boat_sub_ (attention.c:745-812)
+ * scale:   y = alpha * x             boat_mul_scalar (arithmetic.c:425-484)
+ * add_bias: y[i,j] = x[i,j] + b[j]   boat_add bias broadcast (arithmetic.c:199-203)
+ * mul:     y = a * b                 boat_mul, equal shapes (arithmetic.c:240-285)
+ * cast:    FP32 <-> BF16, round to nearest even
+ * transpose: out[b, j, i] = in[b, i, j]   boat_transpose of the last two dims (linear.c:238-406) */
+int boat_cuda_colsum(const void* X, int x_type, int64_t rows, int64_t cols, float* out);
+int boat_cuda_axpy(float* y, const float* x, float alpha, int64_t n);
+int boat_cuda_scale(float* y, const float* x, float alpha, int64_t n);
+int boat_cuda_add_bias(float* y, const float* x, const float* bias, int64_t rows, int64_t cols);
+int boat_cuda_mul(float* y, const float* a, const float* b, int64_t n);
+int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64_t n);
+int boat_cuda_transpose(float* out, const float* in, int64_t batch, int64_t rows, int64_t cols);
+
+/* ---- gradient exchange between GPUs (nothing in the reference: it is single-process) ---
+ * One process per GPU.  Rank 0 makes an id (128 bytes) and hands it to the others by any
+ * host channel; every rank then calls comm_init.  allreduce sums an FP32 buffer in place
+ * across ranks on the library stream. */
+int boat_cuda_comm_unique_id(void* id_out_host_128B);
+int boat_cuda_comm_init(int rank, int world, const void* id_host_128B);
+int boat_cuda_comm_world(void);                 /* 1 when no communicator exists */
+int boat_cuda_allreduce_sum_f32(float* buf, int64_t n);
+int boat_cuda_comm_destroy(void);
+
+#pragma GCC visibility pop
+#ifdef __cplusplus
+}
+#endif
+#endif /* BOAT_CUDA_H */

@@ -1,0 +1,282 @@
+"""Python access to the CPU checkers.  TEST INFRASTRUCTURE, NOT PRODUCT.
+
+Two checkers, same call shape:
+
+* ``port_step``  - ``liboracle.so``, our plain-C restatement (``attention_oracle.c``).
+* ``ref_step``   - ``_ref/libboat_ref.so``, the reference itself compiled from its own
+  sources (see ``Makefile``), driven through its public C API exactly as its tests drive it:
+  ``boat_attention_create``, weights written through the accessors, ``boat_attention_forward``,
+  ``boat_attention_backward``.
+
+Only ``tests/``, the smoke check and the benchmark's CPU-baseline legs import this module.
+"""
+import contextlib
+import ctypes as C
+import os
+import subprocess
+import tempfile
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+PORT_PATH = os.path.join(_HERE, "liboracle.so")
+REF_PATH = os.path.join(_HERE, "_ref", "libboat_ref.so")
+
+_port = None
+_ref = None
+
+_FP = C.POINTER(C.c_float)
+_FP4 = _FP * 4
+
+
+def build():
+    """Compile liboracle.so and, when the reference tree is present, _ref/libboat_ref.so."""
+    proc = subprocess.run(["make", "-C", _HERE], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("building the oracle failed:\n" + proc.stdout[-4000:])
+
+
+def have_ref():
+    return os.path.exists(REF_PATH)
+
+
+def _fp(a):
+    return a.ctypes.data_as(_FP) if a is not None else None
+
+
+def port():
+    global _port
+    if _port is None:
+        if not os.path.exists(PORT_PATH):
+            build()
+        lib = C.CDLL(PORT_PATH)
+        lib.oracle_attention_step.restype = C.c_int
+        lib.oracle_attention_step.argtypes = [C.c_int64] * 4 + [C.c_int] + [_FP] * 3 + [C.c_void_p, C.c_void_p] + \
+            [_FP] * 5 + [C.c_void_p, C.c_void_p, _FP]
+        lib.oracle_attention_core.restype = C.c_int
+        lib.oracle_attention_core.argtypes = [C.c_int64] * 3 + [C.c_int, C.c_float] + [_FP] * 8
+        lib.oracle_sgd.restype = None
+        lib.oracle_sgd.argtypes = [_FP, _FP, C.c_float, C.c_int64]
+        lib.oracle_threads.restype = C.c_int
+        lib.oracle_set_threads.argtypes = [C.c_int]
+        _port = lib
+    return _port
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def port_step(q, k, v, w, b, dout, nh, causal, want_lse=False):
+    """Forward (+ backward when dout is given) through the C restatement.
+
+    q,k,v,dout: [B,S,H]; w: four [H,H] arrays (Wq,Wk,Wv,Wo, stored [in,out]); b: four [H]
+    arrays or None.  Returns a dict with out, and dq,dk,dv,dw (list of 4),db (list of 4 or
+    None) after a backward, lse when asked.
+    """
+    lib = port()
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    B, S, H = q.shape
+    w = [_f32(x) for x in w]
+    b = [_f32(x) for x in b] if b is not None else None
+    res = {"out": np.empty_like(q)}
+    warr = _FP4(*[_fp(x) for x in w])
+    barr = _FP4(*[_fp(x) for x in b]) if b is not None else None
+    lse = np.empty(B * nh * S, dtype=np.float32) if want_lse else None
+    if dout is not None:
+        dout = _f32(dout)
+        res.update(dq=np.empty_like(q), dk=np.empty_like(q), dv=np.empty_like(q),
+                   dw=[np.empty((H, H), np.float32) for _ in range(4)],
+                   db=[np.empty(H, np.float32) for _ in range(4)] if b is not None else None)
+        dwarr = _FP4(*[_fp(x) for x in res["dw"]])
+        dbarr = _FP4(*[_fp(x) for x in res["db"]]) if b is not None else None
+        rc = lib.oracle_attention_step(B, S, H, nh, int(causal), _fp(q), _fp(k), _fp(v),
+                                       C.cast(warr, C.c_void_p), C.cast(barr, C.c_void_p) if barr else None,
+                                       _fp(dout), _fp(res["out"]), _fp(res["dq"]), _fp(res["dk"]), _fp(res["dv"]),
+                                       C.cast(dwarr, C.c_void_p), C.cast(dbarr, C.c_void_p) if dbarr else None,
+                                       _fp(lse))
+    else:
+        rc = lib.oracle_attention_step(B, S, H, nh, int(causal), _fp(q), _fp(k), _fp(v),
+                                       C.cast(warr, C.c_void_p), C.cast(barr, C.c_void_p) if barr else None,
+                                       None, _fp(res["out"]), None, None, None, None, None, _fp(lse))
+    if rc != 0:
+        raise MemoryError("oracle_attention_step ran out of memory")
+    if want_lse:
+        res["lse"] = lse.reshape(B * nh, S)
+    return res
+
+
+def port_core(q, k, v, dout, causal, scale):
+    """Attention core alone on [units,S,hs] arrays: dict with o (and dq,dk,dv if dout given)."""
+    lib = port()
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    units, S, hs = q.shape
+    res = {"o": np.empty_like(q)}
+    if dout is not None:
+        dout = _f32(dout)
+        res.update(dq=np.empty_like(q), dk=np.empty_like(q), dv=np.empty_like(q))
+    rc = lib.oracle_attention_core(units, S, hs, int(causal), float(scale), _fp(q), _fp(k), _fp(v), _fp(dout),
+                                   _fp(res["o"]), _fp(res.get("dq")), _fp(res.get("dk")), _fp(res.get("dv")))
+    if rc != 0:
+        raise MemoryError("oracle_attention_core ran out of memory")
+    return res
+
+
+def port_sgd(param, grad, lr):
+    p = _f32(param).copy()
+    port().oracle_sgd(_fp(p), _fp(_f32(grad)), float(lr), p.size)
+    return p
+
+
+# ---- the reference itself ---------------------------------------------------------------------
+
+class _RefConfig(C.Structure):
+    _fields_ = [("hidden_size", C.c_size_t), ("num_heads", C.c_size_t), ("head_size", C.c_size_t),
+                ("dropout_prob", C.c_float), ("causal_mask", C.c_bool), ("use_bias", C.c_bool),
+                ("use_rotary", C.c_bool), ("rotary_theta", C.c_float)]
+
+
+def ref():
+    """The reference library (its own code), typed for the handful of calls used here."""
+    global _ref
+    if _ref is None:
+        if not have_ref():
+            raise FileNotFoundError(REF_PATH + " is not built (needs the reference source tree, see oracle/Makefile)")
+        lib = C.CDLL(REF_PATH, mode=os.RTLD_LOCAL | os.RTLD_NOW)
+        P = C.c_void_p
+        lib.boat_tensor_create.restype = P
+        lib.boat_tensor_create.argtypes = [C.POINTER(C.c_int64), C.c_size_t, C.c_int, C.c_int]
+        lib.boat_tensor_data.restype = P
+        lib.boat_tensor_data.argtypes = [P]
+        lib.boat_tensor_nelements.restype = C.c_size_t
+        lib.boat_tensor_nelements.argtypes = [P]
+        lib.boat_tensor_unref.argtypes = [P]
+        lib.boat_attention_create.restype = P
+        lib.boat_attention_create.argtypes = [C.POINTER(_RefConfig)]
+        lib.boat_attention_free.argtypes = [P]
+        lib.boat_attention_forward.restype = P
+        lib.boat_attention_forward.argtypes = [P] * 5
+        lib.boat_attention_backward.restype = C.c_bool
+        lib.boat_attention_backward.argtypes = [P, P, C.POINTER(P), C.POINTER(P), C.POINTER(P)]
+        lib.boat_attention_update.argtypes = [P, C.c_float]
+        for kind in ("weight", "bias", "grad_weight", "grad_bias"):
+            for p in "qkvo":
+                fn = getattr(lib, "boat_attention_get_%s_%s" % (kind, p))
+                fn.restype = P
+                fn.argtypes = [P]
+        _ref = lib
+    return _ref
+
+
+@contextlib.contextmanager
+def _quiet_scratch_cwd():
+    """The reference's backward prints [DEBUG] lines and appends to a file with a Windows
+    path name in the current directory (src/layers/attention.c:478-488): run it in a scratch
+    directory with stdout pointed at /dev/null."""
+    old_cwd = os.getcwd()
+    saved = os.dup(1)
+    devnull = os.open(os.devnull, os.O_WRONLY)
+    with tempfile.TemporaryDirectory() as tmp:
+        os.chdir(tmp)
+        os.dup2(devnull, 1)
+        try:
+            yield
+        finally:
+            C.CDLL(None).fflush(None)
+            os.dup2(saved, 1)
+            os.close(saved)
+            os.close(devnull)
+            os.chdir(old_cwd)
+
+
+class RefTensor:
+    def __init__(self, lib, h):
+        self.lib, self.h = lib, h
+
+    def view(self, shape=None):
+        n = self.lib.boat_tensor_nelements(self.h)
+        buf = (C.c_float * n).from_address(self.lib.boat_tensor_data(self.h))
+        a = np.frombuffer(buf, dtype=np.float32)
+        return a.reshape(shape) if shape is not None else a
+
+
+def _ref_new(lib, a):
+    shape = (C.c_int64 * a.ndim)(*a.shape)
+    h = lib.boat_tensor_create(shape, a.ndim, 1, 0)          # FLOAT32, CPU
+    RefTensor(lib, h).view()[:] = a.ravel()
+    return h
+
+
+class RefLayer:
+    """A reference attention layer with weights written through the accessors."""
+
+    def __init__(self, H, nh, causal, w, b):
+        lib = ref()
+        self.lib = lib
+        cfg = _RefConfig(H, nh, H // nh, 0.0, bool(causal), b is not None, False, 10000.0)
+        self.h = lib.boat_attention_create(C.byref(cfg))
+        if not self.h:
+            raise RuntimeError("reference boat_attention_create returned NULL")
+        for i, p in enumerate("qkvo"):
+            RefTensor(lib, getattr(lib, "boat_attention_get_weight_" + p)(self.h)).view()[:] = _f32(w[i]).ravel()
+            if b is not None:
+                RefTensor(lib, getattr(lib, "boat_attention_get_bias_" + p)(self.h)).view()[:] = _f32(b[i]).ravel()
+
+    def step(self, q, k, v, dout):
+        lib = self.lib
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        B, S, H = q.shape
+        hq = _ref_new(lib, q)
+        hk = hq if k is q else _ref_new(lib, k)
+        hv = hq if v is q else _ref_new(lib, v)
+        res = {}
+        with _quiet_scratch_cwd():
+            ho = lib.boat_attention_forward(self.h, hq, hk, hv, None)
+            if not ho:
+                raise RuntimeError("reference forward returned NULL")
+            res["out"] = RefTensor(lib, ho).view((B, S, H)).copy()
+            if dout is not None:
+                hg = _ref_new(lib, _f32(dout))
+                gq, gk, gv = C.c_void_p(), C.c_void_p(), C.c_void_p()
+                ok = lib.boat_attention_backward(self.h, hg, C.byref(gq), C.byref(gk), C.byref(gv))
+                if not ok:
+                    raise RuntimeError("reference backward failed")
+                for name, g in (("dq", gq), ("dk", gk), ("dv", gv)):
+                    res[name] = RefTensor(lib, g.value).view((B, S, H)).copy()
+                    lib.boat_tensor_unref(g)
+                res["dw"] = [RefTensor(lib, getattr(lib, "boat_attention_get_grad_weight_" + p)(self.h))
+                             .view((H, H)).copy() for p in "qkvo"]
+                hb = lib.boat_attention_get_grad_bias_q(self.h)
+                res["db"] = [RefTensor(lib, getattr(lib, "boat_attention_get_grad_bias_" + p)(self.h))
+                             .view((H,)).copy() for p in "qkvo"] if hb else None
+                lib.boat_tensor_unref(hg)
+            lib.boat_tensor_unref(ho)
+        for h in {hq, hk, hv}:
+            lib.boat_tensor_unref(h)
+        return res
+
+    def update(self, lr):
+        self.lib.boat_attention_update(self.h, lr)
+
+    def weights(self):
+        H = None
+        out = []
+        for p in "qkvo":
+            a = RefTensor(self.lib, getattr(self.lib, "boat_attention_get_weight_" + p)(self.h)).view()
+            H = int(round(a.size ** 0.5))
+            out.append(a.reshape(H, H).copy())
+        return out
+
+    def free(self):
+        if self.h:
+            self.lib.boat_attention_free(self.h)
+        self.h = None
+
+
+def ref_step(q, k, v, w, b, dout, nh, causal):
+    """Same contract as port_step, computed by the reference's own code."""
+    layer = RefLayer(np.shape(q)[2], nh, causal, w, b)
+    try:
+        return layer.step(q, k, v, dout)
+    finally:
+        layer.free()

@@ -1,0 +1,77 @@
+"""Seeded attention-step problems shared by the golden-vector generator and the tests.
+
+Inputs follow the configurations of the benchmark specification: X ~ N(0, std_x),
+W ~ N(0, std_w), upstream gradient ~ N(0, 1); seed 42 and fixed tensor ids
+(boat_b200.rng).  `self_attn` means query = key = value (one tensor), as in the workload.
+"""
+import numpy as np
+
+from boat_b200 import rng
+
+SEED = 42
+
+
+class Case:
+    def __init__(self, name, B, S, H, nh, causal=False, bias=True, self_attn=True, std_x=1.0, std_w=None,
+                 bias_std=0.0):
+        self.name, self.B, self.S, self.H, self.nh = name, B, S, H, nh
+        self.causal, self.bias, self.self_attn = causal, bias, self_attn
+        self.std_x = std_x
+        self.std_w = std_w if std_w is not None else 1.0 / np.sqrt(H)
+        self.bias_std = bias_std
+
+    def inputs(self, bf16=False):
+        """dict: q,k,v,dout [B,S,H]; w (4 x [H,H]); b (4 x [H]) or None.  With bf16 every
+        value is rounded to BF16 first (still FP32 arrays), so that a BF16 device path and
+        the FP32 CPU checker start from identical numbers."""
+        shape = (self.B, self.S, self.H)
+        f = rng.bf16_round if bf16 else (lambda a: a)
+        q = f(rng.normal(SEED, rng.X, shape, self.std_x))
+        if self.self_attn:
+            k = v = q
+        else:
+            k = f(rng.normal(SEED, rng.KEY, shape, self.std_x))
+            v = f(rng.normal(SEED, rng.VALUE, shape, self.std_x))
+        w = [f(rng.normal(SEED, rng.WQ + i, (self.H, self.H), self.std_w)) for i in range(4)]
+        b = None
+        if self.bias:
+            b = [rng.normal(SEED, rng.BQ + i, (self.H,), self.bias_std) if self.bias_std > 0
+                 else np.zeros(self.H, np.float32) for i in range(4)]
+        dout = f(rng.normal(SEED, rng.DOUT, shape, 1.0))
+        return dict(q=q, k=k, v=v, w=w, b=b, dout=dout)
+
+
+# Small problems whose reference outputs are committed under tests/golden/.
+GOLDEN_CASES = [
+    # the reference's CPU-runnable configuration: B=2, S=64, d=64, 4 heads, N(0,0.02), zero bias
+    Case("c1", 2, 64, 64, 4, std_x=0.02, std_w=0.02),
+    Case("c1_causal_bias", 2, 64, 64, 4, causal=True, std_x=0.02, std_w=0.02, bias_std=0.1),
+    # shape of the reference's own attention tests (B=2, S=4, H=32, 4 heads), distinct q/k/v
+    Case("reftest_shape", 2, 4, 32, 4, self_attn=False, bias_std=0.1),
+    # ragged: S not a multiple of anything useful, 3 heads of 16, causal, no bias
+    Case("ragged_causal_nobias", 1, 37, 48, 3, causal=True, bias=False, self_attn=False),
+    # one token: softmax over a single score
+    Case("single_token", 3, 1, 16, 2, bias_std=0.1),
+    # 128-row tile boundary with head size 64 (shapes the tensor-core kernels take)
+    Case("tile_128x64", 1, 128, 128, 2, causal=True, bias_std=0.1),
+]
+
+RESULT_KEYS = ("out", "dq", "dk", "dv", "dw0", "dw1", "dw2", "dw3", "db0", "db1", "db2", "db3")
+
+
+def flatten_result(res):
+    """dict from oracle.port_step/ref_step or the GPU path -> flat dict of arrays."""
+    flat = {k: res[k] for k in ("out", "dq", "dk", "dv")}
+    for i in range(4):
+        flat["dw%d" % i] = res["dw"][i]
+        if res.get("db") is not None:
+            flat["db%d" % i] = res["db"][i]
+    return flat
+
+
+def rel_err(a, ref):
+    """max|a - ref| / max|ref|, the error measure of the benchmark specification."""
+    a = np.asarray(a, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    denom = np.abs(ref).max()
+    return float(np.abs(a - ref).max() / denom) if denom > 0 else float(np.abs(a).max())

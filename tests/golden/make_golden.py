@@ -1,0 +1,54 @@
+"""Regenerate tests/golden/attention_golden.npz from the reference itself.
+
+Run in a checkout that has the reference tree (oracle/Makefile builds
+oracle/_ref/libboat_ref.so from it):
+
+    python tests/golden/make_golden.py
+
+For every case in tests/cases.py::GOLDEN_CASES the reference's own boat_attention_forward
+and boat_attention_backward are executed on the seeded inputs and every output and gradient
+is stored (FP32, bit patterns as the reference produced them), together with a checksum of
+the inputs so that drift of the input generator is noticed.
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from oracle import oracle          # noqa: E402
+import cases                       # noqa: E402
+
+
+def input_digest(inp):
+    h = hashlib.sha256()
+    for key in ("q", "k", "v", "dout"):
+        h.update(np.ascontiguousarray(inp[key]).tobytes())
+    for w in inp["w"]:
+        h.update(np.ascontiguousarray(w).tobytes())
+    for b in inp["b"] or []:
+        h.update(np.ascontiguousarray(b).tobytes())
+    return h.hexdigest()
+
+
+def main():
+    oracle.build()
+    out = {}
+    for case in cases.GOLDEN_CASES:
+        inp = case.inputs()
+        res = oracle.ref_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], case.nh, case.causal)
+        for key, val in cases.flatten_result(res).items():
+            out["%s/%s" % (case.name, key)] = val
+        out["%s/digest" % case.name] = np.frombuffer(input_digest(inp).encode(), dtype=np.uint8)
+        print(case.name, "ok")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "attention_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()
