@@ -75,3 +75,21 @@ def rel_err(a, ref):
     ref = np.asarray(ref, dtype=np.float64)
     denom = np.abs(ref).max()
     return float(np.abs(a - ref).max() / denom) if denom > 0 else float(np.abs(a).max())
+
+
+def errors(res, ref):
+    """Per-tensor max|res - ref| / max|ref| for two flat result dicts.
+
+    The key-bias gradient is identically zero in exact arithmetic (adding a constant to
+    every key shifts all scores of a query alike, which the softmax ignores), so the
+    reference value of db1 is round-off noise; the four bias gradients are therefore
+    measured against their common largest magnitude."""
+    db_scale = max([float(np.abs(ref[k]).max()) for k in ref if k.startswith("db")] or [0.0])
+    out = {}
+    for key, r in ref.items():
+        a = np.asarray(res[key], dtype=np.float64)
+        r64 = np.asarray(r, dtype=np.float64)
+        denom = db_scale if key.startswith("db") else float(np.abs(r64).max())
+        diff = float(np.abs(a - r64).max())
+        out[key] = diff / denom if denom > 0 else diff
+    return out

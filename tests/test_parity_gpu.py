@@ -1,0 +1,167 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the reference's golden
+vectors and against the CPU restatement on seeded inputs.
+
+Tolerances (max|ours - ref| / max|ref| per tensor):
+  exact FP32 path   1e-5   (summation order differs from the reference, nothing else)
+  TF32 tensor cores 5e-3
+  BF16 tensor cores 2e-2
+"""
+import numpy as np
+import pytest
+
+import cases
+from boat_b200 import capi
+from gpu_driver import gpu_step
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32, TOL_TF32, TOL_BF16 = 1e-5, 5e-3, 2e-2
+
+
+def assert_close(res, ref, tol, what):
+    flat, fref = cases.flatten_result(res), cases.flatten_result(ref)
+    for key, r in fref.items():
+        assert flat[key].shape == r.shape, (what, key)
+        assert np.isfinite(flat[key]).all(), (what, key, "non-finite values")
+    worst = cases.errors(flat, fref)
+    bad = {k: v for k, v in worst.items() if v > tol}
+    assert not bad, "%s: relative error above %g: %s (all: %s)" % (what, tol, bad, worst)
+
+
+@pytest.mark.parametrize("device", [capi.DEVICE_CPU, capi.DEVICE_CUDA], ids=["host_tensors", "cuda_tensors"])
+@pytest.mark.parametrize("case", cases.GOLDEN_CASES, ids=lambda c: c.name)
+def test_fp32_path_matches_reference_golden(gpu_lib, golden, case, device):
+    inp = case.inputs()
+    res = gpu_step(inp, case.nh, case.causal, device=device, precision=capi.MMA_FP32)
+    ref = {k.split("/", 1)[1]: golden[k] for k in golden.files if k.startswith(case.name + "/") and "digest" not in k}
+    worst = cases.errors(cases.flatten_result(res), ref)
+    bad = {k: v for k, v in worst.items() if v > TOL_FP32}
+    assert not bad, "%s: %s" % (case.name, bad)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 8, 1), (2, 3, 24, 3), (1, 65, 32, 2), (2, 130, 64, 4), (1, 200, 256, 2),
+                                   (1, 257, 128, 1)])
+@pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
+def test_fp32_path_matches_restatement_on_ragged_shapes(gpu_lib, shape, causal):
+    B, S, H, nh = shape
+    case = cases.Case("ragged", B, S, H, nh, causal=causal, self_attn=False, bias_std=0.1)
+    inp = case.inputs()
+    ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], nh, causal)
+    res = gpu_step(inp, nh, causal, device=capi.DEVICE_CUDA, precision=capi.MMA_FP32)
+    assert_close(res, ref, TOL_FP32, str(shape))
+
+
+def test_self_attention_sums_into_one_gradient_through_autodiff(gpu_lib):
+    """boat_var_attention + boat_variable_backward: one variable passed as query, key and
+    value ends with dq + dk + dv in its .grad."""
+    import ctypes as C
+    from boat_b200.host import Attention, Tensor
+    case = cases.Case("autodiff", 2, 16, 32, 4, causal=True, bias_std=0.1)
+    inp = case.inputs()
+    ref = oracle.port_step(inp["q"], inp["q"], inp["q"], inp["w"], inp["b"], inp["dout"], 4, True)
+    lib = gpu_lib
+    layer = Attention(32, 4, causal=True)
+    for i, p in enumerate("qkvo"):
+        layer.param("weight_" + p).set(inp["w"][i])
+        layer.param("bias_" + p).set(inp["b"][i])
+    layer.set_precision(capi.MMA_FP32)
+    x = Tensor.from_numpy(inp["q"])
+    var = C.c_void_p(lib.boat_variable_create(x.h, True))
+    out = C.c_void_p(lib.boat_var_attention(var, var, var, layer.h, None))
+    assert out.value
+    g = Tensor.from_numpy(inp["dout"])
+    lib.boat_variable_backward(out, g.h)
+    grad = Tensor(lib.boat_variable_grad(var), own=False).numpy()
+    want = ref["dq"] + ref["dk"] + ref["dv"]
+    assert cases.rel_err(grad, want) <= TOL_FP32
+    assert cases.rel_err(Tensor(lib.boat_variable_data(out), own=False).numpy(), ref["out"]) <= TOL_FP32
+    lib.boat_variable_free(out)
+    lib.boat_variable_free(var)
+    layer.free()
+
+
+def test_sgd_update_is_bit_exact(gpu_lib):
+    case = cases.GOLDEN_CASES[1]
+    inp = case.inputs()
+    for device in (capi.DEVICE_CPU, capi.DEVICE_CUDA):
+        res = gpu_step(inp, case.nh, case.causal, device=device, precision=capi.MMA_FP32, lr=0.01)
+        for i in range(4):
+            assert np.array_equal(res["w_after"][i], oracle.port_sgd(inp["w"][i], res["dw"][i], 0.01))
+            assert np.array_equal(res["b_after"][i], oracle.port_sgd(inp["b"][i], res["db"][i], 0.01))
+
+
+def test_reference_training_loop_losses(gpu_lib):
+    """The reference's training test (5 steps, lr 0.01) through our library prints the same
+    losses as the reference does: 0.324671 ... 0.324215."""
+    import ctypes
+    from boat_b200.host import Attention, Tensor
+    libc = ctypes.CDLL(None)
+    libc.rand.restype = ctypes.c_int
+    f32 = np.float32
+    draw = lambda: f32(f32(libc.rand()) / f32(2147483647))
+    libc.srand(1)
+    layer = Attention(32, 4, head_size=8)           # draws its weights from rand(), like the reference
+    libc.srand(42)
+    n = 2 * 4 * 32
+    q, k, v = np.empty(n, f32), np.empty(n, f32), np.empty(n, f32)
+    for i in range(n):
+        q[i] = draw() * f32(2) - f32(1)
+        k[i] = draw() * f32(2) - f32(1)
+        v[i] = draw() * f32(2) - f32(1)
+    target = np.array([draw() * f32(2) - f32(1) for _ in range(n)], dtype=f32)
+    tq, tk, tv = (Tensor.from_numpy(a.reshape(2, 4, 32)) for a in (q, k, v))
+    losses = []
+    for _ in range(5):
+        out = layer.forward(tq, tk, tv)
+        diff = out.numpy().ravel() - target
+        losses.append(float(np.mean(diff.astype(np.float64) ** 2)))
+        g = Tensor.from_numpy((f32(2) * diff / f32(n)).reshape(2, 4, 32))
+        layer.backward(g)
+        layer.update(0.01)
+    assert np.allclose(losses, [0.324671, 0.324557, 0.324443, 0.324329, 0.324215], atol=2e-6), losses
+    dwq = layer.param("grad_weight_q").numpy().ravel()
+    assert abs(float(np.abs(dwq[:10]).sum()) - 0.002070) < 2e-6
+    layer.free()
+
+
+def test_error_behaviour_matches_reference(gpu_lib):
+    import ctypes as C
+    from boat_b200.host import Attention, Tensor
+    lib = gpu_lib
+    cfg = capi.AttentionConfig(30, 4, 0, 0.0, False, True, False, 10000.0)
+    assert not lib.boat_attention_create(C.byref(cfg))            # 30 % 4 != 0
+    assert not lib.boat_attention_create(None)
+    layer = Attention(32, 4)
+    x = Tensor.from_numpy(np.zeros((2, 4, 32), np.float32))
+    assert not lib.boat_attention_forward(layer.h, None, x.h, x.h, None)
+    assert not lib.boat_attention_forward(None, x.h, x.h, x.h, None)
+    g = Tensor.from_numpy(np.ones((2, 4, 32), np.float32))
+    gq = C.c_void_p()
+    assert lib.boat_attention_backward(layer.h, g.h, C.byref(gq), None, None) is False   # no forward yet
+    assert lib.boat_attention_get_grad_weight_q(layer.h) is None                       # NULL before backward
+    bad = Tensor.from_numpy(np.zeros((2, 4, 16), np.float32))
+    assert not lib.boat_attention_forward(layer.h, bad.h, bad.h, bad.h, None)           # wrong hidden size
+    out = layer.forward(x)
+    assert lib.boat_attention_backward(layer.h, g.h, None, None, None) is True          # NULL out-params tolerated
+    assert lib.boat_attention_get_grad_weight_q(layer.h) is not None
+    layer.free()
+
+
+def test_scaled_dot_product_attention_entry_point(gpu_lib):
+    import ctypes as C
+    from boat_b200.host import Tensor
+    lib = gpu_lib
+    case = cases.Case("sdpa", 2, 19, 24, 3, self_attn=False)
+    inp = case.inputs()
+    shp = (2, 3, 19, 8)
+    q, k, v = (inp[n].reshape(shp) for n in "qkv")
+    for causal in (False, True):
+        ref = oracle.port_core(q.reshape(6, 19, 8), k.reshape(6, 19, 8), v.reshape(6, 19, 8), None, causal, 0.3)
+        tq, tk, tv = (Tensor.from_numpy(a) for a in (q, k, v))
+        out = Tensor(lib.boat_scaled_dot_product_attention(tq.h, tk.h, tv.h, 0.3, None, causal, 0.0))
+        assert out.shape == shp
+        assert cases.rel_err(out.numpy().reshape(6, 19, 8), ref["o"]) <= TOL_FP32
+    t3 = Tensor.from_numpy(inp["v"])                                       # 3-D: copy of value
+    out = Tensor(lib.boat_scaled_dot_product_attention(t3.h, t3.h, t3.h, 1.0, None, False, 0.0))
+    assert np.array_equal(out.numpy(), inp["v"])
