@@ -1,5 +1,328 @@
-#include "common.cuh"
+// gemm_tc.cu - the projection GEMMs of the attention layer on Blackwell tensor cores.
+//
+//   C[M,N] = op(A) . op(B) (+ bias)      BF16 storage (kind::f16) or FP32 storage (kind::tf32),
+//                                         FP32 accumulation in tensor memory
+//
+// Replaces boat_matmul (reference src/ops/linear.c:116-130) inside linear_projection
+// (src/layers/attention.c:247-308) and linear_projection_backward (attention.c:1186-1293).
+// The three products of a projection differ only in which operand is stored transposed;
+// instead of materialising transposes as the reference does (linear.c:306-334), the shared
+// memory descriptors tell the tensor core which way each operand lies:
+//
+//   Y  = X . W      A = X  [M,K] K-major      B = W  [K,N] N-major
+//   dX = dY . W^T   A = dY [M,K] K-major      B = W  [N,K] K-major
+//   dW = X^T . dY   A = X  [K,M] M-major      B = dY [K,N] N-major
+//
+// Kernel shape: persistent, one 192-thread CTA per SM.  Warp 0 feeds a 4-stage shared-memory
+// ring with TMA (128-byte swizzle, no multicast); one thread of warp 1 issues tcgen05.mma
+// 128 x BN x (32 bytes of K) and commits stages back to the producer; warps 2-5 drain the
+// accumulator from tensor memory (tcgen05.ld), add the bias, convert and store.  The
+// accumulator is double-buffered in tensor memory (2 x BN columns) so that the epilogue of one
+// tile overlaps the main loop of the next.  Weight gradients have few output tiles and a
+// very long K: they are split along K over several CTAs that add into a zeroed output.
+#include "tc_common.cuh"
+
 namespace boatcu {
-bool gemm_tc_supported(int, int, int, int64_t, int64_t, int64_t, const void*, int64_t, const void*, int64_t, int, const void*, int64_t, int) { return false; }
-int gemm_tc(int, int, int, int64_t, int64_t, int64_t, const void*, int64_t, const void*, int64_t, int, void*, int64_t, int, const float*) { return set_error(99, "no tc"); }
+
+using namespace tc;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int STAGES = 4;
+constexpr int kThreads = 192;
+constexpr int kSMs = 148;
+
+template <typename T, int BN>
+struct Cfg {
+    static constexpr int ES = sizeof(T);
+    static constexpr int BK = 128 / ES;             // one 128-byte swizzle row of K (or of M/N)
+    static constexpr int UK = 32 / ES;              // K extent of one tcgen05.mma
+    static constexpr int A_BYTES = BM * 128;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int CHUNK_BYTES = BK * 128;    // one [BK rows x 128 B] box of an MN-major operand
+    static constexpr int SMEM = STAGES * (A_BYTES + B_BYTES) + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;   // two accumulators
+};
+
+struct Params {
+    void* C;
+    const float* bias;
+    int64_t ldc;
+    int M, N, K;
+    int out_type;
+    int split_k;
+    unsigned int* status;
+};
+
+template <typename T, bool A_MN, bool B_MN, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+    using C = Cfg<T, BN>;
+    constexpr bool TF32 = sizeof(T) == 4;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_smem = smem;
+    uint8_t* b_smem = smem + STAGES * C::A_BYTES;
+    uint64_t* bars = (uint64_t*)(smem + STAGES * (C::A_BYTES + C::B_BYTES));
+    uint64_t* full = bars;                 // [STAGES] TMA -> MMA
+    uint64_t* empty = bars + STAGES;       // [STAGES] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * STAGES;       // [2] MMA -> epilogue
+    uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
+    const int k_blocks = (p.K + C::BK - 1) / C::BK;
+    const int work_items = m_tiles * n_tiles * p.split_k;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 128);
+        }
+        fence_barrier_init();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+                const int tile = w / p.split_k, split = w % p.split_k;
+                const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+                const int kb0 = (int)((int64_t)split * k_blocks / p.split_k);
+                const int kb1 = (int)((int64_t)(split + 1) * k_blocks / p.split_k);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, p.status, kTimeoutProducer)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full[s], C::A_BYTES + C::B_BYTES);
+                    const int k0 = kb * C::BK;
+                    uint8_t* a_dst = a_smem + s * C::A_BYTES;
+                    uint8_t* b_dst = b_smem + s * C::B_BYTES;
+                    if (A_MN) {
+                        for (int c = 0; c < BM / C::BK; ++c)
+                            tma_load_2d(a_dst + c * C::CHUNK_BYTES, &map_a, &full[s], m0 + c * C::BK, k0);
+                    } else {
+                        tma_load_2d(a_dst, &map_a, &full[s], k0, m0);
+                    }
+                    if (B_MN) {
+                        for (int c = 0; c < BN / C::BK; ++c)
+                            tma_load_2d(b_dst + c * C::CHUNK_BYTES, &map_b, &full[s], n0 + c * C::BK, k0);
+                    } else {
+                        tma_load_2d(b_dst, &map_b, &full[s], k0, n0);
+                    }
+                }
+            }
+            if (!ok) {
+                // give loads already in flight time to land before the CTA's memory goes away
+                for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(TF32 ? kTF32 : kBF16, A_MN, B_MN, BM, BN);
+            uint32_t it = 0, acc_it = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x, ++acc_it) {
+                const int split = w % p.split_k;
+                const int kb0 = (int)((int64_t)split * k_blocks / p.split_k);
+                const int kb1 = (int)((int64_t)(split + 1) * k_blocks / p.split_k);
+                const int buf = acc_it & 1;
+                if (!mbar_wait(&acc_empty[buf], ((acc_it >> 1) & 1) ^ 1, p.status, kTimeoutMma)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full[s], (it / STAGES) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(a_smem + s * C::A_BYTES);
+                    const uint32_t b_addr = smem_u32(b_smem + s * C::B_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < C::BK / C::UK; ++kk) {
+                        const uint64_t a_desc = A_MN ? smem_desc_mn(a_addr + kk * C::UK * 128, C::CHUNK_BYTES, TF32)
+                                                     : smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+                        const uint64_t b_desc = B_MN ? smem_desc_mn(b_addr + kk * C::UK * 128, C::CHUNK_BYTES, TF32)
+                                                     : smem_desc_sw128(b_addr + kk * 32, 16, 1024);
+                        mma_ss<TF32>(d_tmem, a_desc, b_desc, idesc, kb > kb0 || kk > 0);
+                    }
+                    mma_commit(&empty[s]);            // stage reusable once these MMAs have read it
+                }
+                if (ok) mma_commit(&acc_full[buf]);   // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 ----------------
+        const int lane_group = warp & 3;              // TMEM lanes this warp may touch
+        uint32_t acc_it = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x, ++acc_it) {
+            const int tile = w / p.split_k, split = w % p.split_k;
+            const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+            const int buf = acc_it & 1;
+            if (!mbar_wait(&acc_full[buf], (acc_it >> 1) & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
+            tc_fence_after_sync();
+            const int row = m0 + lane_group * 32 + lane;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * BN;
+            const bool add_bias = p.bias != nullptr && split == 0;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(t_addr + c * 32, r);
+                tmem_wait_ld();
+                const int col0 = n0 + c * 32;
+                if (row < p.M && col0 < p.N) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (add_bias) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+                    }
+                    if (p.split_k > 1) {
+                        float* dst = (float*)p.C + (int64_t)row * p.ldc + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.N) atomicAdd(dst + j, v[j]);
+                    } else if (p.out_type == BOAT_CUDA_F32) {
+                        float* dst = (float*)p.C + (int64_t)row * p.ldc + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            if (col0 + j < p.N)       // N is a multiple of 4 on this path
+                                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)p.C + (int64_t)row * p.ldc + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (col0 + j < p.N) {     // N is a multiple of 8 on this path
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                uint4 o;
+                                o.x = *reinterpret_cast<uint32_t*>(&h0);
+                                o.y = *reinterpret_cast<uint32_t*>(&h1);
+                                o.z = *reinterpret_cast<uint32_t*>(&h2);
+                                o.w = *reinterpret_cast<uint32_t*>(&h3);
+                                *reinterpret_cast<uint4*>(dst + j) = o;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
 }
+
+template <typename T, bool A_MN, bool B_MN, int BN>
+int launch(int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B, int64_t ldb, void* Cp,
+           int64_t ldc, int out_type, const float* bias) {
+    using C = Cfg<T, BN>;
+    CUtensorMap map_a, map_b;
+    // A: K-major -> matrix [M rows, K cols], box [BM, BK].  M-major -> stored [K rows, M cols], box [BK, BK].
+    if (int rc = A_MN ? make_tensor_map_2d(&map_a, A, C::ES, (uint64_t)K, (uint64_t)M, (uint64_t)lda, C::BK, C::BK, C::ES == 4)
+                      : make_tensor_map_2d(&map_a, A, C::ES, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, C::BK))
+        return rc;
+    if (int rc = B_MN ? make_tensor_map_2d(&map_b, B, C::ES, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, C::BK, C::BK, C::ES == 4)
+                      : make_tensor_map_2d(&map_b, B, C::ES, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, C::BK))
+        return rc;
+    const int m_tiles = (int)ceil_div(M, BM), n_tiles = (int)ceil_div(N, BN);
+    const int k_blocks = (int)ceil_div(K, C::BK);
+    const int tiles = m_tiles * n_tiles;
+    int split_k = 1;
+    if (out_type == BOAT_CUDA_F32 && tiles * 2 <= kSMs) {
+        // few output tiles (weight gradients): spread K over the idle SMs, at least 8 K-blocks each
+        split_k = kSMs / tiles;
+        if (split_k > k_blocks / 8) split_k = k_blocks / 8;
+        if (split_k < 1) split_k = 1;
+    }
+    if (split_k > 1) {
+        if (ldc == N) {
+            BOATCU_CHECK(cudaMemsetAsync(Cp, 0, (size_t)M * N * sizeof(float), stream()));
+        } else {
+            BOATCU_CHECK(cudaMemset2DAsync(Cp, (size_t)ldc * sizeof(float), 0, (size_t)N * sizeof(float), (size_t)M, stream()));
+        }
+    }
+    Params p;
+    p.C = Cp;
+    p.bias = bias;
+    p.ldc = ldc;
+    p.M = (int)M;
+    p.N = (int)N;
+    p.K = (int)K;
+    p.out_type = out_type;
+    p.split_k = split_k;
+    p.status = kernel_status_ptr();
+    auto kern = gemm_tc_kernel<T, A_MN, B_MN, BN>;
+    static bool configured = false;
+    if (!configured) {
+        BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured = true;
+    }
+    int work = tiles * split_k;
+    int grid = work < kSMs ? work : kSMs;
+    kern<<<grid, kThreads, C::SMEM, stream()>>>(map_a, map_b, p);
+    BOATCU_LAUNCH_OK("gemm_tc");
+    return 0;
+}
+
+template <typename T>
+int dispatch_layout(int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
+                    int64_t ldb, void* C, int64_t ldc, int out_type, const float* bias) {
+    // trans_a: A stored [K,M] (M-major).  trans_b == 0: B stored [K,N] (N-major).
+    if (!ta && !tb) return launch<T, false, true, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    if (!ta && tb) return launch<T, false, false, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    if (ta && !tb) return launch<T, true, true, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    return launch<T, true, false, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+}
+
+}  // namespace
+
+bool gemm_tc_supported(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                       const void* B, int64_t ldb, int in_type, const void* C, int64_t ldc, int out_type) {
+    (void)ta;
+    (void)tb;
+    if (mma != BOAT_MMA_BF16 && mma != BOAT_MMA_TF32) return false;
+    const int es = mma == BOAT_MMA_BF16 ? 2 : 4;
+    if ((mma == BOAT_MMA_BF16) != (in_type == BOAT_CUDA_BF16)) return false;
+    const int oes = out_type == BOAT_CUDA_BF16 ? 2 : 4;
+    if (M < 128 || N < 64 || K < 128 / es) return false;               // small problems: CUDA cores
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return false;
+    if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return false;
+    if ((lda * es) % 16 || (ldb * es) % 16 || (ldc * oes) % 16) return false;
+    if (N % (16 / oes)) return false;
+    return true;
+}
+
+int gemm_tc(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
+            int64_t ldb, int in_type, void* C, int64_t ldc, int out_type, const float* bias) {
+    (void)in_type;
+    if (int rc = ensure_init()) return rc;
+    if (mma == BOAT_MMA_BF16)
+        return dispatch_layout<__nv_bfloat16>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    return dispatch_layout<float>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+}
+
+}  // namespace boatcu

@@ -2,7 +2,7 @@
 // host<->HBM copies.  Stands in for the device stubs of the reference's memory layer
 // (src/core/memory.c:174-186 allocate_device/free_device and :230-247 copy/set, which were
 // malloc/memcpy/memset regardless of the device argument).
-#include "common.cuh"
+#include "tc_common.cuh"
 #include <stdarg.h>
 #include <stdlib.h>
 #include <string.h>
@@ -15,11 +15,13 @@ namespace boatcu {
 static thread_local char g_err[512] = "";
 static std::mutex g_mu;
 static bool g_ready = false;
-static int g_device = -1;
+static int g_device = -1;   // device the library is bound to
 static cudaStream_t g_stream = 0;
 static std::atomic<uint64_t> g_launches{0};
 static std::unordered_map<void*, size_t>* g_live = nullptr;
 static size_t g_live_bytes = 0;
+static unsigned int* g_status_host = nullptr;   // kernel status word, host view
+static unsigned int* g_status_dev = nullptr;    // the same word as kernels see it
 
 int set_error(int status, const char* fmt, ...) {
     va_list ap;
@@ -66,8 +68,61 @@ static int init_locked(int device) {
     uint64_t keep = UINT64_MAX;
     BOATCU_CHECK(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
     if (!g_live) g_live = new std::unordered_map<void*, size_t>();
+    BOATCU_CHECK(cudaHostAlloc((void**)&g_status_host, sizeof(unsigned int), cudaHostAllocMapped));
+    *g_status_host = 0;
+    BOATCU_CHECK(cudaHostGetDevicePointer((void**)&g_status_dev, g_status_host, 0));
     g_device = dev;
     g_ready = true;
+    return 0;
+}
+
+// ---- kernel status word ---------------------------------------------------------------------
+// One 32-bit word in mapped pinned host memory.  Kernels write a code there when a bounded
+// wait gives up; the host reads it after a synchronisation without any copy.
+unsigned int* kernel_status_ptr() { return g_status_dev; }
+
+unsigned int take_kernel_status() {
+    if (!g_status_host) return 0;
+    unsigned int v = *(volatile unsigned int*)g_status_host;
+    if (v) *(volatile unsigned int*)g_status_host = 0;
+    return v;
+}
+
+static int report_kernel_status(const char* where) {
+    unsigned int v = take_kernel_status();
+    if (v == 0) return 0;
+    return set_error(30, "%s: a tensor-core kernel gave up waiting (role code %u); its results are invalid", where, v);
+}
+
+// ---- tensor maps -------------------------------------------------------------------------------
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_tiled_fn g_encode = nullptr;
+
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int esize, uint64_t rows, uint64_t cols, uint64_t ld,
+                       uint32_t box_rows, uint32_t box_cols, bool atom32) {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        BOATCU_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (!fn || q != cudaDriverEntryPointSuccess) return set_error(31, "cuTensorMapEncodeTiled is not available");
+        g_encode = (encode_tiled_fn)fn;
+    }
+    if (((uintptr_t)base & 15) != 0 || ((ld * (uint64_t)esize) & 15) != 0)
+        return set_error(31, "tensor map: base or row pitch not 16-byte aligned");
+    if (box_cols * (uint32_t)esize != 128 || box_rows > 256 || box_rows == 0)
+        return set_error(31, "tensor map: box must be 128 bytes wide and at most 256 rows");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * (uint64_t)esize};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapDataType dt = esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(31, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return 0;
 }
 
@@ -109,7 +164,7 @@ int boat_cuda_set_stream(void* s) {
 int boat_cuda_sync(void) {
     if (int rc = ensure_init()) return rc;
     BOATCU_CHECK(cudaStreamSynchronize(g_stream));
-    return 0;
+    return report_kernel_status("boat_cuda_sync");
 }
 
 int boat_cuda_malloc(void** ptr, size_t bytes) {
@@ -154,7 +209,7 @@ int boat_cuda_memcpy_d2h(void* dst, const void* src, size_t bytes) {
     if (int rc = ensure_init()) return rc;
     BOATCU_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g_stream));
     BOATCU_CHECK(cudaStreamSynchronize(g_stream));
-    return 0;
+    return report_kernel_status("boat_cuda_memcpy_d2h");
 }
 
 int boat_cuda_memcpy_d2d(void* dst, const void* src, size_t bytes) {

@@ -1,0 +1,111 @@
+"""GPU tests of the kernel ABI (include/boat_cuda.h) one entry point at a time, against
+numpy in float64 on the same (storage-rounded) inputs."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from boat_b200 import capi, rng
+from boat_b200.host import DeviceBuffer, check
+
+pytestmark = pytest.mark.gpu
+
+TOL = {capi.MMA_FP32: 1e-5, capi.MMA_TF32: 5e-3, capi.MMA_BF16: 2e-2}
+
+
+def rel(a, ref):
+    return float(np.abs(a.astype(np.float64) - ref).max() / np.abs(ref).max())
+
+
+def run_gemm(lib, mma, ta, tb, M, N, K, out_bf16=False, bias=True, seed=1):
+    bf = mma == capi.MMA_BF16
+    a_shape = (K, M) if ta else (M, K)
+    b_shape = (N, K) if tb else (K, N)
+    A = rng.normal(seed, 0, a_shape)
+    B = rng.normal(seed, 1, b_shape, std=1.0 / np.sqrt(K))
+    bvec = rng.normal(seed, 2, (N,)) if bias else None
+    if bf:
+        A, B = rng.bf16_round(A), rng.bf16_round(B)
+    dA, dB = DeviceBuffer.from_numpy(A, bf16=bf), DeviceBuffer.from_numpy(B, bf16=bf)
+    dbias = DeviceBuffer.from_numpy(bvec) if bias else None
+    dC = DeviceBuffer(M * N * (2 if out_bf16 else 4))
+    check(lib.boat_cuda_gemm(mma, ta, tb, M, N, K, dA.p, a_shape[1], dB.p, b_shape[1],
+                             capi.CUDA_BF16 if bf else capi.CUDA_F32, dC.p, N,
+                             capi.CUDA_BF16 if out_bf16 else capi.CUDA_F32, dbias.p if bias else None), "gemm")
+    check(lib.boat_cuda_sync(), "sync")
+    got = dC.numpy((M, N), bf16=out_bf16)
+    opA = A.T if ta else A
+    opB = B.T if tb else B
+    ref = opA.astype(np.float64) @ opB.astype(np.float64)
+    if bias:
+        ref = ref + bvec.astype(np.float64)
+    return got, ref
+
+
+LAYOUTS = [(0, 0), (0, 1), (1, 0)]
+
+
+@pytest.mark.parametrize("mma", [capi.MMA_FP32, capi.MMA_BF16, capi.MMA_TF32], ids=["fp32", "bf16", "tf32"])
+@pytest.mark.parametrize("layout", LAYOUTS, ids=["nn", "nt", "tn"])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 512), (384, 256, 192), (1024, 1024, 1024),
+                                   (200, 328, 136), (4096, 512, 512)])
+def test_gemm_matches_float64(gpu_lib, mma, layout, shape):
+    M, N, K = shape
+    got, ref = run_gemm(gpu_lib, mma, layout[0], layout[1], M, N, K)
+    assert np.isfinite(got).all()
+    assert rel(got, ref) <= TOL[mma]
+
+
+@pytest.mark.parametrize("layout", LAYOUTS, ids=["nn", "nt", "tn"])
+def test_gemm_bf16_output_and_no_bias(gpu_lib, layout):
+    got, ref = run_gemm(gpu_lib, capi.MMA_BF16, layout[0], layout[1], 512, 256, 256, out_bf16=True, bias=False)
+    assert rel(got, ref) <= TOL[capi.MMA_BF16]
+
+
+def test_weight_gradient_shape_uses_split_k(gpu_lib):
+    """dW = X^T dY: 512 x 512 outputs, K = 16384 rows - few tiles, long K."""
+    for mma in (capi.MMA_BF16, capi.MMA_TF32):
+        got, ref = run_gemm(gpu_lib, mma, 1, 0, 512, 512, 16384, bias=False)
+        assert rel(got, ref) <= TOL[mma]
+
+
+@pytest.mark.parametrize("mma", [capi.MMA_FP32, capi.MMA_BF16, capi.MMA_TF32], ids=["fp32", "bf16", "tf32"])
+def test_gemm_tiny_and_ragged_shapes(gpu_lib, mma):
+    for (M, N, K) in [(1, 1, 1), (3, 5, 7), (8, 32, 32), (127, 65, 33)]:
+        got, ref = run_gemm(gpu_lib, mma, 0, 0, M, N, K)
+        assert rel(got, ref) <= TOL[mma], (M, N, K)
+
+
+def test_elementwise_tail(gpu_lib):
+    lib = gpu_lib
+    for n in (1, 7, 1024, 100003):
+        x, y = rng.normal(3, 0, (n,)), rng.normal(3, 1, (n,))
+        dx, dy = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(y)
+        check(lib.boat_cuda_axpy(dy.p, dx.p, C.c_float(-0.01), n))
+        assert np.array_equal(dy.numpy((n,)), y + (np.float32(-0.01) * x))
+        check(lib.boat_cuda_scale(dy.p, dx.p, C.c_float(0.5), n))
+        assert np.array_equal(dy.numpy((n,)), x * np.float32(0.5))
+        check(lib.boat_cuda_mul(dy.p, dx.p, dx.p, n))
+        assert np.array_equal(dy.numpy((n,)), x * x)
+        db = DeviceBuffer(n * 2)
+        check(lib.boat_cuda_cast(db.p, capi.CUDA_BF16, dx.p, capi.CUDA_F32, n))
+        assert np.array_equal(db.numpy((n,), bf16=True), rng.bf16_round(x))
+        check(lib.boat_cuda_cast(dy.p, capi.CUDA_F32, db.p, capi.CUDA_BF16, n))
+        assert np.array_equal(dy.numpy((n,)), rng.bf16_round(x))
+    for rows, cols in ((1, 1), (5, 3), (1000, 64), (4096, 520), (33, 1000)):
+        x = rng.normal(4, 0, (rows, cols))
+        for bf in (False, True):
+            xs = rng.bf16_round(x) if bf else x
+            dx = DeviceBuffer.from_numpy(xs, bf16=bf)
+            out = DeviceBuffer(cols * 4)
+            check(lib.boat_cuda_colsum(dx.p, capi.CUDA_BF16 if bf else capi.CUDA_F32, rows, cols, out.p))
+            ref = xs.astype(np.float64).sum(0)
+            assert np.abs(out.numpy((cols,)) - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
+        b = rng.normal(4, 1, (cols,))
+        dx, db_, dy = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(b), DeviceBuffer(rows * cols * 4)
+        check(lib.boat_cuda_add_bias(dy.p, dx.p, db_.p, rows, cols))
+        assert np.array_equal(dy.numpy((rows, cols)), x + b)
+    x = rng.normal(5, 0, (3, 45, 70))
+    dx, dy = DeviceBuffer.from_numpy(x), DeviceBuffer(x.size * 4)
+    check(lib.boat_cuda_transpose(dy.p, dx.p, 3, 45, 70))
+    assert np.array_equal(dy.numpy((3, 70, 45)), x.transpose(0, 2, 1))
