@@ -1,7 +1,72 @@
-#include "common.cuh"
+// flash_tc.cu - host side of the tcgen05 attention-core kernels: shape support, tensor maps,
+// launches.  The kernels themselves are in flash_fwd_tc.cuh and flash_bwd_tc.cuh.
+#include "flash_fwd_tc.cuh"
+
 namespace boatcu {
-bool attn_tc_supported(int, int64_t, int64_t, int64_t, int) { return false; }
-int attn_fwd_tc(int, int64_t, int64_t, int64_t, int, float, const void*, const void*, const void*, int, void*, float*) { return set_error(99, "no tc"); }
-size_t attn_bwd_tc_scratch_bytes(int, int64_t, int64_t, int64_t) { return 0; }
-int attn_bwd_tc(int, int64_t, int64_t, int64_t, int, float, const void*, const void*, const void*, const void*, const float*, const float*, int, void*, void*, void*, void*, size_t) { return set_error(99, "no tc"); }
+
+using namespace flash;
+
+namespace {
+
+template <typename T, int HS>
+int launch_fwd(int64_t units, int64_t S, int causal, float scale, const void* Q, const void* K, const void* V,
+               void* O, float* lse) {
+    using C = FwdCfg<T, HS>;
+    CUtensorMap mq, mk, mv;
+    const uint64_t rows = (uint64_t)units * (uint64_t)S;
+    if (int rc = make_tensor_map_2d(&mq, Q, C::ES, rows, HS, HS, kTile, C::BOXC)) return rc;
+    if (int rc = make_tensor_map_2d(&mk, K, C::ES, rows, HS, HS, kTile, C::BOXC)) return rc;
+    // V is read by the tensor core along its contiguous head dimension: FP32 needs the
+    // 32-byte-unit swizzle for that
+    if (int rc = make_tensor_map_2d(&mv, V, C::ES, rows, HS, HS, kTile, C::BOXC, C::TF32)) return rc;
+    FwdParams p;
+    p.O = O;
+    p.lse = lse;
+    p.S = (int)S;
+    p.units = (int)units;
+    p.causal = causal;
+    p.scale = scale;
+    p.status = kernel_status_ptr();
+    auto kern = flash_fwd_kernel<T, HS>;
+    static bool configured = false;
+    if (!configured) {
+        BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured = true;
+    }
+    const int64_t grid = units * (S / kTile);
+    kern<<<(unsigned)grid, kFwdThreads, C::SMEM, stream()>>>(mq, mk, mv, p);
+    BOATCU_LAUNCH_OK("flash_fwd");
+    return 0;
 }
+
+}  // namespace
+
+bool attn_tc_supported(int mma, int64_t units, int64_t S, int64_t hs, int io_type) {
+    if (S < kTile || S % kTile != 0) return false;
+    if (units * (S / kTile) > 0x7fffffffLL || units * S > 0x7fffffffLL) return false;
+    if (mma == BOAT_MMA_BF16) return io_type == BOAT_CUDA_BF16 && (hs == 64 || hs == 128);
+    if (mma == BOAT_MMA_TF32) return io_type == BOAT_CUDA_F32 && hs == 64;
+    return false;
+}
+
+int attn_fwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q, const void* K,
+                const void* V, int io_type, void* O, float* lse) {
+    (void)io_type;
+    if (int rc = ensure_init()) return rc;
+    if (mma == BOAT_MMA_BF16) {
+        if (hs == 64) return launch_fwd<__nv_bfloat16, 64>(units, S, causal, scale, Q, K, V, O, lse);
+        return launch_fwd<__nv_bfloat16, 128>(units, S, causal, scale, Q, K, V, O, lse);
+    }
+    return launch_fwd<float, 64>(units, S, causal, scale, Q, K, V, O, lse);
+}
+
+size_t attn_bwd_tc_scratch_bytes(int, int64_t, int64_t, int64_t) { return 0; }
+
+int attn_bwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q, const void* K,
+                const void* V, const void* dO, const float* lse, const float* delta, int io_type, void* dQ, void* dK,
+                void* dV, void* scratch, size_t scratch_bytes) {
+    (void)mma; (void)scratch; (void)scratch_bytes;
+    return attn_bwd_simt(units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV);
+}
+
+}  // namespace boatcu

@@ -109,3 +109,85 @@ def test_elementwise_tail(gpu_lib):
     dx, dy = DeviceBuffer.from_numpy(x), DeviceBuffer(x.size * 4)
     check(lib.boat_cuda_transpose(dy.p, dx.p, 3, 45, 70))
     assert np.array_equal(dy.numpy((3, 70, 45)), x.transpose(0, 2, 1))
+
+
+# ---- attention core through boat_cuda_attn_fwd / boat_cuda_attn_bwd ----------------------------
+
+def np_core(q, k, v, go, causal, scale):
+    """float64 attention core on [units,S,hs]: O, lse and (with go) dQ,dK,dV."""
+    q, k, v = (a.astype(np.float64) for a in (q, k, v))
+    s = np.einsum("uid,ujd->uij", q, k) * scale
+    if causal:
+        S = q.shape[1]
+        s = np.where(np.triu(np.ones((S, S), bool), 1)[None], -np.inf, s)
+    m = s.max(-1, keepdims=True)
+    e = np.exp(s - m)
+    l = e.sum(-1, keepdims=True)
+    p = e / l
+    res = {"o": p @ v, "lse": (m + np.log(l))[..., 0]}
+    if go is not None:
+        go = go.astype(np.float64)
+        dv = np.einsum("uij,uid->ujd", p, go)
+        dp = np.einsum("uid,ujd->uij", go, v)
+        ds = p * (dp - (dp * p).sum(-1, keepdims=True)) * scale
+        res.update(dq=ds @ k, dk=np.einsum("uij,uid->ujd", ds, q), dv=dv)
+    return res
+
+
+def run_core(lib, mma, units, S, hs, causal, backward=True, seed=7):
+    bf = mma == capi.MMA_BF16
+    io = capi.CUDA_BF16 if bf else capi.CUDA_F32
+    f = rng.bf16_round if bf else (lambda a: a)
+    shape = (units, S, hs)
+    q, k, v, go = (f(rng.normal(seed, i, shape)) for i in range(4))
+    scale = 1.0 / np.sqrt(hs)
+    dq_, dk_, dv_, dgo = (DeviceBuffer.from_numpy(a, bf16=bf) for a in (q, k, v, go))
+    es = 2 if bf else 4
+    n = units * S * hs
+    do_, dlse = DeviceBuffer(n * es), DeviceBuffer(units * S * 4)
+    check(lib.boat_cuda_attn_fwd(mma, units, S, hs, int(causal), C.c_float(scale), dq_.p, dk_.p, dv_.p, io, do_.p, dlse.p),
+          "attn_fwd")
+    check(lib.boat_cuda_sync(), "sync")
+    got = {"o": do_.numpy(shape, bf16=bf), "lse": dlse.numpy((units, S))}
+    if backward:
+        gq, gk, gv = DeviceBuffer(n * es), DeviceBuffer(n * es), DeviceBuffer(n * es)
+        nbytes = lib.boat_cuda_attn_bwd_scratch_bytes(mma, units, S, hs)
+        scratch = DeviceBuffer(max(nbytes, 256))
+        check(lib.boat_cuda_attn_bwd(mma, units, S, hs, int(causal), C.c_float(scale), dq_.p, dk_.p, dv_.p, do_.p, dgo.p,
+                                     dlse.p, io, gq.p, gk.p, gv.p, scratch.p, scratch.nbytes), "attn_bwd")
+        check(lib.boat_cuda_sync(), "sync")
+        got.update(dq=gq.numpy(shape, bf16=bf), dk=gk.numpy(shape, bf16=bf), dv=gv.numpy(shape, bf16=bf))
+    ref = np_core(q, k, v, go if backward else None, causal, scale)
+    return got, ref
+
+
+@pytest.mark.parametrize("mma,hs", [(capi.MMA_FP32, 16), (capi.MMA_FP32, 64), (capi.MMA_BF16, 64), (capi.MMA_BF16, 128),
+                                    (capi.MMA_TF32, 64)], ids=["fp32_hs16", "fp32_hs64", "bf16_hs64", "bf16_hs128", "tf32_hs64"])
+@pytest.mark.parametrize("S", [128, 384, 1024])
+@pytest.mark.parametrize("causal", [False, True], ids=["full", "causal"])
+def test_attention_core_matches_float64(gpu_lib, mma, hs, S, causal):
+    got, ref = run_core(gpu_lib, mma, 3, S, hs, causal)
+    tol = TOL[mma]
+    for key in ("o", "dq", "dk", "dv"):
+        assert np.isfinite(got[key]).all(), key
+        assert rel(got[key], ref[key]) <= tol, (key, rel(got[key], ref[key]))
+    assert np.abs(got["lse"] - ref["lse"]).max() <= (1e-4 if mma == capi.MMA_FP32 else 2e-2)
+
+
+def test_attention_core_large_scores_do_not_overflow(gpu_lib):
+    """Rows whose running max keeps growing exercise the rescale of the accumulator."""
+    lib = gpu_lib
+    units, S, hs = 2, 512, 64
+    q = rng.bf16_round(rng.normal(11, 0, (units, S, hs)) * 6.0)
+    k = rng.bf16_round(rng.normal(11, 1, (units, S, hs)) * np.linspace(0.2, 6.0, S)[None, :, None])
+    v = rng.bf16_round(rng.normal(11, 2, (units, S, hs)))
+    scale = 1.0 / np.sqrt(hs)
+    bufs = [DeviceBuffer.from_numpy(a, bf16=True) for a in (q, k, v)]
+    do_, dlse = DeviceBuffer(q.size * 2), DeviceBuffer(units * S * 4)
+    check(lib.boat_cuda_attn_fwd(capi.MMA_BF16, units, S, hs, 0, C.c_float(scale), bufs[0].p, bufs[1].p, bufs[2].p,
+                                 capi.CUDA_BF16, do_.p, dlse.p))
+    check(lib.boat_cuda_sync())
+    ref = np_core(q, k, v, None, False, scale)
+    o = do_.numpy((units, S, hs), bf16=True)
+    assert np.isfinite(o).all()
+    assert rel(o, ref["o"]) <= TOL[capi.MMA_BF16]
