@@ -1,0 +1,427 @@
+#!/usr/bin/env python
+"""Benchmark of the attention training step (forward + backward) through Boat's C API.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl ours|reference]
+
+One step = boat_attention_forward + boat_attention_backward on one batch of synthetic input
+(self-attention: query = key = value), on every rank, plus the all-reduce of the parameter
+gradients when N > 1 (data parallel over batch x heads units, weak scaling: every rank holds
+the full per-GPU workload).  Prints ONE JSON line on rank 0.
+
+  value   tokens/s over all ranks, inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e     the same step called with HOST tensors: uploads and downloads inside the timed region
+  roofline  the dominant kernel's algorithmic FLOP/s against the measured BF16 (or TF32) peak
+  cpu_baseline  the reference's own CPU code on a bounded sample, extrapolated by FLOP rate
+
+--impl reference times the reference's CPU implementation (oracle/_ref, else the C
+restatement) on all host cores with the same metric and config.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B (per GPU), S, d_model, heads, causal, arithmetic
+    "c2": dict(B=8, S=512, d=512, nh=8, causal=False, mma="tf32"),
+    "c3": dict(B=16, S=2048, d=1024, nh=16, causal=True, mma="bf16"),
+    "c4": dict(B=4, S=8192, d=2048, nh=16, causal=True, mma="bf16"),
+    "target": dict(B=8, S=4096, d=2048, nh=16, causal=True, mma="bf16"),
+}
+DEFAULT_WORKLOAD = "c4"
+SEED = 42
+
+
+def algorithmic_flops(B, S, d, causal):
+    """24*T*d^2 for the four projections (forward + both gradients) + 12*c*B*S^2*d for the
+    attention core (c = 1/2 when causal); recomputation inside the backward is not counted."""
+    T = B * S
+    return 24.0 * T * d * d + 12.0 * (0.5 if causal else 1.0) * B * S * S * d
+
+
+def reference_flops(B, S, d):
+    """What the reference's CPU code executes: it computes the full S x S product even when
+    the mask is causal, so c = 1."""
+    return algorithmic_flops(B, S, d, False)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            pk = json.load(f)
+        return dict(hbm=pk.get("hbm_gbs", 6650.0), bf16=pk.get("bf16_tflops", 1590.0),
+                    bf16_sustained=pk.get("bf16_tflops_sustained", 1400.0), source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+# ---- clocks ----------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        self.lines = []
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- CPU reference timing ------------------------------------------------------------------------------
+
+def cpu_sample_shape(cfg, seconds):
+    """A problem with the workload's d_model and head count, one batch, short enough to take
+    about `seconds` at the reference's ~1 GFLOP/s per core."""
+    d, nh = cfg["d"], cfg["nh"]
+    budget = seconds * 0.9e9
+    S = int(budget / (24.0 * d * d))
+    S = max(nh, min(cfg["S"], S))
+    S = max(nh, (S // nh) * nh)
+    return 1, S
+
+
+def cpu_reference_seconds(args):
+    """Runs forward + backward once on the sample (in this process); returns seconds."""
+    B, S, d, nh, causal, use_ref = args
+    from boat_b200 import rng
+    from oracle import oracle
+    x = rng.normal(SEED, rng.X, (B, S, d))
+    w = [rng.normal(SEED, rng.WQ + i, (d, d), 1.0 / np.sqrt(d)) for i in range(4)]
+    b = [np.zeros(d, np.float32) for _ in range(4)]
+    g = rng.normal(SEED, rng.DOUT, (B, S, d))
+    if use_ref:
+        layer = oracle.RefLayer(d, nh, causal, w, b)
+        t0 = time.perf_counter()
+        layer.step(x, x, x, g)
+        dt = time.perf_counter() - t0
+        layer.free()
+    else:
+        oracle.port().oracle_set_threads(1)
+        t0 = time.perf_counter()
+        oracle.port_step(x, x, x, w, b, g, nh, causal)
+        dt = time.perf_counter() - t0
+    return dt
+
+
+def cpu_baseline(cfg, seconds, procs):
+    """tokens/s of the reference's CPU path for the workload `cfg`, measured on a bounded
+    sample by `procs` independent processes and extrapolated by executed FLOPs."""
+    from oracle import oracle
+    use_ref = oracle.have_ref()
+    if not use_ref:
+        oracle.port()          # builds the restatement if needed
+    Bs, Ss = cpu_sample_shape(cfg, seconds)
+    job = (Bs, Ss, cfg["d"], cfg["nh"], cfg["causal"], use_ref)
+    if procs == 1:
+        times = [cpu_reference_seconds(job)]
+    else:
+        import multiprocessing as mp
+        with mp.get_context("spawn").Pool(procs) as pool:
+            times = pool.map(cpu_reference_seconds, [job] * procs)
+    dt = max(times)
+    rate = procs * reference_flops(Bs, Ss, cfg["d"]) / dt                 # FLOP/s of the box
+    full = reference_flops(cfg["B"], cfg["S"], cfg["d"])
+    tokens_per_s = cfg["B"] * cfg["S"] / (full / rate)
+    return dict(value=tokens_per_s, unit="tokens/s", cores=procs, kind="reference" if use_ref else "port",
+                sample=("forward+backward of B=%d S=%d d=%d heads=%d on %d process(es) took %.2f s "
+                        "(%.2f GFLOP/s total); scaled to the workload by executed FLOPs "
+                        "(the reference computes the full S x S product)" %
+                        (Bs, Ss, cfg["d"], cfg["nh"], procs, dt, rate / 1e9)),
+                seconds=dt)
+
+
+def run_reference_arm(args, cfg, rank, world):
+    if rank != 0:
+        return
+    procs = os.cpu_count() or 1
+    per_step = max(3.0, min(15.0, 150.0 / max(1, args.steps + args.warmup)))
+    vals = []
+    for i in range(args.warmup + args.steps):
+        r = cpu_baseline(cfg, per_step, procs)
+        if i >= args.warmup:
+            vals.append(r)
+    value = float(np.mean([v["value"] for v in vals]))
+    secs = float(np.mean([v["seconds"] for v in vals]))
+    base = dict(vals[-1])
+    base["value"] = value
+    base.pop("seconds", None)
+    line = dict(impl="reference", metric="attention_fwd_bwd_tokens_per_s", value=value, unit="tokens/s", n_gpus=world,
+                steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * cfg["B"] * cfg["S"] / value,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                config=workload_config(args.workload, cfg, world), cpu_baseline=base,
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                sample_seconds_per_step=secs)
+    print(json.dumps(line))
+
+
+def workload_config(name, cfg, world):
+    return dict(workload="%s: attention fwd+bwd, batch=%d per GPU, seq=%d, d_model=%d, heads=%d (head_dim %d), %s, %s" %
+                (name, cfg["B"], cfg["S"], cfg["d"], cfg["nh"], cfg["d"] // cfg["nh"],
+                 "causal" if cfg["causal"] else "non-causal",
+                 "BF16 storage, FP32 accumulate" if cfg["mma"] == "bf16" else "FP32 storage, TF32 MMA"),
+                batch_per_gpu=cfg["B"], global_batch=cfg["B"] * world, seq_len=cfg["S"], d_model=cfg["d"],
+                heads=cfg["nh"], causal=cfg["causal"], parallelism="dp%d over batch x heads units" % world,
+                l2="inputs larger than L2: activations of one step exceed 126 MB" if
+                cfg["B"] * cfg["S"] * cfg["d"] * 2 > 126e6 else "L2 flushed between steps by a 256 MB fill")
+
+
+# ---- our arm -------------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    cfg = dict(WORKLOADS[args.workload])
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, cfg, rank, world)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import boat_b200
+    from boat_b200 import capi, rng
+    from boat_b200.host import Attention, Tensor, check
+
+    lib = boat_b200.load()
+    if lib.boat_cuda_device_count() < 1:
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    check(lib.boat_cuda_init(local_rank), "boat_cuda_init")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        idbuf = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            raw = (C.c_ubyte * 128)()
+            check(lib.boat_cuda_comm_unique_id(raw), "comm_unique_id")
+            idbuf.copy_(torch.tensor(list(raw), dtype=torch.uint8))
+        dist.broadcast(idbuf, 0)
+        raw = (C.c_ubyte * 128)(*idbuf.cpu().tolist())
+        check(lib.boat_cuda_comm_init(rank, world, raw), "comm_init")
+
+    B, S, d, nh, causal = cfg["B"], cfg["S"], cfg["d"], cfg["nh"], cfg["causal"]
+    bf16 = cfg["mma"] == "bf16"
+    mma = capi.MMA_BF16 if bf16 else capi.MMA_TF32
+    rnd = rng.bf16_round if bf16 else (lambda a: a)
+    T = B * S
+
+    # ---- synthetic inputs: X ~ N(0,1) (per-rank slice of the global batch), W ~ N(0, 1/sqrt(d)), dO ~ N(0,1)
+    x_host = rnd(rng.normal(SEED, rng.X, (B, S, d), offset=rank * T * d))
+    g_host = rnd(rng.normal(SEED, rng.DOUT, (B, S, d), offset=rank * T * d))
+    w_host = [rnd(rng.normal(SEED, rng.WQ + i, (d, d), 1.0 / np.sqrt(d))) for i in range(4)]
+
+    layer = Attention(d, nh, causal=causal, use_bias=True)
+    for i, p in enumerate("qkvo"):
+        layer.param("weight_" + p).set(w_host[i])
+    layer.to_device(capi.DEVICE_CUDA)
+    layer.set_precision(mma)
+    x = Tensor.from_numpy(x_host, capi.DEVICE_CUDA, bf16=bf16)
+    g = Tensor.from_numpy(g_host, capi.DEVICE_CUDA, bf16=bf16)
+    flush = None
+    if T * d * 2 <= 126e6:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def step():
+        out = layer.forward(x, x, x)
+        gq, gk, gv = layer.backward(g)
+        if world > 1:
+            layer.allreduce_grads()
+        for t in (out, gq, gk, gv):
+            t.free()
+
+    def sync_all():
+        check(lib.boat_cuda_sync(), "sync")
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync_all()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = lib.boat_cuda_launch_count()
+    check(lib.boat_cuda_profile_enable(1), "profile_enable")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    elapsed_ms = 0.0
+    if flush is None:
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        sync_all()
+        elapsed_ms = start.elapsed_time(stop)
+    else:
+        for _ in range(args.steps):           # small workload: flush L2 outside the timed intervals
+            flush.fill_(1)
+            start.record()
+            step()
+            stop.record()
+            torch.cuda.synchronize()
+            elapsed_ms += start.elapsed_time(stop)
+        sync_all()
+    report = C.create_string_buffer(8192)
+    check(lib.boat_cuda_profile_report(report, 8192), "profile_report")
+    check(lib.boat_cuda_profile_enable(0), "profile_enable")
+    launches = lib.boat_cuda_launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+
+    t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    tokens_per_s = world * T / (ms_per_step * 1e-3)
+    flops = algorithmic_flops(B, S, d, causal)
+    tflops_per_gpu = flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel family ----
+    peaks = load_peaks()
+    kern = {}
+    for line in report.value.decode().splitlines():
+        name, n, ms = line.split()
+        kern[name] = (int(n), float(ms))
+    core_c = 0.5 if causal else 1.0
+    kflops = {   # algorithmic FLOPs per launch scope
+        "gemm_tc_nn": 2.0 * T * d * d, "gemm_tc_nt": 2.0 * T * d * d, "gemm_tc_tn": 2.0 * T * d * d,
+        "gemm_simt": 2.0 * T * d * d,
+        "flash_fwd": 4.0 * core_c * B * S * S * d, "attn_fwd_simt": 4.0 * core_c * B * S * S * d,
+        "flash_bwd": 8.0 * core_c * B * S * S * d, "attn_bwd_simt": 8.0 * core_c * B * S * S * d,
+    }
+    roofline = None
+    if kern:
+        top = max((k for k in kern if k in kflops), key=lambda k: kern[k][1], default=None)
+        if top:
+            n, ms = kern[top]
+            achieved = kflops[top] / (ms / n * 1e-3) / 1e12
+            # kernels are timed inside a long step: the sustained figure is the denominator;
+            # TF32 has no measured entry, half of the BF16 figure stands in for it
+            peak = peaks["bf16_sustained"] if bf16 else peaks["bf16_sustained"] / 2
+            roofline = dict(bound="tensor", kernel=top, achieved=achieved, peak=peak, unit="TFLOP/s",
+                            frac=achieved / peak, traffic=None, launches=n, avg_ms=ms / n,
+                            peak_source=peaks["source"] + (" bf16 sustained" if bf16 else " bf16 sustained / 2 for tf32"),
+                            kernels={k: dict(scopes=v[0], ms=round(v[1], 3), share=round(v[1] / sum(x[1] for x in kern.values()), 4))
+                                     for k, v in sorted(kern.items(), key=lambda kv: -kv[1][1])})
+
+    # ---- end to end through the public API with host tensors (rank 0 reports) ----
+    e2e = None
+    if not args.no_e2e:
+        host_layer = Attention(d, nh, causal=causal, use_bias=True)
+        for i, p in enumerate("qkvo"):
+            host_layer.param("weight_" + p).set(w_host[i])
+        host_layer.set_precision(mma)
+        hx = Tensor.from_numpy(x_host, capi.DEVICE_CPU, bf16=bf16)
+        hg = Tensor.from_numpy(g_host, capi.DEVICE_CPU, bf16=bf16)
+        for tns in (hx, hg):
+            lib.boat_cuda_host_register(tns.data_ptr, tns.nbytes)
+
+        def host_step():
+            out = host_layer.forward(hx, hx, hx)
+            gq, gk, gv = host_layer.backward(hg)
+            loss_proxy = float(out.host_view().ravel()[0]) if not bf16 else 0.0   # touches the result on the host
+            for tt in (out, gq, gk, gv):
+                tt.free()
+            return loss_proxy
+
+        es = 2 if bf16 else 4
+        n_e2e = max(2, min(args.steps, 5))
+        host_step()
+        if dist is not None:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            host_step()
+        check(lib.boat_cuda_sync(), "sync")
+        dt = (time.perf_counter() - t0) / n_e2e
+        te = torch.tensor([dt], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        dt = float(te.item())
+        wbytes = (4 * d * d + 4 * d) * 4
+        e2e = dict(value=world * T / dt, unit="tokens/s", ms_per_step=dt * 1e3,
+                   h2d_bytes_per_step=2 * T * d * es + 2 * wbytes,        # X, dOut, parameters for fwd and bwd
+                   d2h_bytes_per_step=4 * T * d * es + wbytes,            # out, dq, dk, dv, parameter gradients
+                   note="host BF16 tensors in and out through boat_attention_forward/backward; wall clock" if bf16
+                   else "host FP32 tensors in and out through boat_attention_forward/backward; wall clock")
+        for tns in (hx, hg):
+            lib.boat_cuda_host_unregister(tns.data_ptr)
+        host_layer.free()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(cfg, 12.0, 1)
+        cpu.pop("seconds", None)
+
+    if rank == 0:
+        line = dict(metric="attention_fwd_bwd_tokens_per_s", value=tokens_per_s, unit="tokens/s", n_gpus=world,
+                    steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True,
+                    scaling="weak", vs_baseline=None, dtype="bf16" if bf16 else "tf32", data="synthetic",
+                    config=workload_config(args.workload, cfg, world),
+                    tflops_per_gpu=tflops_per_gpu,
+                    frac_of_bf16_peak=(tflops_per_gpu / peaks["bf16_sustained"]) if bf16 else None,
+                    roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches), clocks=clocks)
+        print(json.dumps(line))
+    if dist is not None:
+        check(lib.boat_cuda_comm_destroy(), "comm_destroy")
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -15,6 +15,14 @@ cudaStream_t stream();
 void count_launch(int n = 1);
 int ensure_init();
 
+// Optional per-kernel timing (boat_cuda_profile_*): while enabled, a scope records a CUDA
+// event pair on the library stream around the launches it encloses.
+struct ProfileScope {
+    explicit ProfileScope(const char* name);
+    ~ProfileScope();
+    int slot;
+};
+
 #define BOATCU_CHECK(expr)                                                          \
     do {                                                                            \
         cudaError_t err__ = (expr);                                                 \

@@ -38,6 +38,7 @@ int boat_cuda_gemm(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, con
         // Small or unaligned problems: same storage types, FP32 FMA arithmetic (more
         // accurate than the requested tensor-core format, never less).
     }
+    ProfileScope prof("gemm_simt");
     return gemm_simt(ta, tb, M, N, K, A, lda, B, ldb, in_type, C, ldc, out_type, bias);
 }
 
@@ -49,6 +50,7 @@ int boat_cuda_attn_fwd(int mma, int64_t units, int64_t S, int64_t hs, int causal
     if (!Q || !K || !V || !O || !lse) return set_error(11, "boat_cuda_attn_fwd: NULL operand");
     if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type))
         return attn_fwd_tc(mma, units, S, hs, causal, scale, Q, K, V, io_type, O, lse);
+    ProfileScope prof("attn_fwd_simt");
     return attn_fwd_simt(units, S, hs, causal, scale, Q, K, V, io_type, O, lse);
 }
 
@@ -74,10 +76,14 @@ int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal
     if (((uintptr_t)scratch & 255) != 0) return set_error(12, "boat_cuda_attn_bwd: scratch must be 256-byte aligned");
     float* delta = (float*)scratch;
     size_t delta_bytes = ((size_t)units * (size_t)S * sizeof(float) + 255) & ~(size_t)255;
-    if (int rc = rowdot(dO, O, io_type, units * S, hs, delta)) return rc;
+    {
+        ProfileScope prof("attn_delta");
+        if (int rc = rowdot(dO, O, io_type, units * S, hs, delta)) return rc;
+    }
     if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type))
         return attn_bwd_tc(mma, units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV,
                            (char*)scratch + delta_bytes, scratch_bytes - delta_bytes);
+    ProfileScope prof("attn_bwd_simt");
     return attn_bwd_simt(units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV);
 }
 

@@ -315,6 +315,7 @@ int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64
     if (dst_type == src_type) return boat_cuda_memcpy_d2d(dst, src, (size_t)n * type_size(dst_type));
     int vec = aligned16(dst) && aligned16(src) && (n % 8) == 0;
     int grid = grid_for(vec ? n / 8 : n, kThreads);
+    ProfileScope prof("cast");
     if (dst_type == BOAT_CUDA_BF16)
         cast_f32_to_bf16<<<grid, kThreads, 0, stream()>>>((__nv_bfloat16*)dst, (const float*)src, n, vec);
     else
@@ -326,6 +327,7 @@ int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64
 int boat_cuda_colsum(const void* X, int x_type, int64_t rows, int64_t cols, float* out) {
     if (cols <= 0) return 0;
     if (int rc = ensure_init()) return rc;
+    ProfileScope prof("colsum");
     BOATCU_CHECK(cudaMemsetAsync(out, 0, (size_t)cols * sizeof(float), stream()));
     if (rows <= 0) return 0;
     const int vec = x_type == BOAT_CUDA_BF16 ? 8 : 4;

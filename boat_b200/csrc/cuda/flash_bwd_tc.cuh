@@ -1,0 +1,337 @@
+// flash_bwd_tc.cuh - fused attention backward on tcgen05 (BF16 storage, FP32 accumulation).
+//
+// Replaces attention_backward (reference src/layers/attention.c:1421-1526), which keeps the
+// probabilities of the forward and builds four more [B,nh,S,S] tensors.  Here P is rebuilt
+// from the saved log-sum-exp, tile by tile, and nothing of size S x S touches HBM.
+//
+// One CTA owns one 128-row key/value tile of one (batch,head) unit and walks the query
+// tiles that see it (all of them, or those at or below the diagonal when causal).  K and V
+// stay in shared memory, dK and dV accumulate in tensor memory for the whole walk.  Per
+// query tile, with everything transposed so that key rows sit on the TMEM lanes:
+//
+//   S^T  = K . Q^T            dP^T = V . dO^T                   two SS MMAs
+//   P^T  = exp2(S^T*c - lse)  dS^T = P^T * (dP^T - delta) / sqrt(hs)
+//                                                               4 softmax warps, thread = key row
+//   dV  += P^T . dO           A = P^T in tensor memory (written over S^T)
+//   dK  += dS^T . Q           A = dS^T from shared memory (K-major view)
+//   dQ_i = dS . K             A = the same shared-memory tile read along M (MN-major view)
+//
+// dQ of a query tile gets one contribution per key tile; CTAs add theirs into an FP32 buffer
+// with vector reductions (red.global.add.v4.f32) from four dedicated warps, and a cast
+// kernel turns the sum into the output type afterwards.  With head size 128 the 512 TMEM
+// columns are exactly S^T/P^T, dP^T (reused for dQ), dV and dK.
+// Warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: softmax + final dK/dV store,
+// warps 6-9: dQ reduction.
+#pragma once
+#include "flash_fwd_tc.cuh"
+
+namespace boatcu {
+namespace flash {
+
+constexpr int kBwdThreads = 320;
+
+template <int HS>
+struct BwdCfg {
+    static constexpr int ROWB = HS * 2;
+    static constexpr int NBOX = ROWB / 128;
+    static constexpr int TILE_BYTES = NBOX * kBoxBytes;       // one 128 x HS BF16 tile
+    static constexpr int DS_BYTES = 2 * kBoxBytes;             // dS^T: 128 x 128 BF16
+    static constexpr int Q_STAGES = 2;
+    // K,V + Q,dO stages + dS^T + two (lse, delta) buffers + barriers.  With head size 128 this
+    // is 231,680 of the 232,448 bytes a CTA may have, so the base must come 1024-byte aligned
+    // from the launch (checked at kernel entry) - there is no room for manual alignment slack.
+    static constexpr int SMEM = 2 * TILE_BYTES + Q_STAGES * 2 * TILE_BYTES + DS_BYTES + 2048 + 256;
+    // tensor memory columns
+    static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HS;
+    static constexpr bool DQ_ALIASES_DP = (256 + 3 * HS) > 512;
+    static constexpr uint32_t COL_DQ = DQ_ALIASES_DP ? COL_DP : 256 + 2 * HS;
+    static constexpr uint32_t TMEM_COLS = 512;
+};
+
+struct BwdParams {
+    const float* lse;      // [units*S]
+    const float* delta;    // [units*S]
+    float* dq_accum;       // [units*S, hs] FP32, zeroed before the launch
+    void* dK;
+    void* dV;
+    int S, units, causal;
+    float scale;
+    unsigned int* status;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int HS>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                 const BwdParams p) {
+    using C = BwdCfg<HS>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if ((smem_u32(smem) & 1023u) != 0) {         // uniform for the whole CTA; nothing to undo yet
+        if (threadIdx.x == 0) atomicCAS(p.status, 0u, (unsigned int)kTimeoutOther + 100u);
+        return;
+    }
+    uint8_t* k_smem = smem;
+    uint8_t* v_smem = k_smem + C::TILE_BYTES;
+    uint8_t* q_smem = v_smem + C::TILE_BYTES;                          // [Q_STAGES]
+    uint8_t* do_smem = q_smem + C::Q_STAGES * C::TILE_BYTES;           // [Q_STAGES]
+    uint8_t* ds_smem = do_smem + C::Q_STAGES * C::TILE_BYTES;
+    float* stat_s = (float*)(ds_smem + C::DS_BYTES);                   // [2][lse*log2e[128], delta[128]]
+    uint64_t* bars = (uint64_t*)(stat_s + 512);
+    uint64_t* kv_full = bars;                   // 1
+    uint64_t* q_full = bars + 1;                // [2]
+    uint64_t* q_empty = bars + 3;               // [2]
+    uint64_t* s_full = bars + 5;                // S^T and dP^T complete
+    uint64_t* ds_full = bars + 6;               // P^T in TMEM, dS^T in smem (128 arrivals)
+    uint64_t* dq_full = bars + 7;               // dV, dK, dQ MMAs of the tile complete
+    uint64_t* dq_empty = bars + 8;              // dQ read out (128 arrivals)
+    uint64_t* all_done = bars + 9;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    volatile uint32_t* softmax_ok = tmem_slot + 1;     // written by one softmax thread, read by all 128
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = p.S / kTile;
+    const int unit = blockIdx.x % p.units;
+    const int jt = blockIdx.x / p.units;                 // key tile; small jt = long walk, scheduled first
+    const int i_begin = p.causal ? jt : 0;
+    const int n_q = n_tiles - i_begin;
+    const int row_base = unit * p.S;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&q_full[s], 1);
+            mbar_init(&q_empty[s], 1);
+        }
+        mbar_init(s_full, 1);
+        mbar_init(ds_full, 128);
+        mbar_init(dq_full, 1);
+        mbar_init(dq_empty, 128);
+        mbar_init(all_done, 1);
+        fence_barrier_init();
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+        tma_prefetch_desc(&map_do);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            mbar_arrive_expect_tx(kv_full, 2 * C::TILE_BYTES);
+            for (int b = 0; b < C::NBOX; ++b) {
+                tma_load_2d(k_smem + b * kBoxBytes, &map_k, kv_full, b * 64, row_base + jt * kTile);
+                tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jt * kTile);
+            }
+            for (int t = 0; t < n_q && ok; ++t) {
+                const int s = t & 1;
+                if (!mbar_wait(&q_empty[s], ((t >> 1) & 1) ^ 1, p.status, kTimeoutProducer)) { ok = false; break; }
+                mbar_arrive_expect_tx(&q_full[s], 2 * C::TILE_BYTES);
+                const int y = row_base + (i_begin + t) * kTile;
+                for (int b = 0; b < C::NBOX; ++b) {
+                    tma_load_2d(q_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[s], b * 64, y);
+                    tma_load_2d(do_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_do, &q_full[s], b * 64, y);
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_st = make_idesc(kBF16, false, false, kTile, kTile);   // K.Q^T, V.dO^T
+            constexpr uint32_t idesc_acc = make_idesc(kBF16, false, true, kTile, HS);      // dV, dK
+            constexpr uint32_t idesc_dq = make_idesc(kBF16, true, true, kTile, HS);        // dQ
+            const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
+            bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutMma);
+            for (int t = 0; t < n_q && ok; ++t) {
+                const int s = t & 1;
+                if (!mbar_wait(&q_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
+                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < C::ROWB / 32; ++kk) {
+                    const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+                    mma_ss<false>(tmem_base + C::COL_S, smem_desc_sw128(k_addr + off, 16, 1024),
+                                  smem_desc_sw128(q_addr + off, 16, 1024), idesc_st, kk > 0);
+                }
+                if (C::DQ_ALIASES_DP && t > 0) {
+                    // dP^T is about to overwrite the columns that still hold the previous dQ
+                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    tc_fence_after_sync();
+                }
+#pragma unroll
+                for (int kk = 0; kk < C::ROWB / 32; ++kk) {
+                    const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+                    mma_ss<false>(tmem_base + C::COL_DP, smem_desc_sw128(v_addr + off, 16, 1024),
+                                  smem_desc_sw128(do_addr + off, 16, 1024), idesc_st, kk > 0);
+                }
+                mma_commit(s_full);
+                if (!mbar_wait(ds_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
+                    mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + kk * 8,
+                                  smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk) {    // dK += dS^T . Q
+                    const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+                    mma_ss<false>(tmem_base + C::COL_DK, smem_desc_sw128(ds_addr + off, 16, 1024),
+                                  smem_desc_mn(q_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
+                }
+                if (!C::DQ_ALIASES_DP && t > 0) {
+                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    tc_fence_after_sync();
+                }
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)      // dQ_i = dS . K        (K = 128 key rows)
+                    mma_ss<false>(tmem_base + C::COL_DQ, smem_desc_mn(ds_addr + kk * 2048, kBoxBytes, false),
+                                  smem_desc_mn(k_addr + kk * 2048, kBoxBytes, false), idesc_dq, kk > 0);
+                mma_commit(&q_empty[s]);
+                mma_commit(dq_full);
+            }
+            if (ok) mma_commit(all_done);
+        }
+    } else if (warp < 6) {
+        // ---------------- softmax / dS: warps 2..5, thread = key row ----------------
+        const int lane_group = warp & 3;
+        const int r = lane_group * 32 + lane;                       // key row inside the tile
+        const int tid128 = (warp - 2) * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+        const float sl2 = p.scale * 1.4426950408889634f;
+        uint8_t* ds_row = ds_smem + r * 128;
+        const int swz = r & 7;
+        bool ok = true;
+        for (int t = 0; t < n_q; ++t) {
+            const int i = i_begin + t;
+            // Stage lse*log2e and delta of this query tile in the buffer of this tile's parity.
+            // A thread can only get two tiles ahead of another by passing the barrier of the
+            // tile in between, which needs that other thread to have left this tile.
+            float* lse_s = stat_s + (t & 1) * 256;
+            float* delta_s = lse_s + 128;
+            {
+                const int64_t g = (int64_t)row_base + (int64_t)i * kTile + tid128;
+                lse_s[tid128] = p.lse[g] * 1.4426950408889634f;
+                delta_s[tid128] = p.delta[g];
+            }
+            // One thread does the bounded wait and publishes the outcome, so that all 128 take
+            // the same branch and nobody is left alone at the named barrier.
+            if (tid128 == 0) *softmax_ok = mbar_wait(s_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
+            named_barrier_sync(1, 128);
+            if (*softmax_ok == 0u) { ok = false; break; }
+            tc_fence_after_sync();
+            const bool diag = p.causal && i == jt;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tmem_base + C::COL_S + lane_addr + c * 32, sv);
+                tmem_ld32(tmem_base + C::COL_DP + lane_addr + c * 32, dv);
+                tmem_wait_ld();
+                uint32_t ph[16], dh[16];
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    const int q0 = c * 32 + x;
+                    float p0 = fast_exp2(fmaf(__uint_as_float(sv[x]), sl2, -lse_s[q0]));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), sl2, -lse_s[q0 + 1]));
+                    if (diag) {                      // query q sees key r only when q >= r
+                        if (q0 < r) p0 = 0.f;
+                        if (q0 + 1 < r) p1 = 0.f;
+                    }
+                    const float d0 = p0 * (__uint_as_float(dv[x]) - delta_s[q0]) * p.scale;
+                    const float d1 = p1 * (__uint_as_float(dv[x + 1]) - delta_s[q0 + 1]) * p.scale;
+                    ph[x >> 1] = pack_bf16(p0, p1);
+                    dh[x >> 1] = pack_bf16(d0, d1);
+                }
+                tmem_st16(tmem_base + C::COL_S + lane_addr + c * 16, ph);      // P^T over S^T, 2 per column
+                // dS^T row r, query columns 32c..32c+31: 4 units of 16 bytes in box c/2
+                uint8_t* box = ds_row + (c >> 1) * kBoxBytes;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int unit16 = (c & 1) * 4 + u;
+                    *reinterpret_cast<uint4*>(box + ((unit16 ^ swz) << 4)) =
+                        make_uint4(dh[4 * u], dh[4 * u + 1], dh[4 * u + 2], dh[4 * u + 3]);
+                }
+            }
+            tmem_wait_st();
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(ds_full);
+        }
+        // final: dK, dV -> global
+        if (ok && mbar_wait(all_done, 0, p.status, kTimeoutEpilogue)) {
+            tc_fence_after_sync();
+            const int64_t grow = (int64_t)row_base + (int64_t)jt * kTile + r;
+#pragma unroll 1
+            for (int which = 0; which < 2; ++which) {
+                __nv_bfloat16* out = (__nv_bfloat16*)(which ? p.dK : p.dV) + grow * HS;
+                const uint32_t col = which ? C::COL_DK : C::COL_DV;
+#pragma unroll 1
+                for (int c = 0; c < HS / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + col + lane_addr + c * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int x = 0; x < 32; x += 8) {
+                        uint4 o;
+                        o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+                        o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                        o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+                        o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
+                        *reinterpret_cast<uint4*>(out + c * 32 + x) = o;
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- dQ reduction: warps 6..9, thread = query row ----------------
+        const int lane_group = warp & 3;
+        const int r = lane_group * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+        for (int t = 0; t < n_q; ++t) {
+            if (!mbar_wait(dq_full, t & 1, p.status, kTimeoutOther)) break;
+            tc_fence_after_sync();
+            float* dst = p.dq_accum + ((int64_t)row_base + (int64_t)(i_begin + t) * kTile + r) * HS;
+#pragma unroll 1
+            for (int c = 0; c < HS / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + C::COL_DQ + lane_addr + c * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 32; x += 4)
+                    red_add_v4(dst + c * 32 + x, __uint_as_float(v[x]), __uint_as_float(v[x + 1]),
+                               __uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+            }
+            tc_fence_before_sync();
+            mbar_arrive(dq_empty);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+}  // namespace flash
+}  // namespace boatcu

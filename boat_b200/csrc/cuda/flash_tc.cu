@@ -1,6 +1,6 @@
 // flash_tc.cu - host side of the tcgen05 attention-core kernels: shape support, tensor maps,
 // launches.  The kernels themselves are in flash_fwd_tc.cuh and flash_bwd_tc.cuh.
-#include "flash_fwd_tc.cuh"
+#include "flash_bwd_tc.cuh"
 
 namespace boatcu {
 
@@ -34,6 +34,7 @@ int launch_fwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
         configured = true;
     }
     const int64_t grid = units * (S / kTile);
+    ProfileScope prof("flash_fwd");
     kern<<<(unsigned)grid, kFwdThreads, C::SMEM, stream()>>>(mq, mk, mv, p);
     BOATCU_LAUNCH_OK("flash_fwd");
     return 0;
@@ -60,12 +61,69 @@ int attn_fwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float
     return launch_fwd<float, 64>(units, S, causal, scale, Q, K, V, O, lse);
 }
 
-size_t attn_bwd_tc_scratch_bytes(int, int64_t, int64_t, int64_t) { return 0; }
+namespace {
+
+template <int HS>
+int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q, const void* K, const void* V,
+               const void* dO, const float* lse, const float* delta, void* dQ, void* dK, void* dV, float* dq_accum) {
+    using C = BwdCfg<HS>;
+    CUtensorMap mq, mk, mv, mdo;
+    const uint64_t rows = (uint64_t)units * (uint64_t)S;
+    if (int rc = make_tensor_map_2d(&mq, Q, 2, rows, HS, HS, kTile, 64)) return rc;
+    if (int rc = make_tensor_map_2d(&mk, K, 2, rows, HS, HS, kTile, 64)) return rc;
+    if (int rc = make_tensor_map_2d(&mv, V, 2, rows, HS, HS, kTile, 64)) return rc;
+    if (int rc = make_tensor_map_2d(&mdo, dO, 2, rows, HS, HS, kTile, 64)) return rc;
+    const size_t n = (size_t)units * (size_t)S * HS;
+    BwdParams p;
+    p.lse = lse;
+    p.delta = delta;
+    p.dq_accum = dq_accum;
+    p.dK = dK;
+    p.dV = dV;
+    p.S = (int)S;
+    p.units = (int)units;
+    p.causal = causal;
+    p.scale = scale;
+    p.status = kernel_status_ptr();
+    auto kern = flash_bwd_kernel<HS>;
+    static bool configured = false;
+    if (!configured) {
+        BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured = true;
+    }
+    {
+        ProfileScope prof("flash_bwd");
+        BOATCU_CHECK(cudaMemsetAsync(dq_accum, 0, n * sizeof(float), stream()));
+        const int64_t grid = units * (S / kTile);
+        kern<<<(unsigned)grid, kBwdThreads, C::SMEM, stream()>>>(mq, mk, mv, mdo, p);
+        BOATCU_LAUNCH_OK("flash_bwd");
+        // the summed FP32 contributions become the BF16 output
+        if (int rc = boat_cuda_cast(dQ, BOAT_CUDA_BF16, dq_accum, BOAT_CUDA_F32, (int64_t)n)) return rc;
+    }
+    return 0;
+}
+
+}  // namespace
+
+// Scratch of the tensor-core backward: the FP32 accumulation buffer of dQ.
+size_t attn_bwd_tc_scratch_bytes(int mma, int64_t units, int64_t S, int64_t hs) {
+    if (mma != BOAT_MMA_BF16) return 0;
+    return (size_t)units * (size_t)S * (size_t)hs * sizeof(float);
+}
 
 int attn_bwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q, const void* K,
                 const void* V, const void* dO, const float* lse, const float* delta, int io_type, void* dQ, void* dK,
                 void* dV, void* scratch, size_t scratch_bytes) {
-    (void)mma; (void)scratch; (void)scratch_bytes;
+    if (int rc = ensure_init()) return rc;
+    if (mma == BOAT_MMA_BF16) {
+        if (scratch_bytes < attn_bwd_tc_scratch_bytes(mma, units, S, hs))
+            return set_error(12, "attention backward: scratch too small for the dQ accumulation buffer");
+        if (hs == 64)
+            return launch_bwd<64>(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV, (float*)scratch);
+        return launch_bwd<128>(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV, (float*)scratch);
+    }
+    // FP32 storage: the backward of the TF32 path still runs on the CUDA cores
+    ProfileScope prof("attn_bwd_simt");
     return attn_bwd_simt(units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV);
 }
 

@@ -283,6 +283,7 @@ int launch(int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const vo
     }
     int work = tiles * split_k;
     int grid = work < kSMs ? work : kSMs;
+    ProfileScope prof(A_MN ? "gemm_tc_tn" : (B_MN ? "gemm_tc_nn" : "gemm_tc_nt"));
     kern<<<grid, kThreads, C::SMEM, stream()>>>(map_a, map_b, p);
     BOATCU_LAUNCH_OK("gemm_tc");
     return 0;

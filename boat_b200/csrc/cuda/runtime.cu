@@ -9,6 +9,9 @@
 #include <atomic>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
+#include <string>
+#include <map>
 
 namespace boatcu {
 
@@ -126,6 +129,28 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int esize, uint64_t r
     return 0;
 }
 
+// ---- per-kernel timing ---------------------------------------------------------------------
+struct ProfileEntry {
+    const char* name;
+    cudaEvent_t start, stop;
+};
+static bool g_profiling = false;
+static std::vector<ProfileEntry>* g_profile = nullptr;
+
+ProfileScope::ProfileScope(const char* name) : slot(-1) {
+    if (!g_profiling) return;
+    ProfileEntry e;
+    e.name = name;
+    if (cudaEventCreate(&e.start) != cudaSuccess || cudaEventCreate(&e.stop) != cudaSuccess) return;
+    cudaEventRecord(e.start, g_stream);
+    g_profile->push_back(e);
+    slot = (int)g_profile->size() - 1;
+}
+
+ProfileScope::~ProfileScope() {
+    if (slot >= 0) cudaEventRecord((*g_profile)[slot].stop, g_stream);
+}
+
 int ensure_init() {
     if (g_ready) return 0;
     std::lock_guard<std::mutex> lk(g_mu);
@@ -223,6 +248,41 @@ int boat_cuda_memset(void* dst, int value, size_t bytes) {
     if (bytes == 0) return 0;
     if (int rc = ensure_init()) return rc;
     BOATCU_CHECK(cudaMemsetAsync(dst, value, bytes, g_stream));
+    return 0;
+}
+
+int boat_cuda_profile_enable(int on) {
+    if (int rc = ensure_init()) return rc;
+    if (!g_profile) g_profile = new std::vector<ProfileEntry>();
+    g_profiling = on != 0;
+    return 0;
+}
+
+// Waits for the stream, then writes one line per kernel family into `out`:
+// "<name> <launch scopes> <total milliseconds>\n".  Clears the record.
+int boat_cuda_profile_report(char* out, size_t out_bytes) {
+    if (!out || out_bytes == 0) return set_error(4, "boat_cuda_profile_report: no buffer");
+    out[0] = 0;
+    if (!g_profile) return 0;
+    BOATCU_CHECK(cudaStreamSynchronize(g_stream));
+    std::map<std::string, std::pair<int, double>> acc;
+    for (auto& e : *g_profile) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, e.start, e.stop) == cudaSuccess) {
+            auto& a = acc[e.name];
+            a.first += 1;
+            a.second += ms;
+        }
+        cudaEventDestroy(e.start);
+        cudaEventDestroy(e.stop);
+    }
+    g_profile->clear();
+    size_t used = 0;
+    for (auto& kv : acc) {
+        int n = snprintf(out + used, out_bytes - used, "%s %d %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        if (n < 0 || (size_t)n >= out_bytes - used) break;
+        used += (size_t)n;
+    }
     return 0;
 }
 

@@ -46,6 +46,10 @@ int         boat_cuda_host_register(void* host, size_t bytes);   /* pin a caller
 int         boat_cuda_host_unregister(void* host);
 size_t      boat_cuda_bytes_in_use(void);        /* bytes handed out by boat_cuda_malloc and not yet freed */
 uint64_t    boat_cuda_launch_count(void);        /* kernels of this library launched so far */
+/* Per-kernel timing for benchmarks: while enabled, every kernel family is bracketed by CUDA
+ * events on the library stream; report() synchronises and writes "<name> <scopes> <ms>" lines. */
+int         boat_cuda_profile_enable(int on);
+int         boat_cuda_profile_report(char* out, size_t out_bytes);
 
 /* ---- contraction: replaces boat_matmul (src/ops/linear.c:12-170) as used by
  *      linear_projection (src/layers/attention.c:247-308) and

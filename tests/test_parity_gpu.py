@@ -165,3 +165,50 @@ def test_scaled_dot_product_attention_entry_point(gpu_lib):
     t3 = Tensor.from_numpy(inp["v"])                                       # 3-D: copy of value
     out = Tensor(lib.boat_scaled_dot_product_attention(t3.h, t3.h, t3.h, 1.0, None, False, 0.0))
     assert np.array_equal(out.numpy(), inp["v"])
+
+
+# ---- tensor-core paths of the whole layer -----------------------------------------------------------
+
+TC_CASES = [
+    # name, B, S, H, nh, causal
+    ("hs64_full", 2, 256, 256, 4, False),
+    ("hs64_causal", 2, 384, 256, 4, True),
+    ("hs128_causal", 1, 256, 256, 2, True),
+    ("hs64_long", 1, 1024, 128, 2, True),
+]
+
+
+@pytest.mark.parametrize("name,B,S,H,nh,causal", TC_CASES, ids=[c[0] for c in TC_CASES])
+@pytest.mark.parametrize("device", [capi.DEVICE_CPU, capi.DEVICE_CUDA], ids=["host_tensors", "cuda_tensors"])
+def test_bf16_tensor_core_path_matches_restatement(gpu_lib, name, B, S, H, nh, causal, device):
+    case = cases.Case(name, B, S, H, nh, causal=causal, bias_std=0.1)
+    inp = case.inputs(bf16=True)           # both sides start from the BF16-rounded values
+    ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], nh, causal)
+    res = gpu_step(inp, nh, causal, device=device, precision=capi.MMA_BF16, bf16=True)
+    assert_close(res, ref, TOL_BF16, name)
+
+
+@pytest.mark.parametrize("name,B,S,H,nh,causal", [c for c in TC_CASES if c[3] // c[4] == 64], ids=lambda v: str(v))
+def test_tf32_tensor_core_path_matches_restatement(gpu_lib, name, B, S, H, nh, causal):
+    case = cases.Case(name, B, S, H, nh, causal=causal, bias_std=0.1)
+    inp = case.inputs()
+    ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], nh, causal)
+    res = gpu_step(inp, nh, causal, device=capi.DEVICE_CUDA, precision=capi.MMA_TF32)
+    assert_close(res, ref, TOL_TF32, name)
+
+
+def test_fp32_inputs_with_bf16_arithmetic(gpu_lib):
+    """FP32 tensors in, BF16 tensor cores inside, FP32 tensors out."""
+    case = cases.Case("mixed", 1, 256, 128, 2, causal=True)
+    inp = case.inputs(bf16=True)
+    ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], 2, True)
+    res = gpu_step(inp, 2, True, device=capi.DEVICE_CUDA, precision=capi.MMA_BF16, bf16=False)
+    assert_close(res, ref, TOL_BF16, "mixed")
+
+
+def test_automatic_precision_uses_tensor_cores_within_tf32_tolerance(gpu_lib):
+    case = cases.Case("auto", 1, 256, 128, 2)
+    inp = case.inputs()
+    ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], 2, False)
+    res = gpu_step(inp, 2, False, device=capi.DEVICE_CUDA, precision=-1)
+    assert_close(res, ref, TOL_TF32, "auto")
