@@ -149,6 +149,8 @@ PROTOTYPES = {
     "boat_cuda_attn_fwd": (_I, [_I, _I64, _I64, _I64, _I, _F, _P, _P, _P, _I, _P, _P]),
     "boat_cuda_attn_bwd_scratch_bytes": (_SZ, [_I, _I64, _I64, _I64]),
     "boat_cuda_attn_bwd": (_I, [_I, _I64, _I64, _I64, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _SZ]),
+    "boat_cuda_attn_bwd_static_capacity": (_SZ, []),
+    "boat_cuda_attn_bwd_static": (_I, [_I, _I64, _I64, _I64, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P]),
     "boat_cuda_colsum": (_I, [_P, _I, _I64, _I64, _P]),
     "boat_cuda_axpy": (_I, [_P, _P, _F, _I64]),
     "boat_cuda_scale": (_I, [_P, _P, _F, _I64]),

@@ -14,6 +14,7 @@ int set_error(int status, const char* fmt, ...);
 cudaStream_t stream();
 void count_launch(int n = 1);
 int ensure_init();
+bool ready();          // has boat_cuda_init (or a first call) bound the library to a device yet?
 
 // Optional per-kernel timing (boat_cuda_profile_*): while enabled, a scope records a CUDA
 // event pair on the library stream around the launches it encloses.

@@ -35,6 +35,7 @@ int set_error(int status, const char* fmt, ...) {
 }
 
 cudaStream_t stream() { return g_stream; }
+bool ready() { return g_ready; }
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
 static int pick_device(int requested) {

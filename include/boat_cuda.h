@@ -90,6 +90,26 @@ int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal
                        const void* dO, const float* lse, int io_type,
                        void* dQ, void* dK, void* dV, void* scratch, size_t scratch_bytes);
 
+/* ---- attention core backward without caller scratch (no counterpart in the reference) -----
+ * Same computation and arguments as boat_cuda_attn_bwd, for callers that cannot provide
+ * scratch because they may not allocate device memory where they call from: serving loops
+ * that ban cudaMalloc (it can stall every stream of the device), programs with a device
+ * memory budget fixed at start-up, plugins inside a host framework that owns all HBM.
+ * The scratch is a fixed 16 MiB block inside the library image (capacity() returns the
+ * size); each GPU that loads the library holds it until the process exits.  Problems whose
+ * boat_cuda_attn_bwd_scratch_bytes() exceeds it are refused with a clear error.
+ * The call makes no cudaMalloc/cudaFree and no allocating library call.  It never
+ * initialises the library: call boat_cuda_init() once beforehand (that does allocate).
+ * The first call on a device looks up the block's device address; make that first call
+ * outside any stream capture.  All calls share the one block and it keeps the previous
+ * call's contents - the kernels clear what they sum into - so two calls whose GPU work
+ * overlaps (different streams, different threads) race on it: keep them on one stream. */
+size_t boat_cuda_attn_bwd_static_capacity(void);
+int boat_cuda_attn_bwd_static(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale,
+                              const void* Q, const void* K, const void* V, const void* O,
+                              const void* dO, const float* lse, int io_type,
+                              void* dQ, void* dK, void* dV);
+
 /* ---- element-wise / reduction tail ----------------------------------------------------
  * colsum:  out[j] = sum_i X[i,j]     bias gradient loop, attention.c:1271-1284
  * axpy:    y += alpha * x            boat_add_ (arithmetic.c:362-391) with alpha = 1 for
