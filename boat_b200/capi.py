@@ -157,6 +157,7 @@ PROTOTYPES = {
     "boat_cuda_add_bias": (_I, [_P, _P, _P, _I64, _I64]),
     "boat_cuda_mul": (_I, [_P, _P, _P, _I64]),
     "boat_cuda_cast": (_I, [_P, _I, _P, _I, _I64]),
+    "boat_cuda_round_tf32": (_I, [_P, _P, _I64]),
     "boat_cuda_transpose": (_I, [_P, _P, _I64, _I64, _I64]),
     "boat_cuda_comm_unique_id": (_I, [_P]),
     "boat_cuda_comm_init": (_I, [_I, _I, _P]),

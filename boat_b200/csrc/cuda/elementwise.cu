@@ -140,6 +140,30 @@ __global__ void cast_bf16_to_f32(float* __restrict__ dst, const __nv_bfloat16* _
     }
 }
 
+// ---- y = x rounded to the nearest TF32 value (10-bit mantissa), still stored as FP32 -------------
+// tcgen05 kind::tf32 drops the low 13 mantissa bits of its operands; a chain of contractions
+// then drifts by a systematic ~2^-11 per stage.  Rounding operands to nearest beforehand
+// makes the truncation exact and the error unbiased.
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+__global__ void round_tf32_kernel(float* __restrict__ y, const float* __restrict__ x, int64_t n, int vec) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t step = (int64_t)gridDim.x * blockDim.x;
+    if (vec) {
+        int64_t n4 = n / 4;
+        for (; i < n4; i += step) {
+            float4 v = reinterpret_cast<const float4*>(x)[i];
+            reinterpret_cast<float4*>(y)[i] = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
+        }
+    } else {
+        for (; i < n; i += step) y[i] = round_tf32(x[i]);
+    }
+}
+
 // ---- column sums: out[j] += sum_i X[i,j] -----------------------------------------------------
 // Block = 32 column lanes x 8 row lanes; a column lane owns VEC adjacent columns.  Row lanes
 // are combined through shared memory, blocks through atomicAdd into a zeroed output.
@@ -321,6 +345,16 @@ int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64
     else
         cast_bf16_to_f32<<<grid, kThreads, 0, stream()>>>((float*)dst, (const __nv_bfloat16*)src, n, vec);
     BOATCU_LAUNCH_OK("cast");
+    return 0;
+}
+
+int boat_cuda_round_tf32(float* y, const float* x, int64_t n) {
+    if (n <= 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    int vec = aligned16(y) && aligned16(x) && (n % 4) == 0;
+    ProfileScope prof("round_tf32");
+    round_tf32_kernel<<<grid_for(vec ? n / 4 : n, kThreads), kThreads, 0, stream()>>>(y, x, n, vec);
+    BOATCU_LAUNCH_OK("round_tf32");
     return 0;
 }
 

@@ -245,8 +245,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if (TF32) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        lsum += pv[i];
-                        r[i] = __float_as_uint(pv[i]);
+                        // round to the nearest TF32 value: the MMA would otherwise truncate
+                        uint32_t t32;
+                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t32) : "f"(pv[i]));
+                        lsum += __uint_as_float(t32);
+                        r[i] = t32;
                     }
                     tmem_st32(tmem_s + lane_addr + c * 32, r);
                 } else {

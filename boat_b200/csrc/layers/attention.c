@@ -93,6 +93,32 @@ static void* stage_in(const boat_tensor_t* t, int type, bool* owned) {
     return out;
 }
 
+/* Operand for arithmetic `mma`: like stage_in, and for TF32 the values are additionally
+ * rounded to the nearest TF32 number (in a private copy - the caller's tensor is never
+ * modified), so that the tensor core's truncation of FP32 operands is exact. */
+static void* stage_operand(const boat_tensor_t* t, int mma, int type, bool* owned) {
+    void* p = stage_in(t, type, owned);
+    if (!p || mma != BOAT_MMA_TF32) return p;
+    void* dst = p;
+    if (!*owned) {
+        dst = dev_alloc(t->nelements * sizeof(float));
+        if (!dst) return NULL;
+        *owned = true;
+    }
+    if (boat_report("TF32 rounding", boat_cuda_round_tf32((float*)dst, (const float*)p, (int64_t)t->nelements)) != 0) {
+        dev_free(dst);
+        *owned = false;
+        return NULL;
+    }
+    return dst;
+}
+
+/* Values a kernel produced that feed another TF32 contraction: round in place. */
+static int settle_tf32(int mma, void* buf, int64_t n) {
+    if (mma != BOAT_MMA_TF32) return 0;
+    return boat_report("TF32 rounding", boat_cuda_round_tf32((float*)buf, (const float*)buf, n));
+}
+
 /* New tensor with the dtype/device of `like`, filled from device buffer `src` (storage
  * `type`, n elements).  `src` may be adopted as the tensor's memory when it already has the
  * right type and place; *adopted tells the caller not to free it then. */
@@ -174,10 +200,10 @@ static void release_params(staged_params_t* p) {
     memset(p, 0, sizeof *p);
 }
 
-static bool stage_params(const boat_attention_t* a, int type, staged_params_t* p) {
+static bool stage_params(const boat_attention_t* a, int mma, int type, staged_params_t* p) {
     memset(p, 0, sizeof *p);
     for (int i = 0; i < 4; ++i) {
-        p->w[i] = stage_in(a->param[WQ + i], type, &p->w_owned[i]);
+        p->w[i] = stage_operand(a->param[WQ + i], mma, type, &p->w_owned[i]);
         if (!p->w[i]) goto fail;
         if (a->param[BQ + i]) {
             p->b[i] = (float*)stage_in(a->param[BQ + i], BOAT_CUDA_F32, &p->b_owned[i]);
@@ -277,7 +303,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
     staged_params_t p;
     void* d_out = NULL;
     boat_tensor_t* result = NULL;
-    if (!stage_params(a, type, &p)) goto done;
+    if (!stage_params(a, mma, type, &p)) goto done;
 
     for (int i = 0; i < 3; ++i) {
         int same = -1;
@@ -287,7 +313,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
             a->d_in[i] = a->d_in[same];
             a->d_in_owned[i] = false;
         } else {
-            a->d_in[i] = stage_in(in[i], type, &a->d_in_owned[i]);
+            a->d_in[i] = stage_operand(in[i], mma, type, &a->d_in_owned[i]);
             if (!a->d_in[i]) goto done;
         }
     }
@@ -297,6 +323,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
         if (boat_report("projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_in[i], H, p.w[i], H, type,
                                                      a->d_proj[i], H, type, p.b[i])) != 0)
             goto done;
+        if (settle_tf32(mma, a->d_proj[i], T * H) != 0) goto done;
     }
     a->d_ctx = dev_alloc(act_bytes);
     a->d_lse = (float*)dev_alloc((size_t)B * nh * S * sizeof(float));
@@ -306,6 +333,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
                                                          1.0f / sqrtf((float)hs), a->d_proj[0], a->d_proj[1],
                                                          a->d_proj[2], type, a->d_ctx, a->d_lse)) != 0)
         goto done;
+    if (settle_tf32(mma, a->d_ctx, T * H) != 0) goto done;
     /* The output projection writes the caller's dtype directly when that is a device
      * storage type the GEMM can emit. */
     {
@@ -386,8 +414,8 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     size_t scratch_bytes;
 
     if (!ensure_grads(a)) goto done;
-    if (!stage_params(a, type, &p)) goto done;
-    d_go = stage_in(grad_output, type, &go_owned);
+    if (!stage_params(a, mma, type, &p)) goto done;
+    d_go = stage_operand(grad_output, mma, type, &go_owned);
     if (!d_go) goto done;
     /* gradients are produced in HBM; a host layer receives them with one copy at the end */
     d_bucket = a->device == BOAT_DEVICE_CUDA ? (float*)a->grad_bucket->data
@@ -404,6 +432,7 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     d_dctx = dev_alloc(act_bytes);
     if (!d_dctx) goto done;
     if (boat_report("dOut.Wo^T", boat_cuda_gemm(mma, 0, 1, T, H, H, d_go, H, p.w[WO], H, type, d_dctx, H, type, NULL)) != 0) goto done;
+    if (settle_tf32(mma, d_dctx, T * H) != 0) goto done;
     if (boat_report("dWo", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_ctx, H, d_go, H, type, d_dw[WO], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
     if (bias && boat_report("dbo", boat_cuda_colsum(d_go, type, T, H, d_db[WO])) != 0) goto done;
 
@@ -420,6 +449,8 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
                                        a->d_proj[0], a->d_proj[1], a->d_proj[2], a->d_ctx, d_dctx, a->d_lse, type,
                                        d_dproj[0], d_dproj[1], d_dproj[2], scratch, scratch_bytes)) != 0)
         goto done;
+    for (int i = 0; i < 3; ++i)
+        if (settle_tf32(mma, d_dproj[i], T * H) != 0) goto done;
 
     /* input projections: dX = dP . W^T,  dW = X^T . dP,  db = colsum(dP) */
     for (int i = 0; i < 3; ++i) {

@@ -120,6 +120,8 @@ int boat_cuda_attn_bwd_static(int mma, int64_t units, int64_t S, int64_t hs, int
  * add_bias: y[i,j] = x[i,j] + b[j]   boat_add bias broadcast (arithmetic.c:199-203)
  * mul:     y = a * b                 boat_mul, equal shapes (arithmetic.c:240-285)
  * cast:    FP32 <-> BF16, round to nearest even
+ * round_tf32: y = x rounded to the nearest TF32 value, stored as FP32 (in place allowed);
+ *          operands prepared this way make the tensor core's own truncation exact
  * transpose: out[b, j, i] = in[b, i, j]   boat_transpose of the last two dims (linear.c:238-406) */
 int boat_cuda_colsum(const void* X, int x_type, int64_t rows, int64_t cols, float* out);
 int boat_cuda_axpy(float* y, const float* x, float alpha, int64_t n);
@@ -127,6 +129,7 @@ int boat_cuda_scale(float* y, const float* x, float alpha, int64_t n);
 int boat_cuda_add_bias(float* y, const float* x, const float* bias, int64_t rows, int64_t cols);
 int boat_cuda_mul(float* y, const float* a, const float* b, int64_t n);
 int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64_t n);
+int boat_cuda_round_tf32(float* y, const float* x, int64_t n);
 int boat_cuda_transpose(float* out, const float* in, int64_t batch, int64_t rows, int64_t cols);
 
 /* ---- gradient exchange between GPUs (nothing in the reference: it is single-process) ---
