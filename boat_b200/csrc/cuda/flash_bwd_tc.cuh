@@ -11,24 +11,26 @@
 //
 //   S^T  = K . Q^T            dP^T = V . dO^T                   two SS MMAs
 //   P^T  = exp2(S^T*c - lse)  dS^T = P^T * (dP^T - delta) / sqrt(hs)
-//                                                               4 softmax warps, thread = key row
+//                                                               8 softmax warps, thread = key row x half
 //   dV  += P^T . dO           A = P^T in tensor memory (written over S^T)
 //   dK  += dS^T . Q           A = dS^T from shared memory (K-major view)
 //   dQ_i = dS . K             A = the same shared-memory tile read along M (MN-major view)
 //
 // dQ of a query tile gets one contribution per key tile; CTAs add theirs into an FP32 buffer
-// with vector reductions (red.global.add.v4.f32) from four dedicated warps, and a cast
-// kernel turns the sum into the output type afterwards.  With head size 128 the 512 TMEM
+// with TMA reduce-add (cp.reduce.async.bulk.tensor), staged through the dS^T tile by four
+// dedicated warps, and a cast kernel turns the sum into the output type afterwards.  With head size 128 the 512 TMEM
 // columns are exactly S^T/P^T, dP^T (reused for dQ), dV and dK.
-// Warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: softmax + final dK/dV store,
-// warps 6-9: dQ reduction.
+// Warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store (two warps
+// per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.  The score MMA and
+// the dP MMA signal separately, so the exponentials of a tile run while the previous tile's
+// dQ is still being read out of the columns that dP^T re-uses.
 #pragma once
 #include "flash_fwd_tc.cuh"
 
 namespace boatcu {
 namespace flash {
 
-constexpr int kBwdThreads = 320;
+constexpr int kBwdThreads = 448;
 
 template <int HS>
 struct BwdCfg {
@@ -59,10 +61,6 @@ struct BwdParams {
     unsigned int* status;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -76,7 +74,7 @@ template <int HS>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                 const BwdParams p) {
+                 const __grid_constant__ CUtensorMap map_dq, const BwdParams p) {
     using C = BwdCfg<HS>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = smem_raw;
@@ -94,13 +92,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t* kv_full = bars;                   // 1
     uint64_t* q_full = bars + 1;                // [2]
     uint64_t* q_empty = bars + 3;               // [2]
-    uint64_t* s_full = bars + 5;                // S^T and dP^T complete
-    uint64_t* ds_full = bars + 6;               // P^T in TMEM, dS^T in smem (128 arrivals)
+    uint64_t* s_full = bars + 5;                // S^T complete
+    uint64_t* ds_full = bars + 6;               // P^T in TMEM, dS^T in smem (256 arrivals)
     uint64_t* dq_full = bars + 7;               // dV, dK, dQ MMAs of the tile complete
-    uint64_t* dq_empty = bars + 8;              // dQ read out (128 arrivals)
+    uint64_t* dq_empty = bars + 8;              // dQ read out and handed to the TMA unit
     uint64_t* all_done = bars + 9;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
-    volatile uint32_t* softmax_ok = tmem_slot + 1;     // written by one softmax thread, read by all 128
+    uint64_t* dp_full = bars + 10;              // dP^T complete
+    uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+    volatile uint32_t* softmax_ok = tmem_slot + 1;     // [2] written by one softmax thread, read by all 256
+    volatile uint32_t* drain_ok = tmem_slot + 3;       // same idea for the dQ warps
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = p.S / kTile;
@@ -117,15 +117,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             mbar_init(&q_empty[s], 1);
         }
         mbar_init(s_full, 1);
-        mbar_init(ds_full, 128);
+        mbar_init(ds_full, 256);
+        mbar_init(dp_full, 1);
         mbar_init(dq_full, 1);
-        mbar_init(dq_empty, 128);
+        mbar_init(dq_empty, 1);
         mbar_init(all_done, 1);
         fence_barrier_init();
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
         tma_prefetch_desc(&map_do);
+        tma_prefetch_desc(&map_dq);
     }
     if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
     tc_fence_before_sync();
@@ -169,14 +171,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tc_fence_after_sync();
                 const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
                 const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
+                // scores first, on their own barrier: the exponentials start while the previous
+                // tile's dQ is still being read out of the columns dP^T is going to use
 #pragma unroll
                 for (int kk = 0; kk < C::ROWB / 32; ++kk) {
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
                     mma_ss<false>(tmem_base + C::COL_S, smem_desc_sw128(k_addr + off, 16, 1024),
                                   smem_desc_sw128(q_addr + off, 16, 1024), idesc_st, kk > 0);
                 }
-                if (C::DQ_ALIASES_DP && t > 0) {
-                    // dP^T is about to overwrite the columns that still hold the previous dQ
+                mma_commit(s_full);
+                if (t > 0) {
+                    // the previous dQ must be out of its TMEM columns (dP^T re-uses them when the
+                    // head size is 128) and out of the dS^T tile it is staged through (the softmax
+                    // warps rewrite that tile once dP^T is there)
                     if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
                     tc_fence_after_sync();
                 }
@@ -186,22 +193,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     mma_ss<false>(tmem_base + C::COL_DP, smem_desc_sw128(v_addr + off, 16, 1024),
                                   smem_desc_sw128(do_addr + off, 16, 1024), idesc_st, kk > 0);
                 }
-                mma_commit(s_full);
+                mma_commit(dp_full);
                 if (!mbar_wait(ds_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
-                    mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + kk * 8,
+                    mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + (kk / 4) * 64 + (kk % 4) * 8,
                                   smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk) {    // dK += dS^T . Q
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
                     mma_ss<false>(tmem_base + C::COL_DK, smem_desc_sw128(ds_addr + off, 16, 1024),
                                   smem_desc_mn(q_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
-                }
-                if (!C::DQ_ALIASES_DP && t > 0) {
-                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
-                    tc_fence_after_sync();
                 }
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dQ_i = dS . K        (K = 128 key rows)
@@ -212,64 +215,94 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             if (ok) mma_commit(all_done);
         }
-    } else if (warp < 6) {
-        // ---------------- softmax / dS: warps 2..5, thread = key row ----------------
+    } else if (warp < 10) {
+        // ---------------- softmax / dS: warps 2..9 ----------------
+        // thread = (key row r, half h of the 128 query columns); the two warps that share a
+        // TMEM lane group each own 64 columns.
+        const int w = warp - 2;
         const int lane_group = warp & 3;
+        const int half = w >> 2;
         const int r = lane_group * 32 + lane;                       // key row inside the tile
-        const int tid128 = (warp - 2) * 32 + lane;
+        const int tid256 = w * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+        const uint32_t col0 = 64u * half;                           // first query column of this thread
         const float sl2 = p.scale * 1.4426950408889634f;
-        uint8_t* ds_row = ds_smem + r * 128;
+        uint8_t* ds_row = ds_smem + half * kBoxBytes + r * 128;     // box `half` holds query columns 64h..64h+63
         const int swz = r & 7;
         bool ok = true;
         for (int t = 0; t < n_q; ++t) {
             const int i = i_begin + t;
             // Stage lse*log2e and delta of this query tile in the buffer of this tile's parity.
-            // A thread can only get two tiles ahead of another by passing the barrier of the
+            // A thread can only get two tiles ahead of another by passing the barriers of the
             // tile in between, which needs that other thread to have left this tile.
             float* lse_s = stat_s + (t & 1) * 256;
             float* delta_s = lse_s + 128;
             {
-                const int64_t g = (int64_t)row_base + (int64_t)i * kTile + tid128;
-                lse_s[tid128] = p.lse[g] * 1.4426950408889634f;
-                delta_s[tid128] = p.delta[g];
+                const int64_t g = (int64_t)row_base + (int64_t)i * kTile + (tid256 & 127);
+                if (tid256 < 128) lse_s[tid256] = p.lse[g] * 1.4426950408889634f;
+                else delta_s[tid256 - 128] = p.delta[g];
             }
-            // One thread does the bounded wait and publishes the outcome, so that all 128 take
-            // the same branch and nobody is left alone at the named barrier.
-            if (tid128 == 0) *softmax_ok = mbar_wait(s_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
-            named_barrier_sync(1, 128);
-            if (*softmax_ok == 0u) { ok = false; break; }
+            // One thread does each bounded wait and publishes the outcome, so that all 256 take
+            // the same branch and nobody is left alone at a named barrier.
+            if (tid256 == 0) softmax_ok[0] = mbar_wait(s_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
+            named_barrier_sync(1, 256);
+            if (softmax_ok[0] == 0u) { ok = false; break; }
             tc_fence_after_sync();
             const bool diag = p.causal && i == jt;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(tmem_base + C::COL_S + lane_addr + c * 32, sv);
-                tmem_ld32(tmem_base + C::COL_DP + lane_addr + c * 32, dv);
+            // ---- phase A: P^T = exp2(S^T*c - lse) for this thread's 64 columns ----
+            uint32_t ph[32];                                        // 64 probabilities as BF16 pairs
+            {
+                uint32_t s0[32], s1[32];
+                tmem_ld32(tmem_base + C::COL_S + lane_addr + col0, s0);
+                tmem_ld32(tmem_base + C::COL_S + lane_addr + col0 + 32, s1);
                 tmem_wait_ld();
-                uint32_t ph[16], dh[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
-                    const int q0 = c * 32 + x;
-                    float p0 = fast_exp2(fmaf(__uint_as_float(sv[x]), sl2, -lse_s[q0]));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(sv[x + 1]), sl2, -lse_s[q0 + 1]));
+                    const int q0 = col0 + x, q1 = col0 + 32 + x;
+                    float a0 = fast_exp2(fmaf(__uint_as_float(s0[x]), sl2, -lse_s[q0]));
+                    float a1 = fast_exp2(fmaf(__uint_as_float(s0[x + 1]), sl2, -lse_s[q0 + 1]));
+                    float b0 = fast_exp2(fmaf(__uint_as_float(s1[x]), sl2, -lse_s[q1]));
+                    float b1 = fast_exp2(fmaf(__uint_as_float(s1[x + 1]), sl2, -lse_s[q1 + 1]));
                     if (diag) {                      // query q sees key r only when q >= r
-                        if (q0 < r) p0 = 0.f;
-                        if (q0 + 1 < r) p1 = 0.f;
+                        if (q0 < r) a0 = 0.f;
+                        if (q0 + 1 < r) a1 = 0.f;
+                        if (q1 < r) b0 = 0.f;
+                        if (q1 + 1 < r) b1 = 0.f;
                     }
-                    const float d0 = p0 * (__uint_as_float(dv[x]) - delta_s[q0]) * p.scale;
-                    const float d1 = p1 * (__uint_as_float(dv[x + 1]) - delta_s[q0 + 1]) * p.scale;
-                    ph[x >> 1] = pack_bf16(p0, p1);
-                    dh[x >> 1] = pack_bf16(d0, d1);
+                    ph[x >> 1] = pack_bf16(a0, a1);
+                    ph[16 + (x >> 1)] = pack_bf16(b0, b1);
                 }
-                tmem_st16(tmem_base + C::COL_S + lane_addr + c * 16, ph);      // P^T over S^T, 2 per column
-                // dS^T row r, query columns 32c..32c+31: 4 units of 16 bytes in box c/2
-                uint8_t* box = ds_row + (c >> 1) * kBoxBytes;
+                // P^T over this thread's own S^T columns: 64 BF16 = 32 columns starting at col0
+                tmem_st32(tmem_base + C::COL_S + lane_addr + col0, ph);
+            }
+            // ---- phase B: dS^T = P^T * (dP^T - delta) / sqrt(hs) ----
+            if (tid256 == 0) softmax_ok[1] = mbar_wait(dp_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
+            named_barrier_sync(1, 256);
+            if (softmax_ok[1] == 0u) { ok = false; break; }
+            tc_fence_after_sync();
+            {
+                uint32_t d0[32], d1[32];
+                tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0, d0);
+                tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0 + 32, d1);
+                tmem_wait_ld();
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int unit16 = (c & 1) * 4 + u;
-                    *reinterpret_cast<uint4*>(box + ((unit16 ^ swz) << 4)) =
-                        make_uint4(dh[4 * u], dh[4 * u + 1], dh[4 * u + 2], dh[4 * u + 3]);
+                for (int half32 = 0; half32 < 2; ++half32) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {            // one 16-byte unit = 8 query columns
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int x = u * 8 + e * 2;                 // index inside the 32-column chunk
+                            const int q = col0 + half32 * 32 + x;
+                            const uint32_t pk = ph[half32 * 16 + (x >> 1)];
+                            const float p0 = __uint_as_float(pk << 16), p1 = __uint_as_float(pk & 0xffff0000u);
+                            const float dp0 = __uint_as_float(half32 ? d1[x] : d0[x]);
+                            const float dp1 = __uint_as_float(half32 ? d1[x + 1] : d0[x + 1]);
+                            o[e] = pack_bf16(p0 * (dp0 - delta_s[q]) * p.scale, p1 * (dp1 - delta_s[q + 1]) * p.scale);
+                        }
+                        const int unit16 = half32 * 4 + u;
+                        *reinterpret_cast<uint4*>(ds_row + ((unit16 ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
                 }
             }
             tmem_wait_st();
@@ -277,53 +310,72 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             tc_fence_before_sync();
             mbar_arrive(ds_full);
         }
-        // final: dK, dV -> global
+        // final: the first four warps store dV, the other four dK
         if (ok && mbar_wait(all_done, 0, p.status, kTimeoutEpilogue)) {
             tc_fence_after_sync();
             const int64_t grow = (int64_t)row_base + (int64_t)jt * kTile + r;
+            __nv_bfloat16* out = (__nv_bfloat16*)(half ? p.dK : p.dV) + grow * HS;
+            const uint32_t col = half ? C::COL_DK : C::COL_DV;
 #pragma unroll 1
-            for (int which = 0; which < 2; ++which) {
-                __nv_bfloat16* out = (__nv_bfloat16*)(which ? p.dK : p.dV) + grow * HS;
-                const uint32_t col = which ? C::COL_DK : C::COL_DV;
-#pragma unroll 1
-                for (int c = 0; c < HS / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_base + col + lane_addr + c * 32, v);
-                    tmem_wait_ld();
+            for (int c = 0; c < HS / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + col + lane_addr + c * 32, v);
+                tmem_wait_ld();
 #pragma unroll
-                    for (int x = 0; x < 32; x += 8) {
-                        uint4 o;
-                        o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
-                        o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
-                        o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
-                        o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
-                        *reinterpret_cast<uint4*>(out + c * 32 + x) = o;
-                    }
+                for (int x = 0; x < 32; x += 8) {
+                    uint4 o;
+                    o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+                    o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                    o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+                    o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
+                    *reinterpret_cast<uint4*>(out + c * 32 + x) = o;
                 }
             }
         }
     } else {
-        // ---------------- dQ reduction: warps 6..9, thread = query row ----------------
+        // ---------------- dQ reduction: warps 10..13, thread = query row ----------------
+        // The dS^T tile in shared memory is idle between "dV, dK, dQ MMAs complete" and the
+        // next tile's dS^T, so it serves as staging: the dQ tile leaves tensor memory through
+        // it, two 128-row x 128-byte boxes at a time, and one thread hands each pair to the TMA
+        // unit as a reduce-add into the FP32 dQ buffer - full lines, no per-thread atomics.
         const int lane_group = warp & 3;
         const int r = lane_group * 32 + lane;
+        const int tid128 = (warp - 10) * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+        uint8_t* stage_row = ds_smem + r * 128;
+        const int swz = r & 7;
         for (int t = 0; t < n_q; ++t) {
-            if (!mbar_wait(dq_full, t & 1, p.status, kTimeoutOther)) break;
+            if (tid128 == 0) drain_ok[0] = mbar_wait(dq_full, t & 1, p.status, kTimeoutOther) ? 1u : 0u;
+            named_barrier_sync(2, 128);
+            if (drain_ok[0] == 0u) break;
             tc_fence_after_sync();
-            float* dst = p.dq_accum + ((int64_t)row_base + (int64_t)(i_begin + t) * kTile + r) * HS;
+            const int y = row_base + (i_begin + t) * kTile;
 #pragma unroll 1
-            for (int c = 0; c < HS / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + C::COL_DQ + lane_addr + c * 32, v);
-                tmem_wait_ld();
+            for (int pass = 0; pass < HS / 64; ++pass) {
 #pragma unroll
-                for (int x = 0; x < 32; x += 4)
-                    red_add_v4(dst + c * 32 + x, __uint_as_float(v[x]), __uint_as_float(v[x + 1]),
-                               __uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                for (int b = 0; b < 2; ++b) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + C::COL_DQ + lane_addr + (pass * 2 + b) * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        *reinterpret_cast<uint4*>(stage_row + b * kBoxBytes + ((u ^ swz) << 4)) =
+                            make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+                }
+                fence_proxy_async_smem();
+                tc_fence_before_sync();
+                named_barrier_sync(2, 128);                 // both boxes complete
+                if (tid128 == 0) {
+                    tma_reduce_add_2d(&map_dq, ds_smem, (pass * 2) * 32, y);
+                    tma_reduce_add_2d(&map_dq, ds_smem + kBoxBytes, (pass * 2 + 1) * 32, y);
+                    tma_commit_group();
+                    tma_wait_group_read0();                 // staging may be overwritten again
+                    if (pass == HS / 64 - 1) mbar_arrive(dq_empty);   // TMEM columns and staging are free
+                }
+                named_barrier_sync(2, 128);
             }
-            tc_fence_before_sync();
-            mbar_arrive(dq_empty);
         }
+        if (tid128 == 0) tma_wait_group0();                 // all adds have landed before the CTA ends
     }
     tc_fence_before_sync();
     __syncthreads();

@@ -67,12 +67,13 @@ template <int HS>
 int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q, const void* K, const void* V,
                const void* dO, const float* lse, const float* delta, void* dQ, void* dK, void* dV, float* dq_accum) {
     using C = BwdCfg<HS>;
-    CUtensorMap mq, mk, mv, mdo;
+    CUtensorMap mq, mk, mv, mdo, mdq;
     const uint64_t rows = (uint64_t)units * (uint64_t)S;
     if (int rc = make_tensor_map_2d(&mq, Q, 2, rows, HS, HS, kTile, 64)) return rc;
     if (int rc = make_tensor_map_2d(&mk, K, 2, rows, HS, HS, kTile, 64)) return rc;
     if (int rc = make_tensor_map_2d(&mv, V, 2, rows, HS, HS, kTile, 64)) return rc;
     if (int rc = make_tensor_map_2d(&mdo, dO, 2, rows, HS, HS, kTile, 64)) return rc;
+    if (int rc = make_tensor_map_2d(&mdq, dq_accum, 4, rows, HS, HS, kTile, 32)) return rc;   // FP32 reduce-add target
     const size_t n = (size_t)units * (size_t)S * HS;
     BwdParams p;
     p.lse = lse;
@@ -95,7 +96,7 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
         ProfileScope prof("flash_bwd");
         BOATCU_CHECK(cudaMemsetAsync(dq_accum, 0, n * sizeof(float), stream()));
         const int64_t grid = units * (S / kTile);
-        kern<<<(unsigned)grid, kBwdThreads, C::SMEM, stream()>>>(mq, mk, mv, mdo, p);
+        kern<<<(unsigned)grid, kBwdThreads, C::SMEM, stream()>>>(mq, mk, mv, mdo, mdq, p);
         BOATCU_LAUNCH_OK("flash_bwd");
         // the summed FP32 contributions become the BF16 output
         if (int rc = boat_cuda_cast(dQ, BOAT_CUDA_BF16, dq_accum, BOAT_CUDA_F32, (int64_t)n)) return rc;
