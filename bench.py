@@ -236,7 +236,7 @@ def main():
 
     import torch
     import boat_b200
-    from boat_b200 import capi, rng
+    from boat_b200 import capi, rng, shard
     from boat_b200.host import Attention, Tensor, check
 
     lib = boat_b200.load()
@@ -264,8 +264,9 @@ def main():
     T = B * S
 
     # ---- synthetic inputs: X ~ N(0,1) (per-rank slice of the global batch), W ~ N(0, 1/sqrt(d)), dO ~ N(0,1)
-    x_host = rnd(rng.normal(SEED, rng.X, (B, S, d), offset=rank * T * d))
-    g_host = rnd(rng.normal(SEED, rng.DOUT, (B, S, d), offset=rank * T * d))
+    off = shard.element_offset(B * world, S, d, world, rank)
+    x_host = rnd(rng.normal(SEED, rng.X, (B, S, d), offset=off))
+    g_host = rnd(rng.normal(SEED, rng.DOUT, (B, S, d), offset=off))
     w_host = [rnd(rng.normal(SEED, rng.WQ + i, (d, d), 1.0 / np.sqrt(d))) for i in range(4)]
 
     layer = Attention(d, nh, causal=causal, use_bias=True)
