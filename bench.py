@@ -67,7 +67,9 @@ def load_peaks():
 # ---- clocks ----------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    """nvidia-smi sampled every 100 ms; started before the warm-up (the tool takes a moment
+    to start), only the samples between mark() at the start and at the end of the timed
+    region are reported."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
@@ -77,7 +79,7 @@ class ClockSampler:
         self.lines = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -88,7 +90,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def mark(self):
+        """Samples read so far; used to keep only those taken inside the timed region."""
+        return len(self.lines)
+
+    def stop(self, first=0, last=None):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -98,7 +104,8 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        window = self.lines[first:last] if last is not None and last > first else self.lines[first:]
+        for line in window or self.lines[-1:]:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -218,7 +225,7 @@ def workload_config(name, cfg, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -295,10 +302,11 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     sync_all()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    mark0 = sampler.mark() if sampler else 0
     launches0 = lib.boat_cuda_launch_count()
     check(lib.boat_cuda_profile_enable(1), "profile_enable")
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -323,7 +331,7 @@ def main():
     check(lib.boat_cuda_profile_report(report, 8192), "profile_report")
     check(lib.boat_cuda_profile_enable(0), "profile_enable")
     launches = lib.boat_cuda_launch_count() - launches0
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(mark0, sampler.mark()) if sampler else None
 
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
     if dist is not None:

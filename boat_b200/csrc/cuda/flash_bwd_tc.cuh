@@ -87,7 +87,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint8_t* q_smem = v_smem + C::TILE_BYTES;                          // [Q_STAGES]
     uint8_t* do_smem = q_smem + C::Q_STAGES * C::TILE_BYTES;           // [Q_STAGES]
     uint8_t* ds_smem = do_smem + C::Q_STAGES * C::TILE_BYTES;
-    float* stat_s = (float*)(ds_smem + C::DS_BYTES);                   // [2][lse*log2e[128], delta[128]]
+    float* stat_s = (float*)(ds_smem + C::DS_BYTES);                   // [2][-lse*log2e[128], -delta/sqrt(hs)[128]]
     uint64_t* bars = (uint64_t*)(stat_s + 512);
     uint64_t* kv_full = bars;                   // 1
     uint64_t* q_full = bars + 1;                // [2]
@@ -239,8 +239,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             float* delta_s = lse_s + 128;
             {
                 const int64_t g = (int64_t)row_base + (int64_t)i * kTile + (tid256 & 127);
-                if (tid256 < 128) lse_s[tid256] = p.lse[g] * 1.4426950408889634f;
-                else delta_s[tid256 - 128] = p.delta[g];
+                if (tid256 < 128) lse_s[tid256] = -p.lse[g] * 1.4426950408889634f;     // -lse in the log2 domain
+                else delta_s[tid256 - 128] = -p.delta[g] * p.scale;                    // -delta / sqrt(hs)
             }
             // One thread does each bounded wait and publishes the outcome, so that all 256 take
             // the same branch and nobody is left alone at a named barrier.
@@ -257,20 +257,32 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_ld32(tmem_base + C::COL_S + lane_addr + col0 + 32, s1);
                 tmem_wait_ld();
 #pragma unroll
-                for (int x = 0; x < 32; x += 2) {
+                for (int x = 0; x < 32; x += 4) {
+                    // four consecutive query columns from each 32-column chunk; their -lse come
+                    // as one 16-byte shared-memory load (a broadcast: all threads ask for the same)
                     const int q0 = col0 + x, q1 = col0 + 32 + x;
-                    float a0 = fast_exp2(fmaf(__uint_as_float(s0[x]), sl2, -lse_s[q0]));
-                    float a1 = fast_exp2(fmaf(__uint_as_float(s0[x + 1]), sl2, -lse_s[q0 + 1]));
-                    float b0 = fast_exp2(fmaf(__uint_as_float(s1[x]), sl2, -lse_s[q1]));
-                    float b1 = fast_exp2(fmaf(__uint_as_float(s1[x + 1]), sl2, -lse_s[q1 + 1]));
+                    const float4 la = *reinterpret_cast<const float4*>(lse_s + q0);
+                    const float4 lb = *reinterpret_cast<const float4*>(lse_s + q1);
+                    float a[4], b[4];
+                    a[0] = fast_exp2(fmaf(__uint_as_float(s0[x]), sl2, la.x));
+                    a[1] = fast_exp2(fmaf(__uint_as_float(s0[x + 1]), sl2, la.y));
+                    a[2] = fast_exp2(fmaf(__uint_as_float(s0[x + 2]), sl2, la.z));
+                    a[3] = fast_exp2(fmaf(__uint_as_float(s0[x + 3]), sl2, la.w));
+                    b[0] = fast_exp2(fmaf(__uint_as_float(s1[x]), sl2, lb.x));
+                    b[1] = fast_exp2(fmaf(__uint_as_float(s1[x + 1]), sl2, lb.y));
+                    b[2] = fast_exp2(fmaf(__uint_as_float(s1[x + 2]), sl2, lb.z));
+                    b[3] = fast_exp2(fmaf(__uint_as_float(s1[x + 3]), sl2, lb.w));
                     if (diag) {                      // query q sees key r only when q >= r
-                        if (q0 < r) a0 = 0.f;
-                        if (q0 + 1 < r) a1 = 0.f;
-                        if (q1 < r) b0 = 0.f;
-                        if (q1 + 1 < r) b1 = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (q0 + e < r) a[e] = 0.f;
+                            if (q1 + e < r) b[e] = 0.f;
+                        }
                     }
-                    ph[x >> 1] = pack_bf16(a0, a1);
-                    ph[16 + (x >> 1)] = pack_bf16(b0, b1);
+                    ph[x >> 1] = pack_bf16(a[0], a[1]);
+                    ph[(x >> 1) + 1] = pack_bf16(a[2], a[3]);
+                    ph[16 + (x >> 1)] = pack_bf16(b[0], b[1]);
+                    ph[16 + (x >> 1) + 1] = pack_bf16(b[2], b[3]);
                 }
                 // P^T over this thread's own S^T columns: 64 BF16 = 32 columns starting at col0
                 tmem_st32(tmem_base + C::COL_S + lane_addr + col0, ph);
@@ -289,16 +301,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int half32 = 0; half32 < 2; ++half32) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {            // one 16-byte unit = 8 query columns
+                        const int x = u * 8;                                  // index inside the 32-column chunk
+                        const int q = col0 + half32 * 32 + x;
+                        const float4 da = *reinterpret_cast<const float4*>(delta_s + q);
+                        const float4 db = *reinterpret_cast<const float4*>(delta_s + q + 4);
+                        const float nd[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
                         uint32_t o[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int x = u * 8 + e * 2;                 // index inside the 32-column chunk
-                            const int q = col0 + half32 * 32 + x;
-                            const uint32_t pk = ph[half32 * 16 + (x >> 1)];
+                            const uint32_t pk = ph[half32 * 16 + (x >> 1) + e];
                             const float p0 = __uint_as_float(pk << 16), p1 = __uint_as_float(pk & 0xffff0000u);
-                            const float dp0 = __uint_as_float(half32 ? d1[x] : d0[x]);
-                            const float dp1 = __uint_as_float(half32 ? d1[x + 1] : d0[x + 1]);
-                            o[e] = pack_bf16(p0 * (dp0 - delta_s[q]) * p.scale, p1 * (dp1 - delta_s[q + 1]) * p.scale);
+                            const float dp0 = __uint_as_float(half32 ? d1[x + 2 * e] : d0[x + 2 * e]);
+                            const float dp1 = __uint_as_float(half32 ? d1[x + 2 * e + 1] : d0[x + 2 * e + 1]);
+                            // P * (dP - delta) / sqrt(hs), the last two folded into one FMA
+                            o[e] = pack_bf16(p0 * fmaf(dp0, p.scale, nd[2 * e]), p1 * fmaf(dp1, p.scale, nd[2 * e + 1]));
                         }
                         const int unit16 = half32 * 4 + u;
                         *reinterpret_cast<uint4*>(ds_row + ((unit16 ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);

@@ -190,18 +190,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (!mbar_wait(s_full, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
             tc_fence_after_sync();
             const bool diag = p.causal && j == qt;
-            // pass 1: row maximum of the visible scores
+            // pass 1: row maximum of the visible scores (the mask only exists on the diagonal tile)
             float tmax = -FLT_MAX;
 #pragma unroll 1
             for (int c = 0; c < kTile / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld32(tmem_s + lane_addr + c * 32, r);
                 tmem_wait_ld();
+                if (diag) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = __uint_as_float(r[i]);
-                    if (diag && c * 32 + i > r_in_tile) v = -FLT_MAX;
-                    tmax = fmaxf(tmax, v);
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i <= r_in_tile) tmax = fmaxf(tmax, __uint_as_float(r[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        tmax = fmaxf(tmax, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
                 }
             }
             const float m_new = fmaxf(m_ref, tmax);
@@ -236,11 +239,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_ld32(tmem_s + lane_addr + c * 32, r);
                 tmem_wait_ld();
                 float pv[32];
+                if (diag) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float e = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
-                    if (diag && c * 32 + i > r_in_tile) e = 0.f;
-                    pv[i] = e;
+                    for (int i = 0; i < 32; ++i) {
+                        float e = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
+                        pv[i] = (c * 32 + i > r_in_tile) ? 0.f : e;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
                 }
                 if (TF32) {
 #pragma unroll
@@ -257,9 +264,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         __nv_bfloat162 b2 = __floats2bfloat162_rn(pv[2 * i], pv[2 * i + 1]);
-                        // sum what the tensor core will actually multiply: the rounded values
-                        float2 back = __bfloat1622float2(b2);
-                        lsum += back.x + back.y;
+                        lsum += pv[2 * i] + pv[2 * i + 1];
                         h[i] = *reinterpret_cast<uint32_t*>(&b2);
                     }
                     tmem_st16(tmem_s + lane_addr + c * 16, h);
