@@ -378,8 +378,6 @@ def main():
         host_layer.set_precision(mma)
         hx = Tensor.from_numpy(x_host, capi.DEVICE_CPU, bf16=bf16)
         hg = Tensor.from_numpy(g_host, capi.DEVICE_CPU, bf16=bf16)
-        for tns in (hx, hg):
-            lib.boat_cuda_host_register(tns.data_ptr, tns.nbytes)
 
         def host_step():
             out = host_layer.forward(hx, hx, hx)
@@ -409,8 +407,6 @@ def main():
                    d2h_bytes_per_step=4 * T * d * es + wbytes,            # out, dq, dk, dv, parameter gradients
                    note="host BF16 tensors in and out through boat_attention_forward/backward; wall clock" if bf16
                    else "host FP32 tensors in and out through boat_attention_forward/backward; wall clock")
-        for tns in (hx, hg):
-            lib.boat_cuda_host_unregister(tns.data_ptr)
         host_layer.free()
 
     cpu = None

@@ -139,6 +139,8 @@ PROTOTYPES = {
     "boat_cuda_memcpy_d2h": (_I, [_P, _P, _SZ]),
     "boat_cuda_memcpy_d2d": (_I, [_P, _P, _SZ]),
     "boat_cuda_memset": (_I, [_P, _I, _SZ]),
+    "boat_cuda_host_alloc": (_P, [_SZ]),
+    "boat_cuda_host_free": (_I, [_P]),
     "boat_cuda_host_register": (_I, [_P, _SZ]),
     "boat_cuda_host_unregister": (_I, [_P]),
     "boat_cuda_bytes_in_use": (_SZ, []),

@@ -13,7 +13,13 @@ typedef struct {
     boat_device_t device;
     const char* file;
     int line;
+    int pinned;              /* block came from the page-locked pool */
+    int pad_[3];             /* keeps the payload 16-byte aligned */
 } block_header_t;
+
+/* Host blocks of this size and above hold tensor data that will be copied to or from the
+ * GPU; they are taken page-locked (and re-used) when a GPU is present. */
+#define BOAT_PINNED_THRESHOLD ((size_t)256 * 1024)
 
 static boat_memory_stats_t g_stats;
 
@@ -37,7 +43,13 @@ static void note_free(size_t n) {
 
 void* boat_memory_allocate(size_t size, boat_device_t device, const char* file, int line) {
     if (size == 0) return NULL;
-    block_header_t* h = (block_header_t*)malloc(sizeof(block_header_t) + size);
+    block_header_t* h = NULL;
+    int pinned = 0;
+    if (size >= BOAT_PINNED_THRESHOLD && boat_cuda_device_count() > 0) {
+        h = (block_header_t*)boat_cuda_host_alloc(sizeof(block_header_t) + size);
+        pinned = h != NULL;
+    }
+    if (!h) h = (block_header_t*)malloc(sizeof(block_header_t) + size);
     if (!h) {
         fprintf(stderr, "Memory allocation failed: %zu bytes at %s:%d\n", size, file ? file : "?", line);
         return NULL;
@@ -46,6 +58,7 @@ void* boat_memory_allocate(size_t size, boat_device_t device, const char* file, 
     h->device = device;
     h->file = file;
     h->line = line;
+    h->pinned = pinned;
     note_alloc(size);
     return h + 1;
 }
@@ -64,6 +77,14 @@ void* boat_memory_reallocate(void* ptr, size_t new_size, boat_device_t device, c
     }
     block_header_t* old = (block_header_t*)ptr - 1;
     size_t old_size = old->size;
+    if (old->pinned || new_size >= BOAT_PINNED_THRESHOLD) {
+        /* blocks of the page-locked pool cannot be realloc'ed: allocate, copy, free */
+        void* fresh = boat_memory_allocate(new_size, device, file, line);
+        if (!fresh) return NULL;
+        memcpy(fresh, ptr, old_size < new_size ? old_size : new_size);
+        boat_memory_free(ptr);
+        return fresh;
+    }
     block_header_t* h = (block_header_t*)realloc(old, sizeof(block_header_t) + new_size);
     if (!h) return NULL;
     note_free(old_size);
@@ -72,6 +93,7 @@ void* boat_memory_reallocate(void* ptr, size_t new_size, boat_device_t device, c
     h->device = device;
     h->file = file;
     h->line = line;
+    h->pinned = 0;
     return h + 1;
 }
 
@@ -79,7 +101,8 @@ void boat_memory_free(void* ptr) {
     if (!ptr) return;
     block_header_t* h = (block_header_t*)ptr - 1;
     note_free(h->size);
-    free(h);
+    if (h->pinned) boat_cuda_host_free(h);
+    else free(h);
 }
 
 void boat_memory_free_safe(void** ptr_ptr) {

@@ -252,6 +252,44 @@ int boat_cuda_memset(void* dst, int value, size_t bytes) {
     return 0;
 }
 
+// ---- pinned host blocks ---------------------------------------------------------------------
+// Large host tensors are the source and destination of every upload and download of the
+// host-tensor path.  Page-locked memory makes those copies several times faster, but locking
+// pages costs milliseconds per allocation, so freed blocks are kept and handed out again.
+static std::multimap<size_t, void*>* g_pinned_free = nullptr;
+static std::unordered_map<void*, size_t>* g_pinned_size = nullptr;
+
+void* boat_cuda_host_alloc(size_t bytes) {
+    if (bytes == 0 || ensure_init() != 0) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_pinned_free) {
+        g_pinned_free = new std::multimap<size_t, void*>();
+        g_pinned_size = new std::unordered_map<void*, size_t>();
+    }
+    auto it = g_pinned_free->lower_bound(bytes);
+    if (it != g_pinned_free->end() && it->first <= bytes + bytes / 4) {
+        void* p = it->second;
+        g_pinned_free->erase(it);
+        return p;
+    }
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, bytes, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    (*g_pinned_size)[p] = bytes;
+    return p;
+}
+
+int boat_cuda_host_free(void* ptr) {
+    if (!ptr) return 0;
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_pinned_size ? g_pinned_size->find(ptr) : std::unordered_map<void*, size_t>::iterator();
+    if (!g_pinned_size || it == g_pinned_size->end()) return set_error(5, "boat_cuda_host_free: %p is not a pinned block", ptr);
+    g_pinned_free->insert({it->second, ptr});
+    return 0;
+}
+
 int boat_cuda_profile_enable(int on) {
     if (int rc = ensure_init()) return rc;
     if (!g_profile) g_profile = new std::vector<ProfileEntry>();

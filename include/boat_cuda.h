@@ -42,6 +42,8 @@ int         boat_cuda_memcpy_h2d(void* dst, const void* src_host, size_t bytes);
 int         boat_cuda_memcpy_d2h(void* dst_host, const void* src, size_t bytes);  /* returns after arrival */
 int         boat_cuda_memcpy_d2d(void* dst, const void* src, size_t bytes);       /* asynchronous on the stream */
 int         boat_cuda_memset(void* dst, int value, size_t bytes);
+void*       boat_cuda_host_alloc(size_t bytes);          /* page-locked host block from a re-use pool; NULL on failure */
+int         boat_cuda_host_free(void* ptr);              /* back to the pool (never unlocked until exit) */
 int         boat_cuda_host_register(void* host, size_t bytes);   /* pin a caller buffer for fast copies */
 int         boat_cuda_host_unregister(void* host);
 size_t      boat_cuda_bytes_in_use(void);        /* bytes handed out by boat_cuda_malloc and not yet freed */
