@@ -191,3 +191,40 @@ def test_attention_core_large_scores_do_not_overflow(gpu_lib):
     o = do_.numpy((units, S, hs), bf16=True)
     assert np.isfinite(o).all()
     assert rel(o, ref["o"]) <= TOL[capi.MMA_BF16]
+
+
+def test_round_tf32_is_round_to_nearest_on_10_mantissa_bits(gpu_lib):
+    lib = gpu_lib
+    for n in (5, 4096, 100001):
+        x = rng.normal(9, 0, (n,)) * np.float32(3.7)
+        dx, dy = DeviceBuffer.from_numpy(x), DeviceBuffer(n * 4)
+        check(lib.boat_cuda_round_tf32(dy.p, dx.p, n))
+        y = dy.numpy((n,))
+        assert not (y.view(np.uint32) & np.uint32(0x1FFF)).any()          # low 13 mantissa bits are clear
+        assert np.abs(y - x).max() <= np.abs(x).max() * 2.0 ** -11 * 1.0001   # within half a TF32 ulp
+        check(lib.boat_cuda_round_tf32(dx.p, dx.p, n))                     # in place
+        assert np.array_equal(dx.numpy((n,)), y)
+
+
+def test_pinned_host_pool_reuses_blocks(gpu_lib):
+    lib = gpu_lib
+    a = lib.boat_cuda_host_alloc(1 << 20)
+    assert a
+    assert lib.boat_cuda_host_free(a) == 0
+    b = lib.boat_cuda_host_alloc((1 << 20) - 4096)       # close enough in size: the same block comes back
+    assert b == a
+    c = lib.boat_cuda_host_alloc(1 << 20)
+    assert c and c != b
+    assert lib.boat_cuda_host_free(b) == 0 and lib.boat_cuda_host_free(c) == 0
+    assert lib.boat_cuda_host_free(C.c_void_p(12345)) != 0
+
+
+def test_profile_report_lists_kernel_families(gpu_lib):
+    lib = gpu_lib
+    check(lib.boat_cuda_profile_enable(1))
+    run_gemm(lib, capi.MMA_BF16, 0, 0, 256, 256, 256)
+    buf = C.create_string_buffer(4096)
+    check(lib.boat_cuda_profile_report(buf, 4096))
+    check(lib.boat_cuda_profile_enable(0))
+    names = {line.split()[0]: float(line.split()[2]) for line in buf.value.decode().splitlines()}
+    assert "gemm_tc_nn" in names and names["gemm_tc_nn"] > 0
