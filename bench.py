@@ -36,6 +36,8 @@ WORKLOADS = {
     "c3": dict(B=16, S=2048, d=1024, nh=16, causal=True, mma="bf16"),
     "c4": dict(B=4, S=8192, d=2048, nh=16, causal=True, mma="bf16"),
     "target": dict(B=8, S=4096, d=2048, nh=16, causal=True, mma="bf16"),
+    # one batch entry of c4: same kernels and tile shapes, small enough for ncu --set full
+    "c4_small": dict(B=1, S=8192, d=2048, nh=16, causal=True, mma="bf16"),
 }
 DEFAULT_WORKLOAD = "c4"
 SEED = 42
