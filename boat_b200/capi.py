@@ -29,6 +29,12 @@ class AttentionConfig(C.Structure):
                 ("use_rotary", C.c_bool), ("rotary_theta", C.c_float)]
 
 
+class LayerNormConfig(C.Structure):
+    """boat_layernorm_config_t (include/boat/layers/norm.h)."""
+    _fields_ = [("normalized_shape", C.c_size_t), ("eps", C.c_float), ("elementwise_affine", C.c_bool),
+                ("use_bias", C.c_bool)]
+
+
 class MemoryStats(C.Structure):
     """boat_memory_stats_t (include/boat/memory.h)."""
     _fields_ = [("allocated_bytes", C.c_size_t), ("allocated_blocks", C.c_size_t),
@@ -120,7 +126,39 @@ PROTOTYPES = {
     "boat_mul_scalar": (_P, [_P, _D]),
     "boat_matmul": (_P, [_P, _P]),
     "boat_transpose": (_P, [_P, _I, _I]),
+    "boat_gelu": (_P, [_P]),
+    # include/boat/layers/norm.h and the dense / norm entries of include/boat/layers.h
+    "boat_layernorm_create": (_P, [C.POINTER(LayerNormConfig)]),
+    "boat_layernorm_free": (None, [_P]),
+    "boat_layernorm_forward": (_P, [_P, _P]),
+    "boat_layernorm_backward": (_P, [_P, _P]),
+    "boat_layernorm_update": (None, [_P, _F]),
+    "boat_layernorm_set_weight": (None, [_P, _P]),
+    "boat_layernorm_set_bias": (None, [_P, _P]),
+    "boat_dense_layer_create": (_P, [_SZ, _SZ, _B]),
+    "boat_dense_layer_free": (None, [_P]),
+    "boat_dense_layer_forward": (_P, [_P, _P]),
+    "boat_dense_layer_backward": (_P, [_P, _P]),
+    "boat_dense_layer_update": (None, [_P, _F]),
+    "boat_dense_layer_set_weight": (None, [_P, _P]),
+    "boat_dense_layer_set_bias": (None, [_P, _P]),
+    "boat_dense_layer_get_weight": (_P, [_P]),
+    "boat_dense_layer_get_bias": (_P, [_P]),
+    "boat_dense_layer_get_grad_weight": (_P, [_P]),
+    "boat_dense_layer_get_grad_bias": (_P, [_P]),
+    "boat_norm_layer_create": (_P, [_SZ, _F, _B]),
+    "boat_norm_layer_free": (None, [_P]),
+    "boat_norm_layer_forward": (_P, [_P, _P]),
+    "boat_norm_layer_backward": (_P, [_P, _P]),
+    "boat_norm_layer_update": (None, [_P, _F]),
     # include/boat_b200.h
+    "boat_gelu_backward": (_P, [_P, _P]),
+    "boat_layernorm_get_weight": (_P, [_P]),
+    "boat_layernorm_get_bias": (_P, [_P]),
+    "boat_layernorm_get_grad_weight": (_P, [_P]),
+    "boat_layernorm_get_grad_bias": (_P, [_P]),
+    "boat_layernorm_to_device": (_I, [_P, _I]),
+    "boat_dense_layer_to_device": (_I, [_P, _I]),
     "boat_attention_to_device": (_I, [_P, _I]),
     "boat_attention_set_precision": (_I, [_P, _I]),
     "boat_attention_get_precision": (_I, [_P]),
@@ -161,6 +199,10 @@ PROTOTYPES = {
     "boat_cuda_cast": (_I, [_P, _I, _P, _I, _I64]),
     "boat_cuda_round_tf32": (_I, [_P, _P, _I64]),
     "boat_cuda_transpose": (_I, [_P, _P, _I64, _I64, _I64]),
+    "boat_cuda_layernorm_fwd": (_I, [_P, _I, _I64, _I64, _P, _P, _F, _P, _P, _P]),
+    "boat_cuda_layernorm_bwd": (_I, [_P, _P, _I, _I64, _I64, _P, _P, _P, _P, _P, _P]),
+    "boat_cuda_gelu_fwd": (_I, [_P, _P, _I, _I64]),
+    "boat_cuda_gelu_bwd": (_I, [_P, _P, _P, _I, _I64]),
     "boat_cuda_comm_unique_id": (_I, [_P]),
     "boat_cuda_comm_init": (_I, [_I, _I, _P]),
     "boat_cuda_comm_world": (_I, []),

@@ -197,3 +197,36 @@ boat_tensor_t* boat_transpose(const boat_tensor_t* a, int dim0, int dim1) {
     drop(&da);
     return finish(out, &dout, rc, "boat_transpose");
 }
+
+/* ---- GELU (exact erf form).  The reference declares boat_gelu and leaves it a stub returning
+ * NULL (src/ops/activation.c:298-302); FP32 and BF16 tensors, host or device. ---- */
+#include "../core/stage.h"
+#include <boat_b200.h>
+
+static boat_tensor_t* gelu_impl(const boat_tensor_t* x, const boat_tensor_t* grad) {
+    if (!x || !boat_dtype_supported(x->dtype)) return NULL;
+    if (grad && (grad->nelements != x->nelements || grad->dtype != x->dtype)) return NULL;
+    if (boat_report("CUDA start-up", boat_cuda_init(-1)) != 0) return NULL;
+    const int type = boat_storage_of(x->dtype);
+    bool xo = false, go = false;
+    void* dx = boat_stage_in(x, type, &xo);
+    void* dg = grad ? boat_stage_in(grad, type, &go) : NULL;
+    void* dy = boat_dev_alloc(x->nelements * boat_storage_size(type));
+    boat_tensor_t* out = NULL;
+    if (dx && dy && (!grad || dg)) {
+        int rc = grad ? boat_cuda_gelu_bwd(dy, dg, dx, type, (int64_t)x->nelements)
+                      : boat_cuda_gelu_fwd(dy, dx, type, (int64_t)x->nelements);
+        if (boat_report("GELU", rc) == 0) out = boat_emit_out(x->shape, x->ndim, x, dy, type);
+    }
+    boat_dev_free(dy);
+    if (xo) boat_dev_free(dx);
+    if (go) boat_dev_free(dg);
+    return out;
+}
+
+boat_tensor_t* boat_gelu(const boat_tensor_t* a) { return gelu_impl(a, NULL); }
+
+boat_tensor_t* boat_gelu_backward(const boat_tensor_t* grad_output, const boat_tensor_t* input) {
+    if (!grad_output) return NULL;
+    return gelu_impl(input, grad_output);
+}

@@ -26,6 +26,10 @@ BOAT_API void boat_sub_(boat_tensor_t* a, const boat_tensor_t* b);
 
 BOAT_API boat_tensor_t* boat_mul_scalar(const boat_tensor_t* a, double scalar);
 
+/* GELU, exact erf form x/2 (1 + erf(x/sqrt 2)).  A stub returning NULL in the reference
+ * (src/ops/activation.c:298-302); FP32 or BF16 tensors. */
+BOAT_API boat_tensor_t* boat_gelu(const boat_tensor_t* a);
+
 /* 2-D..4-D, leading (batch) dimensions must match exactly (linear.c:32-36). */
 BOAT_API boat_tensor_t* boat_matmul(const boat_tensor_t* a, const boat_tensor_t* b);
 /* Materialised swap of two dimensions. */

@@ -9,6 +9,8 @@
 
 #include "boat/tensor.h"
 #include "boat/layers/attention.h"
+#include "boat/layers/norm.h"
+#include "boat/layers.h"
 #include "boat_cuda.h"
 
 #ifdef __cplusplus
@@ -38,6 +40,17 @@ BOAT_API int boat_attention_grad_bucket(const boat_attention_t* attention, float
  * boat_cuda_comm_init (data-parallel training: every rank holds the same weights and a
  * different slice of the batch).  No-op with a single rank.  Returns 0 on success. */
 BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
+
+/* dx = dy * dGELU/dx(input), the backward of boat_gelu (the reference has neither). */
+BOAT_API boat_tensor_t* boat_gelu_backward(const boat_tensor_t* grad_output, const boat_tensor_t* input);
+
+/* Parameter access and placement for the layers around attention, as for the attention layer. */
+BOAT_API boat_tensor_t* boat_layernorm_get_weight(const boat_layernorm_t* norm);
+BOAT_API boat_tensor_t* boat_layernorm_get_bias(const boat_layernorm_t* norm);
+BOAT_API boat_tensor_t* boat_layernorm_get_grad_weight(const boat_layernorm_t* norm);   /* NULL before backward */
+BOAT_API boat_tensor_t* boat_layernorm_get_grad_bias(const boat_layernorm_t* norm);
+BOAT_API int boat_layernorm_to_device(boat_layernorm_t* norm, boat_device_t device);
+BOAT_API int boat_dense_layer_to_device(boat_dense_layer_t* layer, boat_device_t device);
 
 #ifdef __cplusplus
 }

@@ -134,6 +134,22 @@ int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64
 int boat_cuda_round_tf32(float* y, const float* x, int64_t n);
 int boat_cuda_transpose(float* out, const float* in, int64_t batch, int64_t rows, int64_t cols);
 
+/* ---- LayerNorm and GELU (the pre-LN encoder block around the attention layer) --------------
+ * layernorm_fwd: per row of [rows, cols]: y = (x - mean) / sqrt(var + eps) * gamma + beta with
+ *   the biased variance - boat_layernorm_forward, src/layers/norm.c:231-317.  gamma/beta FP32
+ *   or NULL; mean_out / rstd_out [rows] FP32 (or NULL) are what the backward needs.
+ * layernorm_bwd: dx, and dgamma / dbeta [cols] FP32 (overwritten; NULL to skip).  The
+ *   reference's backward is a stub (norm.c:397-402); this is the analytic gradient.
+ * gelu_fwd / gelu_bwd: y = x/2 (1 + erf(x/sqrt 2)), dx = dy * dGELU(x).  The reference's
+ *   boat_gelu is a stub (src/ops/activation.c:298-302); the exact erf form is used. */
+int boat_cuda_layernorm_fwd(const void* x, int type, int64_t rows, int64_t cols, const float* gamma,
+                            const float* beta, float eps, void* y, float* mean_out, float* rstd_out);
+int boat_cuda_layernorm_bwd(const void* dy, const void* x, int type, int64_t rows, int64_t cols,
+                            const float* gamma, const float* mean, const float* rstd,
+                            void* dx, float* dgamma, float* dbeta);
+int boat_cuda_gelu_fwd(void* y, const void* x, int type, int64_t n);
+int boat_cuda_gelu_bwd(void* dx, const void* dy, const void* x, int type, int64_t n);
+
 /* ---- gradient exchange between GPUs (nothing in the reference: it is single-process) ---
  * One process per GPU.  Rank 0 makes an id (128 bytes) and hands it to the others by any
  * host channel; every rank then calls comm_init.  allreduce sums an FP32 buffer in place

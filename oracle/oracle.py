@@ -280,3 +280,147 @@ def ref_step(q, k, v, w, b, dout, nh, causal):
         return layer.step(q, k, v, dout)
     finally:
         layer.free()
+
+
+# ---- layers around attention (block_oracle.c) --------------------------------------------------------
+
+def _block():
+    lib = port()
+    if not getattr(lib, "_block_typed", False):
+        I64, F = C.c_int64, C.c_float
+        lib.oracle_layernorm_forward.argtypes = [_FP, I64, I64, _FP, _FP, F, _FP]
+        lib.oracle_layernorm_backward.argtypes = [_FP, _FP, I64, I64, _FP, F, _FP, _FP, _FP]
+        lib.oracle_gelu_forward.argtypes = [_FP, _FP, I64]
+        lib.oracle_gelu_backward.argtypes = [_FP, _FP, _FP, I64]
+        lib.oracle_dense_forward.argtypes = [_FP, _FP, _FP, _FP, I64, I64, I64]
+        lib.oracle_dense_backward.argtypes = [_FP, _FP, _FP, _FP, _FP, _FP, I64, I64, I64]
+        lib.oracle_dense_backward.restype = C.c_int
+        lib._block_typed = True
+    return lib
+
+
+def port_layernorm(x, w, b, eps):
+    x = _f32(x)
+    H = x.shape[-1]
+    y = np.empty_like(x)
+    w = _f32(w) if w is not None else None
+    b = _f32(b) if b is not None else None
+    _block().oracle_layernorm_forward(_fp(x), x.size // H, H, _fp(w), _fp(b), float(eps), _fp(y))
+    return y
+
+
+def port_layernorm_backward(dy, x, w, eps):
+    dy, x = _f32(dy), _f32(x)
+    H = x.shape[-1]
+    w = _f32(w) if w is not None else None
+    dx, dg, db = np.empty_like(x), np.empty(H, np.float32), np.empty(H, np.float32)
+    _block().oracle_layernorm_backward(_fp(dy), _fp(x), x.size // H, H, _fp(w), float(eps), _fp(dx), _fp(dg), _fp(db))
+    return dx, dg, db
+
+
+def port_gelu(x):
+    x = _f32(x)
+    y = np.empty_like(x)
+    _block().oracle_gelu_forward(_fp(x), _fp(y), x.size)
+    return y
+
+
+def port_gelu_backward(dy, x):
+    dy, x = _f32(dy), _f32(x)
+    dx = np.empty_like(x)
+    _block().oracle_gelu_backward(_fp(dy), _fp(x), _fp(dx), x.size)
+    return dx
+
+
+def port_dense(x, w, b):
+    x, w = _f32(x), _f32(w)
+    b = _f32(b) if b is not None else None
+    N, I = x.shape
+    O = w.shape[1]
+    y = np.empty((N, O), np.float32)
+    _block().oracle_dense_forward(_fp(x), _fp(w), _fp(b), _fp(y), N, I, O)
+    return y
+
+
+def port_dense_backward(x, w, dy, dw_acc=None, db_acc=None, bias=True):
+    """Returns dx, dw, db where dw/db are the accumulators after adding this call's gradients."""
+    x, w, dy = _f32(x), _f32(w), _f32(dy)
+    N, I = x.shape
+    O = w.shape[1]
+    dx = np.empty((N, I), np.float32)
+    dw = np.zeros((I, O), np.float32) if dw_acc is None else _f32(dw_acc).copy()
+    db = (np.zeros(O, np.float32) if db_acc is None else _f32(db_acc).copy()) if bias else None
+    if _block().oracle_dense_backward(_fp(x), _fp(w), _fp(dy), _fp(dx), _fp(dw), _fp(db), N, I, O):
+        raise MemoryError
+    return dx, dw, db
+
+
+class _RefLNConfig(C.Structure):
+    _fields_ = [("normalized_shape", C.c_size_t), ("eps", C.c_float), ("elementwise_affine", C.c_bool),
+                ("use_bias", C.c_bool)]
+
+
+def ref_layernorm(x, w, b, eps):
+    """boat_layernorm_forward of the reference library itself (weights set in place)."""
+    lib = ref()
+    P = C.c_void_p
+    lib.boat_layernorm_create.restype = P
+    lib.boat_layernorm_create.argtypes = [C.POINTER(_RefLNConfig)]
+    lib.boat_layernorm_forward.restype = P
+    lib.boat_layernorm_forward.argtypes = [P, P]
+    lib.boat_layernorm_free.argtypes = [P]
+    x = _f32(x)
+    H = x.shape[-1]
+    cfg = _RefLNConfig(H, eps, w is not None, b is not None)
+    layer = lib.boat_layernorm_create(C.byref(cfg))
+    # the layer struct starts with the config, then weight and bias tensor pointers
+    base = C.cast(layer, C.POINTER(C.c_void_p))
+    off = (C.sizeof(_RefLNConfig) + 7) // 8
+    if w is not None:
+        RefTensor(lib, base[off]).view()[:] = _f32(w)
+    if b is not None:
+        RefTensor(lib, base[off + 1]).view()[:] = _f32(b)
+    hx = _ref_new(lib, x)
+    hy = lib.boat_layernorm_forward(layer, hx)
+    y = RefTensor(lib, hy).view(x.shape).copy()
+    lib.boat_tensor_unref(hy)
+    lib.boat_tensor_unref(hx)
+    lib.boat_layernorm_free(layer)
+    return y
+
+
+def ref_dense_step(x, w, b, dy, repeats=1):
+    """Reference dense layer: forward, then `repeats` backward calls (gradients accumulate)."""
+    lib = ref()
+    P = C.c_void_p
+    lib.boat_dense_layer_create.restype = P
+    lib.boat_dense_layer_create.argtypes = [C.c_size_t, C.c_size_t, C.c_bool]
+    lib.boat_dense_layer_forward.restype = P
+    lib.boat_dense_layer_forward.argtypes = [P, P]
+    lib.boat_dense_layer_backward.restype = P
+    lib.boat_dense_layer_backward.argtypes = [P, P]
+    lib.boat_dense_layer_free.argtypes = [P]
+    for name in ("weight", "bias", "grad_weight", "grad_bias"):
+        fn = getattr(lib, "boat_dense_layer_get_" + name)
+        fn.restype = P
+        fn.argtypes = [P]
+    x, w, dy = _f32(x), _f32(w), _f32(dy)
+    N, I = x.shape
+    O = w.shape[1]
+    layer = lib.boat_dense_layer_create(I, O, b is not None)
+    RefTensor(lib, lib.boat_dense_layer_get_weight(layer)).view()[:] = w.ravel()
+    if b is not None:
+        RefTensor(lib, lib.boat_dense_layer_get_bias(layer)).view()[:] = _f32(b)
+    hx, hg = _ref_new(lib, x), _ref_new(lib, dy)
+    hy = lib.boat_dense_layer_forward(layer, hx)
+    res = {"y": RefTensor(lib, hy).view((N, O)).copy()}
+    for _ in range(repeats):
+        hdx = lib.boat_dense_layer_backward(layer, hg)
+        res["dx"] = RefTensor(lib, hdx).view((N, I)).copy()
+        lib.boat_tensor_unref(hdx)
+    res["dw"] = RefTensor(lib, lib.boat_dense_layer_get_grad_weight(layer)).view((I, O)).copy()
+    res["db"] = RefTensor(lib, lib.boat_dense_layer_get_grad_bias(layer)).view((O,)).copy() if b is not None else None
+    for h in (hy, hx, hg):
+        lib.boat_tensor_unref(h)
+    lib.boat_dense_layer_free(layer)
+    return res

@@ -93,3 +93,18 @@ def errors(res, ref):
         diff = float(np.abs(a - r64).max())
         out[key] = diff / denom if denom > 0 else diff
     return out
+
+
+# ---- layers around attention: seeded inputs for the golden vectors and tests --------------------------
+
+def layernorm_inputs(rows_shape=(3, 7), H=48):
+    x = rng.normal(SEED, 20, rows_shape + (H,)) * np.float32(1.7) + np.float32(0.3)
+    w = rng.normal(SEED, 21, (H,), 0.5) + np.float32(1.0)
+    b = rng.normal(SEED, 22, (H,), 0.2)
+    dy = rng.normal(SEED, 23, rows_shape + (H,))
+    return dict(x=x, w=w, b=b, dy=dy, eps=1e-5)
+
+
+def dense_inputs(N=19, I=24, O=40):
+    return dict(x=rng.normal(SEED, 30, (N, I)), w=rng.normal(SEED, 31, (I, O), 0.2), b=rng.normal(SEED, 32, (O,), 0.1),
+                dy=rng.normal(SEED, 33, (N, O)))

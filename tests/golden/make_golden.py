@@ -5,6 +5,9 @@ oracle/_ref/libboat_ref.so from it):
 
     python tests/golden/make_golden.py
 
+Also stored: the reference's boat_layernorm_forward and its dense layer (forward, two
+accumulating backward calls) on the seeded inputs of tests/cases.py.
+
 For every case in tests/cases.py::GOLDEN_CASES the reference's own boat_attention_forward
 and boat_attention_backward are executed on the seeded inputs and every output and gradient
 is stored (FP32, bit patterns as the reference produced them), together with a checksum of
@@ -45,6 +48,15 @@ def main():
             out["%s/%s" % (case.name, key)] = val
         out["%s/digest" % case.name] = np.frombuffer(input_digest(inp).encode(), dtype=np.uint8)
         print(case.name, "ok")
+    # layers around attention that the reference implements: LayerNorm forward, dense forward/backward
+    ln = cases.layernorm_inputs()
+    out["layernorm/y"] = oracle.ref_layernorm(ln["x"], ln["w"], ln["b"], ln["eps"])
+    out["layernorm/y_plain"] = oracle.ref_layernorm(ln["x"], None, None, ln["eps"])
+    de = cases.dense_inputs()
+    res = oracle.ref_dense_step(de["x"], de["w"], de["b"], de["dy"], repeats=2)
+    for key in ("y", "dx", "dw", "db"):
+        out["dense/" + key] = res[key]
+    print("layernorm, dense ok")
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "attention_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -1,0 +1,265 @@
+"""GPU tests of the layers the encoder block puts around attention - LayerNorm, dense, GELU -
+through the C ABI, and of one composed pre-LN block training step
+(LN -> attention -> +x -> LN -> dense 4d -> GELU -> dense d -> +, MSE loss).
+
+LayerNorm forward and the dense layer are pinned by the reference (golden vectors); LayerNorm
+backward, GELU and the composition have no reference implementation (stubs there), so they
+are checked against the CPU restatement, which the CPU tests verify by finite differences."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+from boat_b200 import capi, rng
+from boat_b200.host import Attention, Tensor
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32, TOL_BF16 = 1e-5, 2e-2
+
+
+def rel(a, ref):
+    ref = np.asarray(ref, np.float64)
+    return float(np.abs(np.asarray(a, np.float64) - ref).max() / np.abs(ref).max())
+
+
+class LayerNorm:
+    def __init__(self, lib, H, eps, w=None, b=None, device=capi.DEVICE_CPU):
+        self.lib = lib
+        cfg = capi.LayerNormConfig(H, eps, w is not None, b is not None)
+        self.h = C.c_void_p(lib.boat_layernorm_create(C.byref(cfg)))
+        assert self.h.value
+        if w is not None:
+            Tensor(lib.boat_layernorm_get_weight(self.h), own=False).set(w)
+        if b is not None:
+            Tensor(lib.boat_layernorm_get_bias(self.h), own=False).set(b)
+        if device == capi.DEVICE_CUDA:
+            assert lib.boat_layernorm_to_device(self.h, device) == 0
+
+    def forward(self, x):
+        return Tensor(self.lib.boat_layernorm_forward(self.h, x.h))
+
+    def backward(self, g):
+        return Tensor(self.lib.boat_layernorm_backward(self.h, g.h))
+
+    def grads(self):
+        gw, gb = self.lib.boat_layernorm_get_grad_weight(self.h), self.lib.boat_layernorm_get_grad_bias(self.h)
+        return (Tensor(gw, own=False).numpy() if gw else None, Tensor(gb, own=False).numpy() if gb else None)
+
+    def free(self):
+        self.lib.boat_layernorm_free(self.h)
+
+
+class Dense:
+    def __init__(self, lib, I, O, w, b, device=capi.DEVICE_CPU):
+        self.lib = lib
+        self.h = C.c_void_p(lib.boat_dense_layer_create(I, O, b is not None))
+        assert self.h.value
+        Tensor(lib.boat_dense_layer_get_weight(self.h), own=False).set(w)
+        if b is not None:
+            Tensor(lib.boat_dense_layer_get_bias(self.h), own=False).set(b)
+        if device == capi.DEVICE_CUDA:
+            assert lib.boat_dense_layer_to_device(self.h, device) == 0
+
+    def forward(self, x):
+        return Tensor(self.lib.boat_dense_layer_forward(self.h, x.h))
+
+    def backward(self, g):
+        return Tensor(self.lib.boat_dense_layer_backward(self.h, g.h))
+
+    def grads(self):
+        gb = self.lib.boat_dense_layer_get_grad_bias(self.h)
+        return (Tensor(self.lib.boat_dense_layer_get_grad_weight(self.h), own=False).numpy(),
+                Tensor(gb, own=False).numpy() if gb else None)
+
+    def free(self):
+        self.lib.boat_dense_layer_free(self.h)
+
+
+@pytest.mark.parametrize("device", [capi.DEVICE_CPU, capi.DEVICE_CUDA], ids=["host_tensors", "cuda_tensors"])
+def test_layernorm_forward_matches_reference_golden(gpu_lib, golden, device):
+    ln = cases.layernorm_inputs()
+    layer = LayerNorm(gpu_lib, 48, ln["eps"], ln["w"], ln["b"], device)
+    y = layer.forward(Tensor.from_numpy(ln["x"], device))
+    assert y.shape == ln["x"].shape and y.device == device
+    assert rel(y.numpy(), golden["layernorm/y"]) <= TOL_FP32
+    layer.free()
+    plain = LayerNorm(gpu_lib, 48, ln["eps"])
+    assert rel(plain.forward(Tensor.from_numpy(ln["x"], device)).numpy(), golden["layernorm/y_plain"]) <= TOL_FP32
+    plain.free()
+
+
+@pytest.mark.parametrize("shape", [((3, 7), 48), ((5,), 1000), ((2, 130), 1024), ((1,), 7)])
+def test_layernorm_backward_matches_restatement(gpu_lib, shape):
+    rows_shape, H = shape
+    ln = cases.layernorm_inputs(rows_shape, H)
+    layer = LayerNorm(gpu_lib, H, ln["eps"], ln["w"], ln["b"], capi.DEVICE_CUDA)
+    layer.forward(Tensor.from_numpy(ln["x"], capi.DEVICE_CUDA))
+    dx = layer.backward(Tensor.from_numpy(ln["dy"], capi.DEVICE_CUDA)).numpy()
+    rdx, rdg, rdb = oracle.port_layernorm_backward(ln["dy"], ln["x"], ln["w"], ln["eps"])
+    gw, gb = layer.grads()
+    assert rel(dx, rdx) <= 2e-5 and rel(gw, rdg) <= 2e-5 and rel(gb, rdb) <= 2e-5
+    layer.free()
+
+
+def test_layernorm_bf16_storage(gpu_lib):
+    ln = cases.layernorm_inputs((4, 64), 256)
+    x, dy = rng.bf16_round(ln["x"]), rng.bf16_round(ln["dy"])
+    layer = LayerNorm(gpu_lib, 256, ln["eps"], ln["w"], ln["b"], capi.DEVICE_CUDA)
+    y = layer.forward(Tensor.from_numpy(x, capi.DEVICE_CUDA, bf16=True)).numpy()
+    dx = layer.backward(Tensor.from_numpy(dy, capi.DEVICE_CUDA, bf16=True)).numpy()
+    assert rel(y, oracle.port_layernorm(x, ln["w"], ln["b"], ln["eps"])) <= TOL_BF16
+    assert rel(dx, oracle.port_layernorm_backward(dy, x, ln["w"], ln["eps"])[0]) <= TOL_BF16
+    layer.free()
+
+
+@pytest.mark.parametrize("device", [capi.DEVICE_CPU, capi.DEVICE_CUDA], ids=["host_tensors", "cuda_tensors"])
+def test_dense_layer_matches_reference_golden_including_accumulation(gpu_lib, golden, device):
+    de = cases.dense_inputs()
+    layer = Dense(gpu_lib, 24, 40, de["w"], de["b"], device)
+    x, g = Tensor.from_numpy(de["x"], device), Tensor.from_numpy(de["dy"], device)
+    assert rel(layer.forward(x).numpy(), golden["dense/y"]) <= TOL_FP32
+    layer.backward(g)
+    dx = layer.backward(g).numpy()                       # second call: gradients accumulate
+    dw, db = layer.grads()
+    assert rel(dx, golden["dense/dx"]) <= TOL_FP32
+    assert rel(dw, golden["dense/dw"]) <= TOL_FP32 and rel(db, golden["dense/db"]) <= TOL_FP32
+    gpu_lib.boat_dense_layer_update(layer.h, C.c_float(0.1))
+    dw2, db2 = layer.grads()
+    assert not dw2.any() and not db2.any()               # update clears the gradients (dense.c:312-313)
+    w_after = Tensor(gpu_lib.boat_dense_layer_get_weight(layer.h), own=False).numpy()
+    assert np.array_equal(w_after, de["w"] - np.float32(0.1) * dw)
+    bad = Tensor.from_numpy(np.zeros((2, 3, 24), np.float32), device)
+    assert not gpu_lib.boat_dense_layer_forward(layer.h, bad.h)          # 2-D input only, as the reference
+    layer.free()
+
+
+def test_dense_layer_bf16_tensor_cores(gpu_lib):
+    N, I, O = 512, 256, 1024
+    x, w = rng.bf16_round(rng.normal(5, 0, (N, I))), rng.bf16_round(rng.normal(5, 1, (I, O), 1 / 16.0))
+    b, g = rng.normal(5, 2, (O,), 0.1), rng.bf16_round(rng.normal(5, 3, (N, O)))
+    layer = Dense(gpu_lib, I, O, w, b, capi.DEVICE_CUDA)
+    y = layer.forward(Tensor.from_numpy(x, capi.DEVICE_CUDA, bf16=True)).numpy()
+    dx = layer.backward(Tensor.from_numpy(g, capi.DEVICE_CUDA, bf16=True)).numpy()
+    dw, db = layer.grads()
+    x64, w64, g64 = x.astype(np.float64), w.astype(np.float64), g.astype(np.float64)
+    assert rel(y, x64 @ w64 + b) <= TOL_BF16 and rel(dx, g64 @ w64.T) <= TOL_BF16
+    assert rel(dw, x64.T @ g64) <= TOL_BF16 and rel(db, g64.sum(0)) <= TOL_BF16
+    layer.free()
+
+
+@pytest.mark.parametrize("bf16", [False, True], ids=["fp32", "bf16"])
+def test_gelu_forward_and_backward(gpu_lib, bf16):
+    f = rng.bf16_round if bf16 else (lambda a: a)
+    for n in (1, 37, 4096, 100003):
+        x, dy = f(rng.normal(6, 0, (n,)) * np.float32(2.5)), f(rng.normal(6, 1, (n,)))
+        tx, tg = Tensor.from_numpy(x, capi.DEVICE_CUDA, bf16=bf16), Tensor.from_numpy(dy, capi.DEVICE_CUDA, bf16=bf16)
+        y = Tensor(gpu_lib.boat_gelu(tx.h)).numpy()
+        dx = Tensor(gpu_lib.boat_gelu_backward(tg.h, tx.h)).numpy()
+        tol = 1e-2 if bf16 else 1e-5
+        assert np.abs(y - oracle.port_gelu(x)).max() <= tol * max(1.0, np.abs(x).max())
+        assert np.abs(dx - oracle.port_gelu_backward(dy, x)).max() <= tol * max(1.0, np.abs(dy).max())
+
+
+def block_reference(inp, nh, causal):
+    """The pre-LN encoder block training step on the CPU restatement (FP32 storage, the
+    unpinned pieces in double inside)."""
+    x, t = inp["x"], inp["target"]
+    B, S, d = x.shape
+    T = B * S
+    h1 = oracle.port_layernorm(x, inp["g1"], inp["b1"], 1e-5)
+    att = oracle.port_step(h1, h1, h1, inp["w"], inp["b"], None, nh, causal)["out"]
+    r1 = x + att
+    h2 = oracle.port_layernorm(r1, inp["g2"], inp["b2"], 1e-5)
+    u = oracle.port_dense(h2.reshape(T, d), inp["w1"], inp["c1"])
+    a = oracle.port_gelu(u)
+    m = oracle.port_dense(a, inp["w2"], inp["c2"]).reshape(B, S, d)
+    out = r1 + m
+    dout = (np.float32(2.0) * (out - t) / np.float32(out.size)).astype(np.float32)        # MSE gradient
+    da, dw2, dc2 = oracle.port_dense_backward(a, inp["w2"], dout.reshape(T, d))
+    du = oracle.port_gelu_backward(da, u)
+    dh2, dw1, dc1 = oracle.port_dense_backward(h2.reshape(T, d), inp["w1"], du)
+    dr1_ln, dg2, db2 = oracle.port_layernorm_backward(dh2.reshape(B, S, d), r1, inp["g2"], 1e-5)
+    dr1 = dout + dr1_ln
+    ab = oracle.port_step(h1, h1, h1, inp["w"], inp["b"], dr1, nh, causal)
+    dh1 = ab["dq"] + ab["dk"] + ab["dv"]
+    dx_ln, dg1, db1 = oracle.port_layernorm_backward(dh1, x, inp["g1"], 1e-5)
+    return dict(out=out, dx=dr1 + dx_ln, dw1=dw1, dw2=dw2, dc1=dc1, dc2=dc2, dg1=dg1, dg2=dg2, db1=db1, db2=db2,
+                dwq=ab["dw"][0], dwo=ab["dw"][3], loss=float(((out - t).astype(np.float64) ** 2).mean()))
+
+
+def block_gpu(lib, inp, nh, causal, bf16):
+    dev = capi.DEVICE_CUDA
+    x_np, t_np = inp["x"], inp["target"]
+    B, S, d = x_np.shape
+    T = B * S
+    ln1, ln2 = LayerNorm(lib, d, 1e-5, inp["g1"], inp["b1"], dev), LayerNorm(lib, d, 1e-5, inp["g2"], inp["b2"], dev)
+    fc1, fc2 = Dense(lib, d, 4 * d, inp["w1"], inp["c1"], dev), Dense(lib, 4 * d, d, inp["w2"], inp["c2"], dev)
+    attn = Attention(d, nh, causal=causal)
+    for i, p in enumerate("qkvo"):
+        attn.param("weight_" + p).set(inp["w"][i])
+        attn.param("bias_" + p).set(inp["b"][i])
+    attn.to_device(dev)
+    attn.set_precision(capi.MMA_BF16 if bf16 else capi.MMA_FP32)
+
+    def reshape(t, shape):
+        arr = (C.c_int64 * len(shape))(*shape)
+        return Tensor(lib.boat_tensor_reshape(t.h, arr, len(shape)))
+
+    def add(a, b):
+        return Tensor(lib.boat_add(a.h, b.h)) if not bf16 else Tensor.from_numpy(a.numpy() + b.numpy(), dev, bf16=True)
+
+    x = Tensor.from_numpy(x_np, dev, bf16=bf16)
+    h1 = ln1.forward(x)
+    att = attn.forward(h1)
+    r1 = add(x, att)
+    h2 = ln2.forward(r1)
+    u = fc1.forward(reshape(h2, (T, d)))
+    a = Tensor(lib.boat_gelu(u.h))
+    m = reshape(fc2.forward(a), (B, S, d))
+    out = add(r1, m)
+    out_np = out.numpy()
+    dout_np = (np.float32(2.0) * (out_np - t_np) / np.float32(out_np.size)).astype(np.float32)
+    dout = Tensor.from_numpy(dout_np, dev, bf16=bf16)
+    da = fc2.backward(reshape(dout, (T, d)))
+    du = Tensor(lib.boat_gelu_backward(da.h, u.h))
+    dh2 = fc1.backward(du)
+    dr1_ln = ln2.backward(reshape(dh2, (B, S, d)))
+    dr1 = add(dout, dr1_ln)
+    gq, gk, gv = attn.backward(dr1)
+    dh1 = add(add(gq, gk), gv)
+    dx_ln = ln1.backward(dh1)
+    dx = add(dr1, dx_ln)
+    res = dict(out=out_np, dx=dx.numpy(), dw1=fc1.grads()[0], dc1=fc1.grads()[1], dw2=fc2.grads()[0], dc2=fc2.grads()[1],
+               dg1=ln1.grads()[0], db1=ln1.grads()[1], dg2=ln2.grads()[0], db2=ln2.grads()[1],
+               dwq=attn.param("grad_weight_q").numpy(), dwo=attn.param("grad_weight_o").numpy(),
+               loss=float(((out_np - t_np).astype(np.float64) ** 2).mean()))
+    for layer in (ln1, ln2, fc1, fc2, attn):
+        layer.free()
+    return res
+
+
+def block_inputs(B, S, d, bf16):
+    f = rng.bf16_round if bf16 else (lambda a: a)
+    n = lambda tid, shape, std: f(rng.normal(77, tid, shape, std))
+    return dict(x=n(0, (B, S, d), 1.0), target=rng.normal(77, 1, (B, S, d), 1.0),
+                w=[n(2 + i, (d, d), 0.02 * 8) for i in range(4)], b=[rng.normal(77, 6 + i, (d,), 0.05) for i in range(4)],
+                g1=rng.normal(77, 10, (d,), 0.1) + 1, b1=rng.normal(77, 11, (d,), 0.1),
+                g2=rng.normal(77, 12, (d,), 0.1) + 1, b2=rng.normal(77, 13, (d,), 0.1),
+                w1=n(14, (d, 4 * d), 0.02 * 8), c1=rng.normal(77, 15, (4 * d,), 0.05),
+                w2=n(16, (4 * d, d), 0.02 * 8), c2=rng.normal(77, 17, (d,), 0.05))
+
+
+# BF16: every tensor that crosses a layer boundary is stored in BF16 (a dozen roundings between
+# the input and dx), so the composed step is held to 3x the per-layer BF16 tolerance.
+@pytest.mark.parametrize("bf16,B,S,d,nh,tol", [(False, 2, 24, 32, 4, 2e-5), (True, 2, 256, 256, 4, 6e-2)], ids=["fp32", "bf16"])
+def test_pre_ln_encoder_block_training_step(gpu_lib, bf16, B, S, d, nh, tol):
+    inp = block_inputs(B, S, d, bf16)
+    ref = block_reference(inp, nh, False)
+    got = block_gpu(gpu_lib, inp, nh, False, bf16)
+    assert abs(got["loss"] - ref["loss"]) <= tol * ref["loss"]
+    worst = {k: rel(got[k], ref[k]) for k in ref if k != "loss"}
+    bad = {k: v for k, v in worst.items() if v > tol}
+    assert not bad, (bad, worst)
