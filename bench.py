@@ -36,6 +36,8 @@ WORKLOADS = {
     "c3": dict(B=16, S=2048, d=1024, nh=16, causal=True, mma="bf16"),
     "c4": dict(B=4, S=8192, d=2048, nh=16, causal=True, mma="bf16"),
     "target": dict(B=8, S=4096, d=2048, nh=16, causal=True, mma="bf16"),
+    # config 5: full pre-LN encoder block step (LN, attention, residual, LN, dense 4d, GELU, dense, residual, MSE)
+    "c5": dict(B=32, S=1024, d=1024, nh=16, causal=False, mma="bf16", block=True),
     # one batch entry of c4: same kernels and tile shapes, small enough for ncu --set full
     "c4_small": dict(B=1, S=8192, d=2048, nh=16, causal=True, mma="bf16"),
 }
@@ -48,6 +50,12 @@ def algorithmic_flops(B, S, d, causal):
     attention core (c = 1/2 when causal); recomputation inside the backward is not counted."""
     T = B * S
     return 24.0 * T * d * d + 12.0 * (0.5 if causal else 1.0) * B * S * S * d
+
+
+def block_flops(B, S, d, causal):
+    """Attention step plus the MLP: two GEMMs of T x d x 4d forward (16*T*d^2) and their input and
+    weight gradients (32*T*d^2).  LayerNorm, GELU and the residual adds are not counted."""
+    return algorithmic_flops(B, S, d, causal) + 48.0 * B * S * d * d
 
 
 def reference_flops(B, S, d):
@@ -278,18 +286,38 @@ def main():
     g_host = rnd(rng.normal(SEED, rng.DOUT, (B, S, d), offset=off))
     w_host = [rnd(rng.normal(SEED, rng.WQ + i, (d, d), 1.0 / np.sqrt(d))) for i in range(4)]
 
-    layer = Attention(d, nh, causal=causal, use_bias=True)
-    for i, p in enumerate("qkvo"):
-        layer.param("weight_" + p).set(w_host[i])
-    layer.to_device(capi.DEVICE_CUDA)
-    layer.set_precision(mma)
+    is_block = bool(cfg.get("block"))
+    block = None
+    if is_block:
+        from boat_b200.host import EncoderBlock
+        std = 0.02
+        params = dict(w=[rnd(rng.normal(SEED, rng.WQ + i, (d, d), std)) for i in range(4)],
+                      w1=rnd(rng.normal(SEED, 40, (d, 4 * d), std)), w2=rnd(rng.normal(SEED, 41, (4 * d, d), std)))
+        block = EncoderBlock(d, nh, causal=causal, device=capi.DEVICE_CUDA, mma=mma, params=params)
+        layer = block.attn
+    else:
+        layer = Attention(d, nh, causal=causal, use_bias=True)
+        for i, p in enumerate("qkvo"):
+            layer.param("weight_" + p).set(w_host[i])
+        layer.to_device(capi.DEVICE_CUDA)
+        layer.set_precision(mma)
     x = Tensor.from_numpy(x_host, capi.DEVICE_CUDA, bf16=bf16)
-    g = Tensor.from_numpy(g_host, capi.DEVICE_CUDA, bf16=bf16)
+    g = Tensor.from_numpy(g_host, capi.DEVICE_CUDA, bf16=bf16)    # upstream gradient (attention) or MSE target (block)
     flush = None
     if T * d * 2 <= 126e6:
         flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
+    def block_step():
+        out, dx = block.step(x, g)
+        if world > 1:
+            layer.allreduce_grads()      # attention bucket; the MLP and LayerNorm gradients are not reduced yet
+        block.zero_dense_grads()
+        out.free()
+        dx.free()
+
     def step():
+        if is_block:
+            return block_step()
         out = layer.forward(x, x, x)
         gq, gk, gv = layer.backward(g)
         if world > 1:
@@ -340,7 +368,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = float(t.item()) / args.steps
     tokens_per_s = world * T / (ms_per_step * 1e-3)
-    flops = algorithmic_flops(B, S, d, causal)
+    flops = block_flops(B, S, d, causal) if is_block else algorithmic_flops(B, S, d, causal)
     tflops_per_gpu = flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- roofline of the dominant kernel family ----
@@ -373,7 +401,7 @@ def main():
 
     # ---- end to end through the public API with host tensors (rank 0 reports) ----
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not is_block:
         host_layer = Attention(d, nh, causal=causal, use_bias=True)
         for i, p in enumerate("qkvo"):
             host_layer.param("weight_" + p).set(w_host[i])
@@ -412,12 +440,12 @@ def main():
         host_layer.free()
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and not is_block:
         cpu = cpu_baseline(cfg, 12.0, 1)
         cpu.pop("seconds", None)
 
     if rank == 0:
-        line = dict(metric="attention_fwd_bwd_tokens_per_s", value=tokens_per_s, unit="tokens/s", n_gpus=world,
+        line = dict(metric="encoder_block_step_tokens_per_s" if is_block else "attention_fwd_bwd_tokens_per_s", value=tokens_per_s, unit="tokens/s", n_gpus=world,
                     steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True,
                     scaling="weak", vs_baseline=None, dtype="bf16" if bf16 else "tf32", data="synthetic",
                     config=workload_config(args.workload, cfg, world),

@@ -121,6 +121,7 @@ PROTOTYPES = {
     # include/boat/ops.h
     "boat_add": (_P, [_P, _P]),
     "boat_mul": (_P, [_P, _P]),
+    "boat_sub": (_P, [_P, _P]),
     "boat_add_": (None, [_P, _P]),
     "boat_sub_": (None, [_P, _P]),
     "boat_mul_scalar": (_P, [_P, _D]),
@@ -153,6 +154,7 @@ PROTOTYPES = {
     "boat_norm_layer_update": (None, [_P, _F]),
     # include/boat_b200.h
     "boat_gelu_backward": (_P, [_P, _P]),
+    "boat_lincomb": (_P, [_P, _F, _P, _F]),
     "boat_layernorm_get_weight": (_P, [_P]),
     "boat_layernorm_get_bias": (_P, [_P]),
     "boat_layernorm_get_grad_weight": (_P, [_P]),
@@ -196,6 +198,7 @@ PROTOTYPES = {
     "boat_cuda_scale": (_I, [_P, _P, _F, _I64]),
     "boat_cuda_add_bias": (_I, [_P, _P, _P, _I64, _I64]),
     "boat_cuda_mul": (_I, [_P, _P, _P, _I64]),
+    "boat_cuda_lincomb": (_I, [_P, _P, _F, _P, _F, _I, _I64]),
     "boat_cuda_cast": (_I, [_P, _I, _P, _I, _I64]),
     "boat_cuda_round_tf32": (_I, [_P, _P, _I64]),
     "boat_cuda_transpose": (_I, [_P, _P, _I64, _I64, _I64]),

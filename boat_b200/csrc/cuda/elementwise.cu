@@ -100,6 +100,29 @@ __global__ void add_bias_kernel(float* __restrict__ y, const float* __restrict__
     }
 }
 
+// ---- y = alpha*a + beta*b on FP32 or BF16 storage (residual adds, differences, MSE gradient) ----
+template <typename T>
+__global__ void lincomb_kernel(T* __restrict__ y, const T* __restrict__ a, float alpha, const T* __restrict__ b,
+                               float beta, int64_t n, int vec) {
+    constexpr int V = 16 / sizeof(T);
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    if (vec) {
+        const int64_t nv = n / V;
+        for (; i < nv; i += step) {
+            uint4 av = reinterpret_cast<const uint4*>(a)[i], bv = reinterpret_cast<const uint4*>(b)[i], ov;
+            const T* ae = reinterpret_cast<const T*>(&av);
+            const T* be = reinterpret_cast<const T*>(&bv);
+            T* oe = reinterpret_cast<T*>(&ov);
+#pragma unroll
+            for (int k = 0; k < V; ++k) oe[k] = from_f32<T>(alpha * to_f32(ae[k]) + beta * to_f32(be[k]));
+            reinterpret_cast<uint4*>(y)[i] = ov;
+        }
+    } else {
+        for (; i < n; i += step) y[i] = from_f32<T>(alpha * to_f32(a[i]) + beta * to_f32(b[i]));
+    }
+}
+
 // ---- casts -----------------------------------------------------------------------------------
 __global__ void cast_f32_to_bf16(__nv_bfloat16* __restrict__ dst, const float* __restrict__ src, int64_t n, int vec) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -345,6 +368,22 @@ int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64
     else
         cast_bf16_to_f32<<<grid, kThreads, 0, stream()>>>((float*)dst, (const __nv_bfloat16*)src, n, vec);
     BOATCU_LAUNCH_OK("cast");
+    return 0;
+}
+
+int boat_cuda_lincomb(void* y, const void* a, float alpha, const void* b, float beta, int type, int64_t n) {
+    if (n <= 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    const int V = type == BOAT_CUDA_BF16 ? 8 : 4;
+    int vec = aligned16(y) && aligned16(a) && aligned16(b) && (n % V) == 0;
+    int grid = grid_for(vec ? n / V : n, kThreads);
+    ProfileScope prof("lincomb");
+    if (type == BOAT_CUDA_BF16)
+        lincomb_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream()>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)a, alpha,
+                                                                       (const __nv_bfloat16*)b, beta, n, vec);
+    else
+        lincomb_kernel<float><<<grid, kThreads, 0, stream()>>>((float*)y, (const float*)a, alpha, (const float*)b, beta, n, vec);
+    BOATCU_LAUNCH_OK("lincomb");
     return 0;
 }
 

@@ -75,7 +75,12 @@ static bool trailing_match(const boat_tensor_t* a, const boat_tensor_t* b) {
     return true;
 }
 
+boat_tensor_t* boat_lincomb(const boat_tensor_t* a, float alpha, const boat_tensor_t* b, float beta);
+
 static boat_tensor_t* binary(const boat_tensor_t* a, const boat_tensor_t* b, bool is_add) {
+    if (is_add && a && b && a->dtype == BOAT_DTYPE_BFLOAT16 && b->dtype == BOAT_DTYPE_BFLOAT16 &&
+        a->nelements == b->nelements)
+        return boat_lincomb(a, 1.0f, b, 1.0f);
     if (!f32_pair(a, b)) return NULL;
     if (b->nelements > a->nelements) {           /* the larger operand leads; both ops commute */
         const boat_tensor_t* t = a;
@@ -222,6 +227,31 @@ static boat_tensor_t* gelu_impl(const boat_tensor_t* x, const boat_tensor_t* gra
     if (xo) boat_dev_free(dx);
     if (go) boat_dev_free(dg);
     return out;
+}
+
+boat_tensor_t* boat_lincomb(const boat_tensor_t* a, float alpha, const boat_tensor_t* b, float beta) {
+    if (!a || !b || a->dtype != b->dtype || a->nelements != b->nelements || !boat_dtype_supported(a->dtype)) return NULL;
+    if (boat_report("CUDA start-up", boat_cuda_init(-1)) != 0) return NULL;
+    const int type = boat_storage_of(a->dtype);
+    bool ao = false, bo = false;
+    void* da = boat_stage_in(a, type, &ao);
+    void* db = boat_stage_in(b, type, &bo);
+    void* dy = boat_dev_alloc(a->nelements * boat_storage_size(type));
+    boat_tensor_t* out = NULL;
+    if (da && db && dy &&
+        boat_report("lincomb", boat_cuda_lincomb(dy, da, alpha, db, beta, type, (int64_t)a->nelements)) == 0)
+        out = boat_emit_out(a->shape, a->ndim, a, dy, type);
+    boat_dev_free(dy);
+    if (ao) boat_dev_free(da);
+    if (bo) boat_dev_free(db);
+    return out;
+}
+
+boat_tensor_t* boat_sub(const boat_tensor_t* a, const boat_tensor_t* b) {
+    if (!a || !b || a->ndim != b->ndim) return NULL;
+    for (size_t i = 0; i < a->ndim; ++i)
+        if (a->shape[i] != b->shape[i]) return NULL;
+    return boat_lincomb(a, 1.0f, b, -1.0f);
 }
 
 boat_tensor_t* boat_gelu(const boat_tensor_t* a) { return gelu_impl(a, NULL); }

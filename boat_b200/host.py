@@ -220,3 +220,140 @@ class DeviceBuffer:
             self.free()
         except Exception:
             pass
+
+
+class LayerNorm:
+    """boat_layernorm_t (include/boat/layers/norm.h)."""
+
+    def __init__(self, H, eps=1e-5, weight=None, bias=None, affine=True, device=capi.DEVICE_CPU):
+        lib = capi.load()
+        has_w = affine or weight is not None
+        has_b = has_w and (affine or bias is not None)
+        cfg = capi.LayerNormConfig(H, eps, has_w, has_b)
+        self.h = C.c_void_p(lib.boat_layernorm_create(C.byref(cfg)))
+        if not self.h.value:
+            raise BoatError("boat_layernorm_create returned NULL")
+        if weight is not None:
+            Tensor(lib.boat_layernorm_get_weight(self.h), own=False).set(weight)
+        if bias is not None:
+            Tensor(lib.boat_layernorm_get_bias(self.h), own=False).set(bias)
+        if device == capi.DEVICE_CUDA and lib.boat_layernorm_to_device(self.h, device):
+            raise BoatError("boat_layernorm_to_device failed")
+
+    def forward(self, x):
+        return Tensor(capi.load().boat_layernorm_forward(self.h, x.h))
+
+    def backward(self, g):
+        return Tensor(capi.load().boat_layernorm_backward(self.h, g.h))
+
+    def grads(self):
+        lib = capi.load()
+        gw, gb = lib.boat_layernorm_get_grad_weight(self.h), lib.boat_layernorm_get_grad_bias(self.h)
+        return (Tensor(gw, own=False).numpy() if gw else None, Tensor(gb, own=False).numpy() if gb else None)
+
+    def free(self):
+        if self.h:
+            capi.load().boat_layernorm_free(self.h)
+        self.h = None
+
+
+class Dense:
+    """boat_dense_layer_t (include/boat/layers.h)."""
+
+    def __init__(self, I, O, weight=None, bias=None, use_bias=True, device=capi.DEVICE_CPU):
+        lib = capi.load()
+        self.h = C.c_void_p(lib.boat_dense_layer_create(I, O, use_bias or bias is not None))
+        if not self.h.value:
+            raise BoatError("boat_dense_layer_create returned NULL")
+        if weight is not None:
+            Tensor(lib.boat_dense_layer_get_weight(self.h), own=False).set(weight)
+        if bias is not None:
+            Tensor(lib.boat_dense_layer_get_bias(self.h), own=False).set(bias)
+        if device == capi.DEVICE_CUDA and lib.boat_dense_layer_to_device(self.h, device):
+            raise BoatError("boat_dense_layer_to_device failed")
+
+    def forward(self, x):
+        return Tensor(capi.load().boat_dense_layer_forward(self.h, x.h))
+
+    def backward(self, g):
+        return Tensor(capi.load().boat_dense_layer_backward(self.h, g.h))
+
+    def grads(self):
+        lib = capi.load()
+        gb = lib.boat_dense_layer_get_grad_bias(self.h)
+        return (Tensor(lib.boat_dense_layer_get_grad_weight(self.h), own=False).numpy(),
+                Tensor(gb, own=False).numpy() if gb else None)
+
+    def update(self, lr):
+        capi.load().boat_dense_layer_update(self.h, C.c_float(lr))
+
+    def free(self):
+        if self.h:
+            capi.load().boat_dense_layer_free(self.h)
+        self.h = None
+
+
+def reshape(t, shape):
+    arr, n = _shape_arg(shape)
+    return Tensor(capi.load().boat_tensor_reshape(t.h, arr, n))
+
+
+def lincomb(a, alpha, b, beta):
+    return Tensor(capi.load().boat_lincomb(a.h, C.c_float(alpha), b.h, C.c_float(beta)))
+
+
+class EncoderBlock:
+    """Pre-LN transformer encoder block composed from the C API, one call per layer:
+    LN -> attention -> +x -> LN -> dense(4d) -> GELU -> dense(d) -> +, mean-squared-error loss.
+    The reference has no block object either; its tests chain layer calls by hand like this."""
+
+    def __init__(self, d, nh, causal=False, device=capi.DEVICE_CUDA, mma=capi.MMA_BF16, params=None):
+        p = params or {}
+        self.d = d
+        self.ln1 = LayerNorm(d, 1e-5, p.get("g1"), p.get("b1"), device=device)
+        self.ln2 = LayerNorm(d, 1e-5, p.get("g2"), p.get("b2"), device=device)
+        self.fc1 = Dense(d, 4 * d, p.get("w1"), p.get("c1"), device=device)
+        self.fc2 = Dense(4 * d, d, p.get("w2"), p.get("c2"), device=device)
+        self.attn = Attention(d, nh, causal=causal)
+        if "w" in p:
+            for i, q in enumerate("qkvo"):
+                self.attn.param("weight_" + q).set(p["w"][i])
+                if p.get("b") is not None:
+                    self.attn.param("bias_" + q).set(p["b"][i])
+        if device == capi.DEVICE_CUDA:
+            self.attn.to_device(device)
+        self.attn.set_precision(mma)
+
+    def step(self, x, target):
+        """Forward, MSE gradient, backward.  Returns (out, dx); parameter gradients stay in the layers."""
+        lib = capi.load()
+        B, S, d = x.shape
+        T = B * S
+        h1 = self.ln1.forward(x)
+        att = self.attn.forward(h1)
+        r1 = lincomb(x, 1.0, att, 1.0)
+        h2 = self.ln2.forward(r1)
+        u = self.fc1.forward(reshape(h2, (T, d)))
+        a = Tensor(lib.boat_gelu(u.h))
+        m = reshape(self.fc2.forward(a), (B, S, d))
+        out = lincomb(r1, 1.0, m, 1.0)
+        scale = 2.0 / float(T * d)
+        dout = lincomb(out, scale, target, -scale)
+        da = self.fc2.backward(reshape(dout, (T, d)))
+        du = Tensor(lib.boat_gelu_backward(da.h, u.h))
+        dh2 = self.fc1.backward(du)
+        dr1 = lincomb(dout, 1.0, self.ln2.backward(reshape(dh2, (B, S, d))), 1.0)
+        gq, gk, gv = self.attn.backward(dr1)
+        dh1 = lincomb(lincomb(gq, 1.0, gk, 1.0), 1.0, gv, 1.0)
+        dx = lincomb(dr1, 1.0, self.ln1.backward(dh1), 1.0)
+        return out, dx
+
+    def zero_dense_grads(self):
+        """Dense gradients accumulate across backward calls (as in the reference); a training loop
+        clears them with the update step - lr 0 leaves the weights alone."""
+        self.fc1.update(0.0)
+        self.fc2.update(0.0)
+
+    def free(self):
+        for layer in (self.ln1, self.ln2, self.fc1, self.fc2, self.attn):
+            layer.free()

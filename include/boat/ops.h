@@ -19,6 +19,8 @@ extern "C" {
  * trailing dimensions of `a` (bias [H] added to [B,S,H]).  Other shape pairs give NULL. */
 BOAT_API boat_tensor_t* boat_add(const boat_tensor_t* a, const boat_tensor_t* b);
 BOAT_API boat_tensor_t* boat_mul(const boat_tensor_t* a, const boat_tensor_t* b);
+/* Equal shapes only; FP32 or BF16 (boat_add of equal shapes accepts BF16 as well). */
+BOAT_API boat_tensor_t* boat_sub(const boat_tensor_t* a, const boat_tensor_t* b);
 
 /* In place, equal element counts required (arithmetic.c:362-422); otherwise no-op. */
 BOAT_API void boat_add_(boat_tensor_t* a, const boat_tensor_t* b);

@@ -41,6 +41,10 @@ BOAT_API int boat_attention_grad_bucket(const boat_attention_t* attention, float
  * different slice of the batch).  No-op with a single rank.  Returns 0 on success. */
 BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
 
+/* alpha*a + beta*b for equal shapes, FP32 or BF16, host or device: one kernel for residual
+ * adds, differences and the mean-squared-error gradient 2(o - t)/n. */
+BOAT_API boat_tensor_t* boat_lincomb(const boat_tensor_t* a, float alpha, const boat_tensor_t* b, float beta);
+
 /* dx = dy * dGELU/dx(input), the backward of boat_gelu (the reference has neither). */
 BOAT_API boat_tensor_t* boat_gelu_backward(const boat_tensor_t* grad_output, const boat_tensor_t* input);
 

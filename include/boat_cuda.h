@@ -121,6 +121,8 @@ int boat_cuda_attn_bwd_static(int mma, int64_t units, int64_t S, int64_t hs, int
  * scale:   y = alpha * x             boat_mul_scalar (arithmetic.c:425-484)
  * add_bias: y[i,j] = x[i,j] + b[j]   boat_add bias broadcast (arithmetic.c:199-203)
  * mul:     y = a * b                 boat_mul, equal shapes (arithmetic.c:240-285)
+ * lincomb: y = alpha*a + beta*b on FP32 or BF16 storage - boat_add / boat_sub of equal shapes
+ *          (arithmetic.c:157-285), the residual adds of the encoder block, the MSE gradient
  * cast:    FP32 <-> BF16, round to nearest even
  * round_tf32: y = x rounded to the nearest TF32 value, stored as FP32 (in place allowed);
  *          operands prepared this way make the tensor core's own truncation exact
@@ -130,6 +132,7 @@ int boat_cuda_axpy(float* y, const float* x, float alpha, int64_t n);
 int boat_cuda_scale(float* y, const float* x, float alpha, int64_t n);
 int boat_cuda_add_bias(float* y, const float* x, const float* bias, int64_t rows, int64_t cols);
 int boat_cuda_mul(float* y, const float* a, const float* b, int64_t n);
+int boat_cuda_lincomb(void* y, const void* a, float alpha, const void* b, float beta, int type, int64_t n);
 int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64_t n);
 int boat_cuda_round_tf32(float* y, const float* x, int64_t n);
 int boat_cuda_transpose(float* out, const float* in, int64_t batch, int64_t rows, int64_t cols);

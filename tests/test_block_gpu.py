@@ -12,6 +12,7 @@ import pytest
 
 import cases
 from boat_b200 import capi, rng
+from boat_b200 import host
 from boat_b200.host import Attention, Tensor
 from oracle import oracle
 
@@ -25,57 +26,12 @@ def rel(a, ref):
     return float(np.abs(np.asarray(a, np.float64) - ref).max() / np.abs(ref).max())
 
 
-class LayerNorm:
-    def __init__(self, lib, H, eps, w=None, b=None, device=capi.DEVICE_CPU):
-        self.lib = lib
-        cfg = capi.LayerNormConfig(H, eps, w is not None, b is not None)
-        self.h = C.c_void_p(lib.boat_layernorm_create(C.byref(cfg)))
-        assert self.h.value
-        if w is not None:
-            Tensor(lib.boat_layernorm_get_weight(self.h), own=False).set(w)
-        if b is not None:
-            Tensor(lib.boat_layernorm_get_bias(self.h), own=False).set(b)
-        if device == capi.DEVICE_CUDA:
-            assert lib.boat_layernorm_to_device(self.h, device) == 0
-
-    def forward(self, x):
-        return Tensor(self.lib.boat_layernorm_forward(self.h, x.h))
-
-    def backward(self, g):
-        return Tensor(self.lib.boat_layernorm_backward(self.h, g.h))
-
-    def grads(self):
-        gw, gb = self.lib.boat_layernorm_get_grad_weight(self.h), self.lib.boat_layernorm_get_grad_bias(self.h)
-        return (Tensor(gw, own=False).numpy() if gw else None, Tensor(gb, own=False).numpy() if gb else None)
-
-    def free(self):
-        self.lib.boat_layernorm_free(self.h)
+def LayerNorm(lib, H, eps, w=None, b=None, device=capi.DEVICE_CPU):
+    return host.LayerNorm(H, eps, w, b, affine=False, device=device)
 
 
-class Dense:
-    def __init__(self, lib, I, O, w, b, device=capi.DEVICE_CPU):
-        self.lib = lib
-        self.h = C.c_void_p(lib.boat_dense_layer_create(I, O, b is not None))
-        assert self.h.value
-        Tensor(lib.boat_dense_layer_get_weight(self.h), own=False).set(w)
-        if b is not None:
-            Tensor(lib.boat_dense_layer_get_bias(self.h), own=False).set(b)
-        if device == capi.DEVICE_CUDA:
-            assert lib.boat_dense_layer_to_device(self.h, device) == 0
-
-    def forward(self, x):
-        return Tensor(self.lib.boat_dense_layer_forward(self.h, x.h))
-
-    def backward(self, g):
-        return Tensor(self.lib.boat_dense_layer_backward(self.h, g.h))
-
-    def grads(self):
-        gb = self.lib.boat_dense_layer_get_grad_bias(self.h)
-        return (Tensor(self.lib.boat_dense_layer_get_grad_weight(self.h), own=False).numpy(),
-                Tensor(gb, own=False).numpy() if gb else None)
-
-    def free(self):
-        self.lib.boat_dense_layer_free(self.h)
+def Dense(lib, I, O, w, b, device=capi.DEVICE_CPU):
+    return host.Dense(I, O, w, b, use_bias=b is not None, device=device)
 
 
 @pytest.mark.parametrize("device", [capi.DEVICE_CPU, capi.DEVICE_CUDA], ids=["host_tensors", "cuda_tensors"])
@@ -192,59 +148,25 @@ def block_reference(inp, nh, causal):
 
 def block_gpu(lib, inp, nh, causal, bf16):
     dev = capi.DEVICE_CUDA
-    x_np, t_np = inp["x"], inp["target"]
-    B, S, d = x_np.shape
-    T = B * S
-    ln1, ln2 = LayerNorm(lib, d, 1e-5, inp["g1"], inp["b1"], dev), LayerNorm(lib, d, 1e-5, inp["g2"], inp["b2"], dev)
-    fc1, fc2 = Dense(lib, d, 4 * d, inp["w1"], inp["c1"], dev), Dense(lib, 4 * d, d, inp["w2"], inp["c2"], dev)
-    attn = Attention(d, nh, causal=causal)
-    for i, p in enumerate("qkvo"):
-        attn.param("weight_" + p).set(inp["w"][i])
-        attn.param("bias_" + p).set(inp["b"][i])
-    attn.to_device(dev)
-    attn.set_precision(capi.MMA_BF16 if bf16 else capi.MMA_FP32)
-
-    def reshape(t, shape):
-        arr = (C.c_int64 * len(shape))(*shape)
-        return Tensor(lib.boat_tensor_reshape(t.h, arr, len(shape)))
-
-    def add(a, b):
-        return Tensor(lib.boat_add(a.h, b.h)) if not bf16 else Tensor.from_numpy(a.numpy() + b.numpy(), dev, bf16=True)
-
-    x = Tensor.from_numpy(x_np, dev, bf16=bf16)
-    h1 = ln1.forward(x)
-    att = attn.forward(h1)
-    r1 = add(x, att)
-    h2 = ln2.forward(r1)
-    u = fc1.forward(reshape(h2, (T, d)))
-    a = Tensor(lib.boat_gelu(u.h))
-    m = reshape(fc2.forward(a), (B, S, d))
-    out = add(r1, m)
+    d = inp["x"].shape[2]
+    blk = host.EncoderBlock(d, nh, causal=causal, device=dev, mma=capi.MMA_BF16 if bf16 else capi.MMA_FP32, params=inp)
+    x = Tensor.from_numpy(inp["x"], dev, bf16=bf16)
+    t = Tensor.from_numpy(inp["target"], dev, bf16=bf16)
+    out, dx = blk.step(x, t)
     out_np = out.numpy()
-    dout_np = (np.float32(2.0) * (out_np - t_np) / np.float32(out_np.size)).astype(np.float32)
-    dout = Tensor.from_numpy(dout_np, dev, bf16=bf16)
-    da = fc2.backward(reshape(dout, (T, d)))
-    du = Tensor(lib.boat_gelu_backward(da.h, u.h))
-    dh2 = fc1.backward(du)
-    dr1_ln = ln2.backward(reshape(dh2, (B, S, d)))
-    dr1 = add(dout, dr1_ln)
-    gq, gk, gv = attn.backward(dr1)
-    dh1 = add(add(gq, gk), gv)
-    dx_ln = ln1.backward(dh1)
-    dx = add(dr1, dx_ln)
-    res = dict(out=out_np, dx=dx.numpy(), dw1=fc1.grads()[0], dc1=fc1.grads()[1], dw2=fc2.grads()[0], dc2=fc2.grads()[1],
-               dg1=ln1.grads()[0], db1=ln1.grads()[1], dg2=ln2.grads()[0], db2=ln2.grads()[1],
-               dwq=attn.param("grad_weight_q").numpy(), dwo=attn.param("grad_weight_o").numpy(),
-               loss=float(((out_np - t_np).astype(np.float64) ** 2).mean()))
-    for layer in (ln1, ln2, fc1, fc2, attn):
-        layer.free()
+    res = dict(out=out_np, dx=dx.numpy(), dw1=blk.fc1.grads()[0], dc1=blk.fc1.grads()[1], dw2=blk.fc2.grads()[0],
+               dc2=blk.fc2.grads()[1], dg1=blk.ln1.grads()[0], db1=blk.ln1.grads()[1], dg2=blk.ln2.grads()[0],
+               db2=blk.ln2.grads()[1], dwq=blk.attn.param("grad_weight_q").numpy(),
+               dwo=blk.attn.param("grad_weight_o").numpy(),
+               loss=float(((out_np - inp["target"]).astype(np.float64) ** 2).mean()))
+    blk.free()
     return res
 
 
 def block_inputs(B, S, d, bf16):
     f = rng.bf16_round if bf16 else (lambda a: a)
     n = lambda tid, shape, std: f(rng.normal(77, tid, shape, std))
-    return dict(x=n(0, (B, S, d), 1.0), target=rng.normal(77, 1, (B, S, d), 1.0),
+    return dict(x=n(0, (B, S, d), 1.0), target=n(1, (B, S, d), 1.0),
                 w=[n(2 + i, (d, d), 0.02 * 8) for i in range(4)], b=[rng.normal(77, 6 + i, (d,), 0.05) for i in range(4)],
                 g1=rng.normal(77, 10, (d,), 0.1) + 1, b1=rng.normal(77, 11, (d,), 0.1),
                 g2=rng.normal(77, 12, (d,), 0.1) + 1, b2=rng.normal(77, 13, (d,), 0.1),

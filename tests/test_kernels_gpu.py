@@ -208,12 +208,13 @@ def test_round_tf32_is_round_to_nearest_on_10_mantissa_bits(gpu_lib):
 
 def test_pinned_host_pool_reuses_blocks(gpu_lib):
     lib = gpu_lib
-    a = lib.boat_cuda_host_alloc(1 << 20)
+    big = 97 << 20                                       # larger than anything the other tests leave in the pool
+    a = lib.boat_cuda_host_alloc(big)
     assert a
     assert lib.boat_cuda_host_free(a) == 0
-    b = lib.boat_cuda_host_alloc((1 << 20) - 4096)       # close enough in size: the same block comes back
+    b = lib.boat_cuda_host_alloc(big - 4096)             # close enough in size: the same block comes back
     assert b == a
-    c = lib.boat_cuda_host_alloc(1 << 20)
+    c = lib.boat_cuda_host_alloc(big)
     assert c and c != b
     assert lib.boat_cuda_host_free(b) == 0 and lib.boat_cuda_host_free(c) == 0
     assert lib.boat_cuda_host_free(C.c_void_p(12345)) != 0
