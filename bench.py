@@ -199,7 +199,8 @@ def run_reference_arm(args, cfg, rank, world):
     if rank != 0:
         return
     procs = os.cpu_count() or 1
-    per_step = max(3.0, min(15.0, 150.0 / max(1, args.steps + args.warmup)))
+    # each step is one bounded sample; size it so that warm-up + K steps stay within ~2.5 minutes
+    per_step = max(1.0, min(15.0, 150.0 / max(1, args.steps + args.warmup)))
     vals = []
     for i in range(args.warmup + args.steps):
         r = cpu_baseline(cfg, per_step, procs)
