@@ -240,6 +240,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--optimizer", default="none", choices=["none", "adam"],
+                    help="adam: every step ends with boat_optimizer_step over the attention parameters")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()
@@ -302,6 +304,11 @@ def main():
             layer.param("weight_" + p).set(w_host[i])
         layer.to_device(capi.DEVICE_CUDA)
         layer.set_precision(mma)
+    adam = None
+    if args.optimizer == "adam":
+        from boat_b200.host import Adam
+        adam = Adam(1e-4)
+        adam.add_attention(layer)
     x = Tensor.from_numpy(x_host, capi.DEVICE_CUDA, bf16=bf16)
     g = Tensor.from_numpy(g_host, capi.DEVICE_CUDA, bf16=bf16)    # upstream gradient (attention) or MSE target (block)
     flush = None
@@ -318,11 +325,16 @@ def main():
 
     def step():
         if is_block:
-            return block_step()
+            block_step()
+            if adam:
+                adam.step()
+            return
         out = layer.forward(x, x, x)
         gq, gk, gv = layer.backward(g)
         if world > 1:
             layer.allreduce_grads()
+        if adam:
+            adam.step()
         for t in (out, gq, gk, gv):
             t.free()
 
@@ -385,6 +397,7 @@ def main():
         "flash_fwd": 4.0 * core_c * B * S * S * d, "attn_fwd_simt": 4.0 * core_c * B * S * S * d,
         "flash_bwd": 8.0 * core_c * B * S * S * d, "attn_bwd_simt": 8.0 * core_c * B * S * S * d,
     }
+    kbytes = {"adam_step": 28.0 * (4 * d * d + 4 * d)}     # p, g, m, v read; p, m, v written (FP32)
     roofline = None
     if kern:
         top = max((k for k in kern if k in kflops), key=lambda k: kern[k][1], default=None)
@@ -399,6 +412,10 @@ def main():
                             peak_source=peaks["source"] + (" bf16 sustained" if bf16 else " bf16 sustained / 2 for tf32"),
                             kernels={k: dict(scopes=v[0], ms=round(v[1], 3), share=round(v[1] / sum(x[1] for x in kern.values()), 4))
                                      for k, v in sorted(kern.items(), key=lambda kv: -kv[1][1])})
+            for k, nbytes in kbytes.items():
+                if k in kern:
+                    gbs = nbytes / (kern[k][1] / kern[k][0] * 1e-3) / 1e9
+                    roofline["kernels"][k].update(hbm_gbs=round(gbs, 1), frac_of_hbm_peak=round(gbs / peaks["hbm"], 3))
 
     # ---- end to end through the public API with host tensors (rank 0 reports) ----
     e2e = None
@@ -449,7 +466,7 @@ def main():
         line = dict(metric="encoder_block_step_tokens_per_s" if is_block else "attention_fwd_bwd_tokens_per_s", value=tokens_per_s, unit="tokens/s", n_gpus=world,
                     steps=args.steps, warmup=args.warmup, ms_per_step=ms_per_step, higher_is_better=True,
                     scaling="weak", vs_baseline=None, dtype="bf16" if bf16 else "tf32", data="synthetic",
-                    config=workload_config(args.workload, cfg, world),
+                    config=dict(workload_config(args.workload, cfg, world), optimizer=args.optimizer),
                     tflops_per_gpu=tflops_per_gpu,
                     frac_of_bf16_peak=(tflops_per_gpu / peaks["bf16_sustained"]) if bf16 else None,
                     roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches), clocks=clocks)

@@ -166,6 +166,16 @@ PROTOTYPES = {
     "boat_attention_get_precision": (_I, [_P]),
     "boat_attention_grad_bucket": (_I, [_P, C.POINTER(C.POINTER(C.c_float)), C.POINTER(_SZ)]),
     "boat_attention_allreduce_grads": (_I, [_P]),
+    "boat_attention_add_to_optimizer": (_I, [_P, _P]),
+    # include/boat/optimizers.h
+    "boat_sgd_optimizer_create": (_P, [_F, _F]),
+    "boat_adam_optimizer_create": (_P, [_F, _F, _F, _F]),
+    "boat_optimizer_step": (None, [_P]),
+    "boat_optimizer_zero_grad": (None, [_P]),
+    "boat_optimizer_free": (None, [_P]),
+    "boat_optimizer_add_parameter": (None, [_P, _P, _P]),
+    "boat_optimizer_get_learning_rate": (_F, [_P]),
+    "boat_optimizer_set_learning_rate": (None, [_P, _F]),
     # include/boat_cuda.h
     "boat_cuda_init": (_I, [_I]),
     "boat_cuda_device_count": (_I, []),
@@ -206,6 +216,7 @@ PROTOTYPES = {
     "boat_cuda_layernorm_bwd": (_I, [_P, _P, _I, _I64, _I64, _P, _P, _P, _P, _P, _P]),
     "boat_cuda_gelu_fwd": (_I, [_P, _P, _I, _I64]),
     "boat_cuda_gelu_bwd": (_I, [_P, _P, _P, _I, _I64]),
+    "boat_cuda_adam_step": (_I, [_I, _P, _P, _P, _P, _P, _F, _F, _F, _F, _F, _F]),
     "boat_cuda_comm_unique_id": (_I, [_P]),
     "boat_cuda_comm_init": (_I, [_I, _I, _P]),
     "boat_cuda_comm_world": (_I, []),

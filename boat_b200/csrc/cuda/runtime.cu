@@ -18,7 +18,6 @@ namespace boatcu {
 static thread_local char g_err[512] = "";
 static std::mutex g_mu;
 static bool g_ready = false;
-static int g_device = -1;   // device the library is bound to
 static cudaStream_t g_stream = 0;
 static std::atomic<uint64_t> g_launches{0};
 static std::unordered_map<void*, size_t>* g_live = nullptr;
@@ -75,7 +74,6 @@ static int init_locked(int device) {
     BOATCU_CHECK(cudaHostAlloc((void**)&g_status_host, sizeof(unsigned int), cudaHostAllocMapped));
     *g_status_host = 0;
     BOATCU_CHECK(cudaHostGetDevicePointer((void**)&g_status_dev, g_status_host, 0));
-    g_device = dev;
     g_ready = true;
     return 0;
 }

@@ -662,6 +662,14 @@ int boat_attention_to_device(boat_attention_t* a, boat_device_t device) {
     return 0;
 }
 
+int boat_attention_add_to_optimizer(boat_attention_t* a, boat_optimizer_t* optimizer) {
+    if (!a || !optimizer) return 1;
+    if (!ensure_grads(a)) return 2;          /* a new bucket starts out zero */
+    for (int i = 0; i < NPARAM; ++i)
+        if (a->param[i] && a->grad[i]) boat_optimizer_add_parameter(optimizer, a->param[i], a->grad[i]);
+    return 0;
+}
+
 int boat_attention_set_precision(boat_attention_t* a, int mma) {
     if (!a || mma < -1 || mma > BOAT_MMA_BF16) return 1;
     a->precision = mma;

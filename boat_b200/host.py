@@ -183,6 +183,52 @@ class Attention:
             pass
 
 
+class Adam:
+    """boat_optimizer_t made by boat_adam_optimizer_create.  Registered tensors are borrowed:
+    keep them alive while the optimizer is."""
+
+    def __init__(self, lr, beta1=0.9, beta2=0.999, eps=1e-8):
+        h = capi.load().boat_adam_optimizer_create(lr, beta1, beta2, eps)
+        if not h:
+            raise BoatError("boat_adam_optimizer_create refused the hyper-parameters")
+        self.h = C.c_void_p(h)
+        self._keep = []
+
+    def add(self, param, grad):
+        self._keep += [param, grad]
+        capi.load().boat_optimizer_add_parameter(self.h, param.h, grad.h)
+
+    def add_attention(self, attention):
+        rc = capi.load().boat_attention_add_to_optimizer(attention.h, self.h)
+        if rc:
+            raise BoatError("boat_attention_add_to_optimizer failed (%d)" % rc)
+
+    def step(self):
+        capi.load().boat_optimizer_step(self.h)
+
+    def zero_grad(self):
+        capi.load().boat_optimizer_zero_grad(self.h)
+
+    @property
+    def lr(self):
+        return capi.load().boat_optimizer_get_learning_rate(self.h)
+
+    @lr.setter
+    def lr(self, value):
+        capi.load().boat_optimizer_set_learning_rate(self.h, value)
+
+    def free(self):
+        if self.h:
+            capi.load().boat_optimizer_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 def check(rc, what="boat_cuda call"):
     if rc != 0:
         raise BoatError("%s failed (%d): %s" % (what, rc, (capi.load().boat_cuda_last_error() or b"").decode()))

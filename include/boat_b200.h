@@ -11,6 +11,7 @@
 #include "boat/layers/attention.h"
 #include "boat/layers/norm.h"
 #include "boat/layers.h"
+#include "boat/optimizers.h"
 #include "boat_cuda.h"
 
 #ifdef __cplusplus
@@ -40,6 +41,14 @@ BOAT_API int boat_attention_grad_bucket(const boat_attention_t* attention, float
  * boat_cuda_comm_init (data-parallel training: every rank holds the same weights and a
  * different slice of the batch).  No-op with a single rank.  Returns 0 on success. */
 BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
+
+/* Register the layer's parameters with an optimizer (boat/optimizers.h), each with its
+ * gradient tensor.  The reference's layer makes new gradient tensors on every backward
+ * (src/layers/attention.c:653-654, :702-703), which leaves an optimizer's registered pointers
+ * dangling; here the gradient tensors are fixed windows into the bucket above and are created
+ * (zeroed) by this call if no backward has run yet.  They are re-made when the layer moves to
+ * another device, so call boat_attention_to_device first.  Returns 0 on success. */
+BOAT_API int boat_attention_add_to_optimizer(boat_attention_t* attention, boat_optimizer_t* optimizer);
 
 /* alpha*a + beta*b for equal shapes, FP32 or BF16, host or device: one kernel for residual
  * adds, differences and the mean-squared-error gradient 2(o - t)/n. */

@@ -153,6 +153,16 @@ int boat_cuda_layernorm_bwd(const void* dy, const void* x, int type, int64_t row
 int boat_cuda_gelu_fwd(void* y, const void* x, int type, int64_t n);
 int boat_cuda_gelu_bwd(void* dx, const void* dy, const void* x, int type, int64_t n);
 
+/* ---- Adam step over a list of FP32 tensors (adam_update_parameter, src/optimizers/adam.c:156-193) ----
+ * For tensor t in [0,count) and each of its nelements[t] elements, in the reference's order of
+ * rounded FP32 operations:  m = b1*m + (1-b1)*g;  v = b2*v + (1-b2)*g*g;
+ * p -= lr*(m/corr1) / (sqrt(v/corr2) + eps),  corr1 = 1-b1^t, corr2 = 1-b2^t computed by the
+ * caller on the host (the reference uses powf there).  The pointer arrays live in host memory;
+ * the tensors they point to live on the device.  One launch covers up to 24 tensors. */
+int boat_cuda_adam_step(int count, float* const* params, const float* const* grads, float* const* m,
+                        float* const* v, const int64_t* nelements, float lr, float beta1, float beta2,
+                        float epsilon, float corr1, float corr2);
+
 /* ---- gradient exchange between GPUs (nothing in the reference: it is single-process) ---
  * One process per GPU.  Rank 0 makes an id (128 bytes) and hands it to the others by any
  * host channel; every rank then calls comm_init.  allreduce sums an FP32 buffer in place

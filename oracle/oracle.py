@@ -424,3 +424,48 @@ def ref_dense_step(x, w, b, dy, repeats=1):
         lib.boat_tensor_unref(h)
     lib.boat_dense_layer_free(layer)
     return res
+
+
+# ---- Adam (optimizer_oracle.c) ------------------------------------------------------------------------
+
+def port_adam(params, grads_per_step, lr, beta1, beta2, eps):
+    """Runs len(grads_per_step) Adam steps over a list of FP32 arrays with the C restatement.
+    grads_per_step[s][i] is the gradient of params[i] at step s.  Returns the final parameters."""
+    lib = port()
+    lib.oracle_adam_step.argtypes = [_FP, _FP, _FP, _FP, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float,
+                                     C.c_int64]
+    ps = [np.ascontiguousarray(p, dtype=np.float32).copy() for p in params]
+    ms = [np.zeros(p.size, np.float32) for p in ps]
+    vs = [np.zeros(p.size, np.float32) for p in ps]
+    for step, grads in enumerate(grads_per_step):
+        for p, g, m, v in zip(ps, grads, ms, vs):
+            g = _f32(g)
+            lib.oracle_adam_step(_fp(p), _fp(g), _fp(m), _fp(v), p.size, lr, beta1, beta2, eps, step)
+    return ps
+
+
+def ref_adam(params, grads_per_step, lr, beta1, beta2, eps):
+    """The same through the reference library's own optimizer API (boat_adam_optimizer_create,
+    boat_optimizer_add_parameter, boat_optimizer_step)."""
+    lib = ref()
+    P = C.c_void_p
+    lib.boat_adam_optimizer_create.restype = P
+    lib.boat_adam_optimizer_create.argtypes = [C.c_float] * 4
+    lib.boat_optimizer_add_parameter.argtypes = [P, P, P]
+    lib.boat_optimizer_step.argtypes = [P]
+    lib.boat_optimizer_free.argtypes = [P]
+    opt = lib.boat_adam_optimizer_create(lr, beta1, beta2, eps)
+    assert opt, "reference refused the Adam hyper-parameters"
+    hp = [_ref_new(lib, _f32(p)) for p in params]
+    hg = [_ref_new(lib, np.zeros_like(_f32(p))) for p in params]
+    for a, b in zip(hp, hg):
+        lib.boat_optimizer_add_parameter(opt, a, b)
+    for grads in grads_per_step:
+        for h, g in zip(hg, grads):
+            RefTensor(lib, h).view()[:] = _f32(g).ravel()
+        lib.boat_optimizer_step(opt)
+    out = [RefTensor(lib, h).view(np.shape(p)).copy() for h, p in zip(hp, params)]
+    lib.boat_optimizer_free(opt)
+    for h in hp + hg:
+        lib.boat_tensor_unref(h)
+    return out

@@ -108,3 +108,25 @@ def layernorm_inputs(rows_shape=(3, 7), H=48):
 def dense_inputs(N=19, I=24, O=40):
     return dict(x=rng.normal(SEED, 30, (N, I)), w=rng.normal(SEED, 31, (I, O), 0.2), b=rng.normal(SEED, 32, (O,), 0.1),
                 dy=rng.normal(SEED, 33, (N, O)))
+
+
+# ---- Adam: seeded parameters and a sequence of gradients ------------------------------------------------
+
+ADAM_HYPER = dict(lr=0.01, beta1=0.9, beta2=0.999, eps=1e-8)
+
+
+def adam_inputs(shapes=((33, 17), (4096 + 5,), (7,), (64, 64)), steps=6, stream=40):
+    """Parameter tensors of ragged sizes (vector and scalar code paths) and `steps` gradients each; a few
+    gradient entries are exactly zero or tiny so that the epsilon term matters."""
+    params = [rng.normal(SEED, stream + i, s) for i, s in enumerate(shapes)]
+    grads = []
+    for t in range(steps):
+        gs = []
+        for i, s in enumerate(shapes):
+            g = rng.normal(SEED, stream + 100 * (t + 1) + i, s, 0.3)
+            flat = g.reshape(-1)
+            flat[::11] = 0.0
+            flat[5::13] *= np.float32(1e-6)
+            gs.append(g)
+        grads.append(gs)
+    return params, grads

@@ -1,4 +1,4 @@
-"""Regenerate tests/golden/attention_golden.npz from the reference itself.
+"""Regenerate tests/golden/attention_golden.npz and adam_golden.npz from the reference itself.
 
 Run in a checkout that has the reference tree (oracle/Makefile builds
 oracle/_ref/libboat_ref.so from it):
@@ -7,6 +7,9 @@ oracle/_ref/libboat_ref.so from it):
 
 Also stored: the reference's boat_layernorm_forward and its dense layer (forward, two
 accumulating backward calls) on the seeded inputs of tests/cases.py.
+
+adam_golden.npz holds the parameters after every step of the reference's Adam optimizer
+(boat_adam_optimizer_create / boat_optimizer_step) on cases.adam_inputs().
 
 For every case in tests/cases.py::GOLDEN_CASES the reference's own boat_attention_forward
 and boat_attention_backward are executed on the seeded inputs and every output and gradient
@@ -59,6 +62,14 @@ def main():
     print("layernorm, dense ok")
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "attention_golden.npz")
     np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+    params, grads = cases.adam_inputs()
+    adam = {}
+    for steps in range(1, len(grads) + 1):
+        for i, p in enumerate(oracle.ref_adam(params, grads[:steps], **cases.ADAM_HYPER)):
+            adam["step%d/p%d" % (steps, i)] = p
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "adam_golden.npz")
+    np.savez_compressed(path, **adam)
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
