@@ -17,13 +17,21 @@
 //   dQ_i = dS . K             A = the same shared-memory tile read along M (MN-major view)
 //
 // dQ of a query tile gets one contribution per key tile; CTAs add theirs into an FP32 buffer
-// with TMA reduce-add (cp.reduce.async.bulk.tensor), staged through the dS^T tile by four
-// dedicated warps, and a cast kernel turns the sum into the output type afterwards.  With head size 128 the 512 TMEM
-// columns are exactly S^T/P^T, dP^T (reused for dQ), dV and dK.
+// with TMA reduce-add (cp.reduce.async.bulk.tensor), and a cast kernel turns the sum into the
+// output type afterwards.  Four dedicated warps move the dQ tile out of tensor memory into
+// the Q / dO shared-memory stage that the tile's MMAs have just finished with (the FP32 dQ
+// tile is exactly as large as the BF16 Q and dO tiles together) and release the TMEM columns
+// at once.  An SM gets reductions out at only about 20 bytes per clock (measured alike for
+// TMA reduce-add and for red.global.add.v4.f32, which also stalls the softmax warps' shared
+// memory traffic), so the 64 KB of a tile keep the TMA unit busy for ~3000 cycles, and the
+// unit works in order: the thread that issues the reductions therefore also issues the loads
+// of the query tile two steps ahead, Q between the two halves of the reduction and dO after
+// it, so that no load queues behind a reduction it does not depend on.  With head size 128
+// the 512 TMEM columns are exactly S^T/P^T, dP^T (reused for dQ), dV and dK.
 // Warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store (two warps
-// per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.  The score MMA and
-// the dP MMA signal separately, so the exponentials of a tile run while the previous tile's
-// dQ is still being read out of the columns that dP^T re-uses.
+// per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.  The score MMA of the
+// next tile is issued right behind dV of the current one and signals on its own barrier, so
+// the exponentials of tile t+1 overlap the dK and dQ MMAs of tile t.
 #pragma once
 #include "flash_fwd_tc.cuh"
 
@@ -90,22 +98,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     float* stat_s = (float*)(ds_smem + C::DS_BYTES);                   // [2][-lse*log2e[128], -delta/sqrt(hs)[128]]
     uint64_t* bars = (uint64_t*)(stat_s + 512);
     uint64_t* kv_full = bars;                   // 1
-    uint64_t* q_full = bars + 1;                // [2]
-    uint64_t* q_empty = bars + 3;               // [2]
+    uint64_t* q_full = bars + 1;                // [2] Q tile landed
     uint64_t* s_full = bars + 5;                // S^T complete
     uint64_t* ds_full = bars + 6;               // P^T in TMEM, dS^T in smem (256 arrivals)
     uint64_t* dq_full = bars + 7;               // dV, dK, dQ MMAs of the tile complete
-    uint64_t* dq_empty = bars + 8;              // dQ read out and handed to the TMA unit
+    uint64_t* dq_empty = bars + 8;              // dQ is out of its TMEM columns
     uint64_t* all_done = bars + 9;
     uint64_t* dp_full = bars + 10;              // dP^T complete
-    uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+    uint64_t* do_full = bars + 11;              // [2] dO tile landed
+    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
     volatile uint32_t* softmax_ok = tmem_slot + 1;     // [2] written by one softmax thread, read by all 256
     volatile uint32_t* drain_ok = tmem_slot + 3;       // same idea for the dQ warps
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = p.S / kTile;
-    const int unit = blockIdx.x % p.units;
-    const int jt = blockIdx.x / p.units;                 // key tile; small jt = long walk, scheduled first
+    // Unit-major order: the CTAs that run at the same time belong to two or three (batch, head)
+    // units, so the FP32 dQ rows they reduce into (S*HS*4 bytes per unit) stay in L2.  With key
+    // tiles as the slow index every unit is active at once, the dQ buffer of a large problem
+    // (268 MB at 64 units x 8192 x 128) no longer fits, and each reduction misses to HBM.
+    // Inside a unit small jt (the long walk when causal) comes first.
+    const int unit = blockIdx.x / n_tiles;
+    const int jt = blockIdx.x % n_tiles;
     const int i_begin = p.causal ? jt : 0;
     const int n_q = n_tiles - i_begin;
     const int row_base = unit * p.S;
@@ -114,7 +127,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_init(kv_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&q_full[s], 1);
-            mbar_init(&q_empty[s], 1);
+            mbar_init(&do_full[s], 1);
         }
         mbar_init(s_full, 1);
         mbar_init(ds_full, 256);
@@ -138,24 +151,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            bool ok = true;
             mbar_arrive_expect_tx(kv_full, 2 * C::TILE_BYTES);
             for (int b = 0; b < C::NBOX; ++b) {
                 tma_load_2d(k_smem + b * kBoxBytes, &map_k, kv_full, b * 64, row_base + jt * kTile);
                 tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jt * kTile);
             }
-            for (int t = 0; t < n_q && ok; ++t) {
-                const int s = t & 1;
-                if (!mbar_wait(&q_empty[s], ((t >> 1) & 1) ^ 1, p.status, kTimeoutProducer)) { ok = false; break; }
-                mbar_arrive_expect_tx(&q_full[s], 2 * C::TILE_BYTES);
+            // the first two query tiles; later ones are loaded by the dQ warps, which stage dQ
+            // through these buffers and know when one is free again
+            for (int t = 0; t < n_q && t < C::Q_STAGES; ++t) {
                 const int y = row_base + (i_begin + t) * kTile;
-                for (int b = 0; b < C::NBOX; ++b) {
-                    tma_load_2d(q_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[s], b * 64, y);
-                    tma_load_2d(do_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_do, &q_full[s], b * 64, y);
-                }
+                mbar_arrive_expect_tx(&q_full[t], C::TILE_BYTES);
+                for (int b = 0; b < C::NBOX; ++b)
+                    tma_load_2d(q_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[t], b * 64, y);
+                mbar_arrive_expect_tx(&do_full[t], C::TILE_BYTES);
+                for (int b = 0; b < C::NBOX; ++b)
+                    tma_load_2d(do_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_do, &do_full[t], b * 64, y);
             }
-            if (!ok)
-                for (int i = 0; i < 1000; ++i) __nanosleep(1000);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -164,15 +175,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             constexpr uint32_t idesc_acc = make_idesc(kBF16, false, true, kTile, HS);      // dV, dK
             constexpr uint32_t idesc_dq = make_idesc(kBF16, true, true, kTile, HS);        // dQ
             const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
-            bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutMma);
-            for (int t = 0; t < n_q && ok; ++t) {
+            // Issue order on the (in-order) tensor pipe:
+            //   S(0) dP(0) | dV(t) S(t+1) dK(t) dQ(t) dP(t+1) | ...
+            // S^T of the next tile follows dV directly - dV is the only reader of P^T, which
+            // lives in the S^T columns - so the exponentials of tile t+1 run under dK, dQ of tile
+            // t; dP^T of the next tile comes last because (head size 128) it re-uses the dQ columns
+            // and has to wait until the dQ warps have read them.
+            auto issue_s = [&](int t) -> bool {
                 const int s = t & 1;
-                if (!mbar_wait(&q_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                if (!mbar_wait(&q_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) return false;
                 tc_fence_after_sync();
                 const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
-                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
-                // scores first, on their own barrier: the exponentials start while the previous
-                // tile's dQ is still being read out of the columns dP^T is going to use
 #pragma unroll
                 for (int kk = 0; kk < C::ROWB / 32; ++kk) {
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
@@ -180,13 +193,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                   smem_desc_sw128(q_addr + off, 16, 1024), idesc_st, kk > 0);
                 }
                 mma_commit(s_full);
-                if (t > 0) {
-                    // the previous dQ must be out of its TMEM columns (dP^T re-uses them when the
-                    // head size is 128) and out of the dS^T tile it is staged through (the softmax
-                    // warps rewrite that tile once dP^T is there)
-                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
-                    tc_fence_after_sync();
+                return true;
+            };
+            auto issue_dp = [&](int t) -> bool {
+                const int s = t & 1;
+                if (!mbar_wait(&do_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) return false;
+                if (t > 0 && C::DQ_ALIASES_DP) {
+                    // the previous dQ must be out of the TMEM columns that dP^T re-uses
+                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) return false;
                 }
+                tc_fence_after_sync();
+                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < C::ROWB / 32; ++kk) {
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
@@ -194,12 +211,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                   smem_desc_sw128(do_addr + off, 16, 1024), idesc_st, kk > 0);
                 }
                 mma_commit(dp_full);
+                return true;
+            };
+            bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutMma);
+            ok = ok && issue_s(0) && issue_dp(0);
+            for (int t = 0; t < n_q && ok; ++t) {
+                const int s = t & 1;
+                const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
+                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
                 if (!mbar_wait(ds_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
                     mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + (kk / 4) * 64 + (kk % 4) * 8,
                                   smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
+                if (t + 1 < n_q && !issue_s(t + 1)) { ok = false; break; }
+                if (t > 0 && !C::DQ_ALIASES_DP) {
+                    // dQ has columns of its own: only the next dQ MMA has to wait for the read-out
+                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    tc_fence_after_sync();
+                }
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk) {    // dK += dS^T . Q
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
@@ -210,8 +241,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dQ_i = dS . K        (K = 128 key rows)
                     mma_ss<false>(tmem_base + C::COL_DQ, smem_desc_mn(ds_addr + kk * 2048, kBoxBytes, false),
                                   smem_desc_mn(k_addr + kk * 2048, kBoxBytes, false), idesc_dq, kk > 0);
-                mma_commit(&q_empty[s]);
-                mma_commit(dq_full);
+                mma_commit(dq_full);      // also: this tile's Q and dO stage is no longer read
+                if (t + 1 < n_q && !issue_dp(t + 1)) { ok = false; break; }
             }
             if (ok) mma_commit(all_done);
         }
@@ -230,6 +261,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         uint8_t* ds_row = ds_smem + half * kBoxBytes + r * 128;     // box `half` holds query columns 64h..64h+63
         const int swz = r & 7;
         bool ok = true;
+        // threads 0..127 carry lse of query row (tid & 127), threads 128..255 delta
+        const float* stat_src = (tid256 < 128 ? p.lse : p.delta) + row_base + (tid256 & 127);
+        float stat_next = stat_src[(int64_t)i_begin * kTile];
         for (int t = 0; t < n_q; ++t) {
             const int i = i_begin + t;
             // Stage lse*log2e and delta of this query tile in the buffer of this tile's parity.
@@ -237,11 +271,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // tile in between, which needs that other thread to have left this tile.
             float* lse_s = stat_s + (t & 1) * 256;
             float* delta_s = lse_s + 128;
-            {
-                const int64_t g = (int64_t)row_base + (int64_t)i * kTile + (tid256 & 127);
-                if (tid256 < 128) lse_s[tid256] = -p.lse[g] * 1.4426950408889634f;     // -lse in the log2 domain
-                else delta_s[tid256 - 128] = -p.delta[g] * p.scale;                    // -delta / sqrt(hs)
-            }
+            // The value was fetched from global memory one tile earlier (a cold line would
+            // otherwise sit on the critical path between two tiles); fetch the next one now.
+            if (tid256 < 128) lse_s[tid256] = stat_next * -1.4426950408889634f;        // -lse in the log2 domain
+            else delta_s[tid256 - 128] = stat_next * -p.scale;                         // -delta / sqrt(hs)
+            if (t + 1 < n_q) stat_next = stat_src[(int64_t)(i + 1) * kTile];
             // One thread does each bounded wait and publishes the outcome, so that all 256 take
             // the same branch and nobody is left alone at a named barrier.
             if (tid256 == 0) softmax_ok[0] = mbar_wait(s_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
@@ -350,45 +384,58 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
     } else {
         // ---------------- dQ reduction: warps 10..13, thread = query row ----------------
-        // The dS^T tile in shared memory is idle between "dV, dK, dQ MMAs complete" and the
-        // next tile's dS^T, so it serves as staging: the dQ tile leaves tensor memory through
-        // it, two 128-row x 128-byte boxes at a time, and one thread hands each pair to the TMA
-        // unit as a reduce-add into the FP32 dQ buffer - full lines, no per-thread atomics.
+        // When the tile's MMAs are complete its Q / dO stage is idle and exactly as large as the
+        // FP32 dQ tile: HS/32 boxes of 128 rows x 128 bytes, the first half over Q, the second
+        // over dO.  The dQ tile leaves tensor memory through it; the TMEM columns are released as
+        // soon as they are read, and each half of the stage is refilled with the query tile two
+        // steps ahead as soon as the TMA unit has read it.
         const int lane_group = warp & 3;
         const int r = lane_group * 32 + lane;
         const int tid128 = (warp - 10) * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
-        uint8_t* stage_row = ds_smem + r * 128;
         const int swz = r & 7;
         for (int t = 0; t < n_q; ++t) {
+            const int s = t & 1;
             if (tid128 == 0) drain_ok[0] = mbar_wait(dq_full, t & 1, p.status, kTimeoutOther) ? 1u : 0u;
             named_barrier_sync(2, 128);
             if (drain_ok[0] == 0u) break;
             tc_fence_after_sync();
             const int y = row_base + (i_begin + t) * kTile;
-#pragma unroll 1
-            for (int pass = 0; pass < HS / 64; ++pass) {
+            const int y2 = y + C::Q_STAGES * kTile;
+            uint8_t* stage_q = q_smem + s * C::TILE_BYTES;
+            uint8_t* stage_do = do_smem + s * C::TILE_BYTES;
 #pragma unroll
-                for (int b = 0; b < 2; ++b) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_base + C::COL_DQ + lane_addr + (pass * 2 + b) * 32, v);
-                    tmem_wait_ld();
+            for (int b = 0; b < HS / 32; ++b) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + C::COL_DQ + lane_addr + b * 32, v);
+                tmem_wait_ld();
+                uint8_t* row = (b < C::NBOX ? stage_q + b * kBoxBytes : stage_do + (b - C::NBOX) * kBoxBytes) + r * 128;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        *reinterpret_cast<uint4*>(stage_row + b * kBoxBytes + ((u ^ swz) << 4)) =
-                            make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+                for (int u = 0; u < 8; ++u)
+                    *reinterpret_cast<uint4*>(row + ((u ^ swz) << 4)) =
+                        make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            named_barrier_sync(2, 128);                     // the whole tile is staged
+            if (tid128 == 0) {
+                mbar_arrive(dq_empty);                      // TMEM columns are free
+                const bool more = t + C::Q_STAGES < n_q;
+                for (int b = 0; b < C::NBOX; ++b) tma_reduce_add_2d(&map_dq, stage_q + b * kBoxBytes, b * 32, y);
+                tma_commit_group();
+                tma_wait_group_read0();                     // the Q half has been read: refill it
+                if (more) {
+                    mbar_arrive_expect_tx(&q_full[s], C::TILE_BYTES);
+                    for (int b = 0; b < C::NBOX; ++b) tma_load_2d(stage_q + b * kBoxBytes, &map_q, &q_full[s], b * 64, y2);
                 }
-                fence_proxy_async_smem();
-                tc_fence_before_sync();
-                named_barrier_sync(2, 128);                 // both boxes complete
-                if (tid128 == 0) {
-                    tma_reduce_add_2d(&map_dq, ds_smem, (pass * 2) * 32, y);
-                    tma_reduce_add_2d(&map_dq, ds_smem + kBoxBytes, (pass * 2 + 1) * 32, y);
-                    tma_commit_group();
-                    tma_wait_group_read0();                 // staging may be overwritten again
-                    if (pass == HS / 64 - 1) mbar_arrive(dq_empty);   // TMEM columns and staging are free
+                for (int b = 0; b < C::NBOX; ++b)
+                    tma_reduce_add_2d(&map_dq, stage_do + b * kBoxBytes, (C::NBOX + b) * 32, y);
+                tma_commit_group();
+                tma_wait_group_read0();
+                if (more) {
+                    mbar_arrive_expect_tx(&do_full[s], C::TILE_BYTES);
+                    for (int b = 0; b < C::NBOX; ++b) tma_load_2d(stage_do + b * kBoxBytes, &map_do, &do_full[s], b * 64, y2);
                 }
-                named_barrier_sync(2, 128);
             }
         }
         if (tid128 == 0) tma_wait_group0();                 // all adds have landed before the CTA ends
