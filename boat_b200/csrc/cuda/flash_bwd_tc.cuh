@@ -9,29 +9,30 @@
 // stay in shared memory, dK and dV accumulate in tensor memory for the whole walk.  Per
 // query tile, with everything transposed so that key rows sit on the TMEM lanes:
 //
-//   S^T  = K . Q^T            dP^T = V . dO^T                   two SS MMAs
-//   P^T  = exp2(S^T*c - lse)  dS^T = P^T * (dP^T - delta) / sqrt(hs)
-//                                                               8 softmax warps, thread = key row x half
-//   dV  += P^T . dO           A = P^T in tensor memory (written over S^T)
-//   dK  += dS^T . Q           A = dS^T from shared memory (K-major view)
-//   dQ_i = dS . K             A = the same shared-memory tile read along M (MN-major view)
+//   S^T  = K . Q^T                                              SS MMA into region R0
+//   P^T  = exp2(S^T*c - lse)        phase A, 8 softmax warps, written over S^T in R0 (BF16)
+//   dV  += P^T . dO                 A = P^T in tensor memory
+//   dP^T = V . dO^T                 SS MMA into R0 again, behind dV on the in-order tensor pipe
+//   dS^T = P^T * (dP^T - delta) / sqrt(hs)    phase B; P^T is kept in registers, dS^T goes to smem
+//   dK  += dS^T . Q                 A = dS^T from shared memory (K-major view)
+//   dQ_i = dS . K                   A = the same shared-memory tile read along M (MN-major view)
+//
+// Tensor memory (512 columns): R0 = S^T / P^T / dP^T (128), dQ (HS), dV (HS), dK (HS).  dP^T
+// shares columns with the scores rather than with dQ, so reading dQ out never holds up the next
+// tile, and S^T of tile t+1 is issued as soon as the softmax warps have loaded dP^T of tile t:
+// it executes while they compute dS^T, and the exponentials of tile t+1 then overlap the dK and
+// dQ MMAs of tile t.  The softmax warps are the critical resource (A, wait for dV and dP^T, B).
 //
 // dQ of a query tile gets one contribution per key tile; CTAs add theirs into an FP32 buffer
 // with TMA reduce-add (cp.reduce.async.bulk.tensor), and a cast kernel turns the sum into the
-// output type afterwards.  Four dedicated warps move the dQ tile out of tensor memory into
-// the Q / dO shared-memory stage that the tile's MMAs have just finished with (the FP32 dQ
-// tile is exactly as large as the BF16 Q and dO tiles together) and release the TMEM columns
-// at once.  An SM gets reductions out at only about 20 bytes per clock (measured alike for
-// TMA reduce-add and for red.global.add.v4.f32, which also stalls the softmax warps' shared
-// memory traffic), so the 64 KB of a tile keep the TMA unit busy for ~3000 cycles, and the
-// unit works in order: the thread that issues the reductions therefore also issues the loads
-// of the query tile two steps ahead, Q between the two halves of the reduction and dO after
-// it, so that no load queues behind a reduction it does not depend on.  With head size 128
-// the 512 TMEM columns are exactly S^T/P^T, dP^T (reused for dQ), dV and dK.
-// Warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store (two warps
-// per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.  The score MMA of the
-// next tile is issued right behind dV of the current one and signals on its own barrier, so
-// the exponentials of tile t+1 overlap the dK and dQ MMAs of tile t.
+// output type afterwards.  Four dedicated warps move the dQ tile out of tensor memory through
+// the tile's dO stage, which is idle once the tile's MMAs are complete, half a tile at a time;
+// the thread that issues the reductions then loads the dO tile two steps ahead into it.  An SM
+// gets reductions out at only about 20 bytes per clock (measured alike for TMA reduce-add and
+// for red.global.add.v4.f32, which also stalls the softmax warps' shared memory traffic), so
+// the read-out of a tile takes most of a tile period - off the critical path.
+// Warp 0: TMA producer (K, V, Q), warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store
+// (two warps per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.
 #pragma once
 #include "flash_fwd_tc.cuh"
 
@@ -52,9 +53,8 @@ struct BwdCfg {
     // from the launch (checked at kernel entry) - there is no room for manual alignment slack.
     static constexpr int SMEM = 2 * TILE_BYTES + Q_STAGES * 2 * TILE_BYTES + DS_BYTES + 2048 + 256;
     // tensor memory columns
-    static constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + HS;
-    static constexpr bool DQ_ALIASES_DP = (256 + 3 * HS) > 512;
-    static constexpr uint32_t COL_DQ = DQ_ALIASES_DP ? COL_DP : 256 + 2 * HS;
+    static constexpr uint32_t COL_S = 0, COL_DP = 0;          // R0: S^T, then P^T, then dP^T
+    static constexpr uint32_t COL_DQ = 128, COL_DV = 128 + HS, COL_DK = 128 + 2 * HS;
     static constexpr uint32_t TMEM_COLS = 512;
 };
 
@@ -100,12 +100,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t* kv_full = bars;                   // 1
     uint64_t* q_full = bars + 1;                // [2] Q tile landed
     uint64_t* s_full = bars + 5;                // S^T complete
-    uint64_t* ds_full = bars + 6;               // P^T in TMEM, dS^T in smem (256 arrivals)
-    uint64_t* dq_full = bars + 7;               // dV, dK, dQ MMAs of the tile complete
+    uint64_t* ds_full = bars + 6;               // dS^T in smem (256 arrivals)
+    uint64_t* dq_full = bars + 7;               // all MMAs of the tile complete
     uint64_t* dq_empty = bars + 8;              // dQ is out of its TMEM columns
     uint64_t* all_done = bars + 9;
     uint64_t* dp_full = bars + 10;              // dP^T complete
     uint64_t* do_full = bars + 11;              // [2] dO tile landed
+    uint64_t* q_empty = bars + 13;              // [2] S^T and dK of the tile are complete: its Q stage is free
+    uint64_t* p_full = bars + 3;                // P^T in TMEM (256 arrivals)
+    uint64_t* r0_free = bars + 4;               // dP^T loaded into registers (256 arrivals)
     uint32_t* tmem_slot = (uint32_t*)(bars + 15);
     volatile uint32_t* softmax_ok = tmem_slot + 1;     // [2] written by one softmax thread, read by all 256
     volatile uint32_t* drain_ok = tmem_slot + 3;       // same idea for the dQ warps
@@ -128,9 +131,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int s = 0; s < 2; ++s) {
             mbar_init(&q_full[s], 1);
             mbar_init(&do_full[s], 1);
+            mbar_init(&q_empty[s], 1);
         }
         mbar_init(s_full, 1);
         mbar_init(ds_full, 256);
+        mbar_init(p_full, 256);
+        mbar_init(r0_free, 256);
         mbar_init(dp_full, 1);
         mbar_init(dq_full, 1);
         mbar_init(dq_empty, 1);
@@ -156,16 +162,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tma_load_2d(k_smem + b * kBoxBytes, &map_k, kv_full, b * 64, row_base + jt * kTile);
                 tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jt * kTile);
             }
-            // the first two query tiles; later ones are loaded by the dQ warps, which stage dQ
-            // through these buffers and know when one is free again
+            // dO of the first two query tiles; later ones are loaded by the dQ warps, which stage
+            // dQ through the dO buffers and know when one is free again
             for (int t = 0; t < n_q && t < C::Q_STAGES; ++t) {
-                const int y = row_base + (i_begin + t) * kTile;
-                mbar_arrive_expect_tx(&q_full[t], C::TILE_BYTES);
-                for (int b = 0; b < C::NBOX; ++b)
-                    tma_load_2d(q_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[t], b * 64, y);
                 mbar_arrive_expect_tx(&do_full[t], C::TILE_BYTES);
                 for (int b = 0; b < C::NBOX; ++b)
-                    tma_load_2d(do_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_do, &do_full[t], b * 64, y);
+                    tma_load_2d(do_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_do, &do_full[t], b * 64,
+                                row_base + (i_begin + t) * kTile);
+            }
+            for (int t = 0; t < n_q; ++t) {
+                const int s = t & 1;
+                if (!mbar_wait(&q_empty[s], ((t >> 1) & 1) ^ 1, p.status, kTimeoutProducer)) break;
+                mbar_arrive_expect_tx(&q_full[s], C::TILE_BYTES);
+                for (int b = 0; b < C::NBOX; ++b)
+                    tma_load_2d(q_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[s], b * 64,
+                                row_base + (i_begin + t) * kTile);
             }
         }
     } else if (warp == 1) {
@@ -175,12 +186,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             constexpr uint32_t idesc_acc = make_idesc(kBF16, false, true, kTile, HS);      // dV, dK
             constexpr uint32_t idesc_dq = make_idesc(kBF16, true, true, kTile, HS);        // dQ
             const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
-            // Issue order on the (in-order) tensor pipe:
-            //   S(0) dP(0) | dV(t) S(t+1) dK(t) dQ(t) dP(t+1) | ...
-            // S^T of the next tile follows dV directly - dV is the only reader of P^T, which
-            // lives in the S^T columns - so the exponentials of tile t+1 run under dK, dQ of tile
-            // t; dP^T of the next tile comes last because (head size 128) it re-uses the dQ columns
-            // and has to wait until the dQ warps have read them.
+            // Issue order on the (in-order) tensor pipe, per tile t:
+            //   dV(t) dP(t) | S(t+1) | dK(t) dQ(t)
+            // dV and dP^T follow phase A; dP^T overwrites P^T in R0, which dV, ahead of it on the
+            // pipe, is the only reader of.  S^T of the next tile overwrites dP^T once the softmax
+            // warps hold it in registers; dK and dQ need dS^T from phase B.
             auto issue_s = [&](int t) -> bool {
                 const int s = t & 1;
                 if (!mbar_wait(&q_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) return false;
@@ -195,42 +205,36 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 mma_commit(s_full);
                 return true;
             };
-            auto issue_dp = [&](int t) -> bool {
-                const int s = t & 1;
-                if (!mbar_wait(&do_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) return false;
-                if (t > 0 && C::DQ_ALIASES_DP) {
-                    // the previous dQ must be out of the TMEM columns that dP^T re-uses
-                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) return false;
-                }
-                tc_fence_after_sync();
-                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < C::ROWB / 32; ++kk) {
-                    const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-                    mma_ss<false>(tmem_base + C::COL_DP, smem_desc_sw128(v_addr + off, 16, 1024),
-                                  smem_desc_sw128(do_addr + off, 16, 1024), idesc_st, kk > 0);
-                }
-                mma_commit(dp_full);
-                return true;
-            };
             bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutMma);
-            ok = ok && issue_s(0) && issue_dp(0);
+            ok = ok && issue_s(0);
             for (int t = 0; t < n_q && ok; ++t) {
                 const int s = t & 1;
                 const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
                 const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
-                if (!mbar_wait(ds_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                if (!mbar_wait(p_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                if (!mbar_wait(&do_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
                     mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + (kk / 4) * 64 + (kk % 4) * 8,
                                   smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
-                if (t + 1 < n_q && !issue_s(t + 1)) { ok = false; break; }
-                if (t > 0 && !C::DQ_ALIASES_DP) {
-                    // dQ has columns of its own: only the next dQ MMA has to wait for the read-out
-                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
-                    tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < C::ROWB / 32; ++kk) {  // dP^T = V . dO^T
+                    const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
+                    mma_ss<false>(tmem_base + C::COL_DP, smem_desc_sw128(v_addr + off, 16, 1024),
+                                  smem_desc_sw128(do_addr + off, 16, 1024), idesc_st, kk > 0);
                 }
+                mma_commit(dp_full);
+                if (t + 1 < n_q) {
+                    if (!mbar_wait(r0_free, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    if (!issue_s(t + 1)) { ok = false; break; }
+                }
+                if (!mbar_wait(ds_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                if (t > 0) {
+                    // the previous dQ must have left its TMEM columns
+                    if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                }
+                tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk) {    // dK += dS^T . Q
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
@@ -241,8 +245,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dQ_i = dS . K        (K = 128 key rows)
                     mma_ss<false>(tmem_base + C::COL_DQ, smem_desc_mn(ds_addr + kk * 2048, kBoxBytes, false),
                                   smem_desc_mn(k_addr + kk * 2048, kBoxBytes, false), idesc_dq, kk > 0);
-                mma_commit(dq_full);      // also: this tile's Q and dO stage is no longer read
-                if (t + 1 < n_q && !issue_dp(t + 1)) { ok = false; break; }
+                mma_commit(&q_empty[s]);
+                mma_commit(dq_full);      // also: this tile's dO stage and the dS^T tile are no longer read
             }
             if (ok) mma_commit(all_done);
         }
@@ -321,6 +325,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 // P^T over this thread's own S^T columns: 64 BF16 = 32 columns starting at col0
                 tmem_st32(tmem_base + C::COL_S + lane_addr + col0, ph);
             }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(p_full);
             // ---- phase B: dS^T = P^T * (dP^T - delta) / sqrt(hs) ----
             if (tid256 == 0) softmax_ok[1] = mbar_wait(dp_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
             named_barrier_sync(1, 256);
@@ -331,6 +338,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0, d0);
                 tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0 + 32, d1);
                 tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(r0_free);                        // R0 may take the next tile's scores
 #pragma unroll
                 for (int half32 = 0; half32 < 2; ++half32) {
 #pragma unroll
@@ -355,9 +364,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     }
                 }
             }
-            tmem_wait_st();
             fence_proxy_async_smem();
-            tc_fence_before_sync();
             mbar_arrive(ds_full);
         }
         // final: the first four warps store dV, the other four dK
@@ -384,11 +391,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
     } else {
         // ---------------- dQ reduction: warps 10..13, thread = query row ----------------
-        // When the tile's MMAs are complete its Q / dO stage is idle and exactly as large as the
-        // FP32 dQ tile: HS/32 boxes of 128 rows x 128 bytes, the first half over Q, the second
-        // over dO.  The dQ tile leaves tensor memory through it; the TMEM columns are released as
-        // soon as they are read, and each half of the stage is refilled with the query tile two
-        // steps ahead as soon as the TMA unit has read it.
+        // The FP32 dQ tile is HS/32 boxes of 128 rows x 128 bytes, twice the size of the tile's dO
+        // stage, which is idle once the tile's MMAs are complete: two passes through it, the
+        // second half waiting in registers meanwhile.  After the second pass the same thread
+        // loads the dO tile two steps ahead into the stage.
         const int lane_group = warp & 3;
         const int r = lane_group * 32 + lane;
         const int tid128 = (warp - 10) * 32 + lane;
@@ -401,40 +407,50 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (drain_ok[0] == 0u) break;
             tc_fence_after_sync();
             const int y = row_base + (i_begin + t) * kTile;
-            const int y2 = y + C::Q_STAGES * kTile;
-            uint8_t* stage_q = q_smem + s * C::TILE_BYTES;
-            uint8_t* stage_do = do_smem + s * C::TILE_BYTES;
+            uint8_t* stage = do_smem + s * C::TILE_BYTES;
+            auto stage_half = [&](const uint32_t (&v)[C::NBOX][32]) {
 #pragma unroll
-            for (int b = 0; b < HS / 32; ++b) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + C::COL_DQ + lane_addr + b * 32, v);
-                tmem_wait_ld();
-                uint8_t* row = (b < C::NBOX ? stage_q + b * kBoxBytes : stage_do + (b - C::NBOX) * kBoxBytes) + r * 128;
+                for (int b = 0; b < C::NBOX; ++b) {
+                    uint8_t* row = stage + b * kBoxBytes + r * 128;
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    *reinterpret_cast<uint4*>(row + ((u ^ swz) << 4)) =
-                        make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
-            }
-            fence_proxy_async_smem();
-            tc_fence_before_sync();
-            named_barrier_sync(2, 128);                     // the whole tile is staged
-            if (tid128 == 0) {
-                mbar_arrive(dq_empty);                      // TMEM columns are free
-                const bool more = t + C::Q_STAGES < n_q;
-                for (int b = 0; b < C::NBOX; ++b) tma_reduce_add_2d(&map_dq, stage_q + b * kBoxBytes, b * 32, y);
-                tma_commit_group();
-                tma_wait_group_read0();                     // the Q half has been read: refill it
-                if (more) {
-                    mbar_arrive_expect_tx(&q_full[s], C::TILE_BYTES);
-                    for (int b = 0; b < C::NBOX; ++b) tma_load_2d(stage_q + b * kBoxBytes, &map_q, &q_full[s], b * 64, y2);
+                    for (int u = 0; u < 8; ++u)
+                        *reinterpret_cast<uint4*>(row + ((u ^ swz) << 4)) =
+                            make_uint4(v[b][4 * u], v[b][4 * u + 1], v[b][4 * u + 2], v[b][4 * u + 3]);
                 }
+                fence_proxy_async_smem();
+            };
+            uint32_t v[C::NBOX][32];
+            // first half: tensor memory -> registers -> stage -> TMA reduce-add
+#pragma unroll
+            for (int b = 0; b < C::NBOX; ++b) tmem_ld32(tmem_base + C::COL_DQ + lane_addr + b * 32, v[b]);
+            tmem_wait_ld();
+            stage_half(v);
+            named_barrier_sync(2, 128);
+            if (tid128 == 0) {
+                for (int b = 0; b < C::NBOX; ++b) tma_reduce_add_2d(&map_dq, stage + b * kBoxBytes, b * 32, y);
+                tma_commit_group();
+            }
+            // second half waits in registers while the TMA unit reads the first; the TMEM columns
+            // are free as soon as it is loaded
+#pragma unroll
+            for (int b = 0; b < C::NBOX; ++b)
+                tmem_ld32(tmem_base + C::COL_DQ + lane_addr + (C::NBOX + b) * 32, v[b]);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            if (tid128 == 0) tma_wait_group_read0();
+            named_barrier_sync(2, 128);                     // all loads done; the stage has been read
+            if (tid128 == 0) mbar_arrive(dq_empty);
+            stage_half(v);
+            named_barrier_sync(2, 128);
+            if (tid128 == 0) {
                 for (int b = 0; b < C::NBOX; ++b)
-                    tma_reduce_add_2d(&map_dq, stage_do + b * kBoxBytes, (C::NBOX + b) * 32, y);
+                    tma_reduce_add_2d(&map_dq, stage + b * kBoxBytes, (C::NBOX + b) * 32, y);
                 tma_commit_group();
                 tma_wait_group_read0();
-                if (more) {
+                if (t + C::Q_STAGES < n_q) {
                     mbar_arrive_expect_tx(&do_full[s], C::TILE_BYTES);
-                    for (int b = 0; b < C::NBOX; ++b) tma_load_2d(stage_do + b * kBoxBytes, &map_do, &do_full[s], b * 64, y2);
+                    for (int b = 0; b < C::NBOX; ++b)
+                        tma_load_2d(stage + b * kBoxBytes, &map_do, &do_full[s], b * 64, y + C::Q_STAGES * kTile);
                 }
             }
         }
