@@ -65,6 +65,7 @@ struct BwdParams {
     void* dK;
     void* dV;
     int S, units, causal;
+    int group;             // units scheduled together, see the kernel
     float scale;
     unsigned int* status;
 };
@@ -115,13 +116,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = p.S / kTile;
-    // Unit-major order: the CTAs that run at the same time belong to two or three (batch, head)
-    // units, so the FP32 dQ rows they reduce into (S*HS*4 bytes per unit) stay in L2.  With key
-    // tiles as the slow index every unit is active at once, the dQ buffer of a large problem
-    // (268 MB at 64 units x 8192 x 128) no longer fits, and each reduction misses to HBM.
-    // Inside a unit small jt (the long walk when causal) comes first.
-    const int unit = blockIdx.x / n_tiles;
-    const int jt = blockIdx.x % n_tiles;
+    // CTA order: units in groups of p.group; inside a group the key tile is the slow index.
+    // The CTAs that run at the same time then belong to a few (batch, head) units, so the FP32 dQ
+    // rows they reduce into (S*HS*4 bytes per unit) and the unit's Q and dO stay in L2 - with
+    // key tiles as the slow index over all units, the dQ buffer of a large problem (268 MB at 64
+    // units x 8192 x 128) no longer fits and every reduction misses to HBM.  Small jt (the long
+    // walk when causal) comes first, so a group ends with its short CTAs.
+    const int per_group = p.group * n_tiles;
+    const int grp = blockIdx.x / per_group;
+    const int rem = blockIdx.x - grp * per_group;
+    const int in_group = min(p.group, p.units - grp * p.group);
+    const int jt = rem / in_group;
+    const int unit = grp * p.group + rem % in_group;
     const int i_begin = p.causal ? jt : 0;
     const int n_q = n_tiles - i_begin;
     const int row_base = unit * p.S;

@@ -84,6 +84,10 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     p.S = (int)S;
     p.units = (int)units;
     p.causal = causal;
+    // units whose dQ (FP32), Q, dO, K and V - 16 bytes per element of the unit - share L2 at a time
+    const int64_t unit_bytes = S * HS * 16;
+    int64_t group = (64ll << 20) / unit_bytes;
+    p.group = (int)(group < 1 ? 1 : (group > units ? units : group));
     p.scale = scale;
     p.status = kernel_status_ptr();
     auto kern = flash_bwd_kernel<HS>;
