@@ -253,6 +253,11 @@ def main():
         run_reference_arm(args, cfg, rank, world)
         return
     args.warmup = max(args.warmup, 3)
+    # Libraries underneath (NCCL prints its version banner on stdout) must not get between the
+    # caller and the one JSON line: everything but that line goes to stderr.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
 
     import torch
     import boat_b200
@@ -470,7 +475,8 @@ def main():
                     tflops_per_gpu=tflops_per_gpu,
                     frac_of_bf16_peak=(tflops_per_gpu / peaks["bf16_sustained"]) if bf16 else None,
                     roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches), clocks=clocks)
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
         check(lib.boat_cuda_comm_destroy(), "comm_destroy")
         dist.destroy_process_group()

@@ -118,6 +118,11 @@ PROTOTYPES = {
     "boat_variable_backward": (None, [_P, _P]),
     "boat_variable_backward_full": (None, [_P]),
     "boat_var_attention": (_P, [_P, _P, _P, _P, _P]),
+    "boat_var_add": (_P, [_P, _P]),
+    "boat_var_sub": (_P, [_P, _P]),
+    "boat_var_mul": (_P, [_P, _P]),
+    "boat_var_matmul": (_P, [_P, _P]),
+    "boat_var_dense": (_P, [_P, _P]),
     # include/boat/ops.h
     "boat_add": (_P, [_P, _P]),
     "boat_mul": (_P, [_P, _P]),

@@ -183,6 +183,66 @@ class Attention:
             pass
 
 
+class Variable:
+    """boat_variable_t: a tensor with gradient tracking.  Ops return new Variables; inputs are
+    borrowed by the op records, so keep them alive until backward has run (held in _inputs)."""
+
+    def __init__(self, tensor=None, requires_grad=True, handle=None, inputs=()):
+        lib = capi.load()
+        h = handle if handle is not None else lib.boat_variable_create(tensor.h, requires_grad)
+        if not h:
+            raise BoatError("NULL variable: " + (lib.boat_cuda_last_error() or b"").decode())
+        self.h = C.c_void_p(h)
+        self._inputs = tuple(inputs) + ((tensor,) if tensor is not None else ())
+
+    def _op(self, name, other):
+        return Variable(handle=getattr(capi.load(), name)(self.h, other.h), inputs=(self, other))
+
+    def __add__(self, other):
+        return self._op("boat_var_add", other)
+
+    def __sub__(self, other):
+        return self._op("boat_var_sub", other)
+
+    def __mul__(self, other):
+        return self._op("boat_var_mul", other)
+
+    def __matmul__(self, other):
+        return self._op("boat_var_matmul", other)
+
+    def dense(self, layer):
+        return Variable(handle=capi.load().boat_var_dense(self.h, layer.h), inputs=(self, layer))
+
+    def attention(self, layer, key=None, value=None):
+        key = self if key is None else key
+        value = self if value is None else value
+        return Variable(handle=capi.load().boat_var_attention(self.h, key.h, value.h, layer.h, None),
+                        inputs=(self, key, value, layer))
+
+    def backward(self, grad=None):
+        capi.load().boat_variable_backward(self.h, grad.h if grad is not None else None)
+
+    @property
+    def data(self):
+        return Tensor(capi.load().boat_variable_data(self.h), own=False)
+
+    @property
+    def grad(self):
+        h = capi.load().boat_variable_grad(self.h)
+        return Tensor(h, own=False) if h else None
+
+    def free(self):
+        if self.h:
+            capi.load().boat_variable_free(self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Adam:
     """boat_optimizer_t made by boat_adam_optimizer_create.  Registered tensors are borrowed:
     keep them alive while the optimizer is."""

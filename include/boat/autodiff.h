@@ -1,11 +1,14 @@
-/* autodiff.h - variables and reverse-mode differentiation, attention op only.
+/* autodiff.h - variables and reverse-mode differentiation for the attention path.
  *
- * Subset of the reference's include/boat/autodiff.h:25-66 that reaches the attention
- * layer: variable create/free/accessors, boat_var_attention and boat_variable_backward
- * (reference implementation: src/autodiff.c:138-463, :569-572, :2388-2532).  The
- * reference keeps op nodes in a generic graph library; here a variable simply points at
- * the op record that produced it, which is all reverse mode needs for this path.  The
- * other 17 op types of the reference are outside this path and are not provided. */
+ * Subset of the reference's include/boat/autodiff.h:25-66: variable create/free/accessors,
+ * boat_variable_backward, the attention op and the ops an encoder block puts next to it -
+ * add, sub, mul, matmul and the dense-layer op (reference implementation:
+ * src/autodiff.c:138-572, :1002-1180, :1454-1496, :2388-2672).  Every op accepts host or
+ * CUDA tensors; with CUDA tensors the graph never leaves the GPU.  The reference keeps op
+ * nodes in a generic graph library; here a variable simply points at the op record that
+ * produced it, which is all reverse mode needs.  The reference's other op types (div, dot,
+ * relu, sigmoid, tanh, softmax, reductions, conv, pool, flatten) are outside this path and
+ * are not provided. */
 #ifndef BOAT_AUTODIFF_H
 #define BOAT_AUTODIFF_H
 
@@ -18,6 +21,7 @@ extern "C" {
 
 typedef struct boat_variable_t boat_variable_t;
 struct boat_attention_t;
+struct boat_dense_layer_t;
 
 /* The variable takes its own reference on `tensor` (autodiff.c:152-153). */
 BOAT_API boat_variable_t* boat_variable_create(boat_tensor_t* tensor, bool requires_grad);
@@ -37,6 +41,19 @@ BOAT_API void boat_variable_zero_grad(boat_variable_t* variable);              /
  * ends with dq+dk+dv (autodiff.c:2482-2526). */
 BOAT_API void boat_variable_backward(boat_variable_t* variable, boat_tensor_t* grad_output);
 BOAT_API void boat_variable_backward_full(const boat_variable_t* variable);
+
+/* Element-wise ops on equal shapes and the 2-D matrix product, with gradient tracking
+ * (autodiff.c:466-499).  Backward: add da=db=g; sub da=g, db=-g; mul da=g*b, db=g*a;
+ * matmul dA=g.B^T, dB=A^T.g. */
+BOAT_API boat_variable_t* boat_var_add(const boat_variable_t* a, const boat_variable_t* b);
+BOAT_API boat_variable_t* boat_var_sub(const boat_variable_t* a, const boat_variable_t* b);
+BOAT_API boat_variable_t* boat_var_mul(const boat_variable_t* a, const boat_variable_t* b);
+BOAT_API boat_variable_t* boat_var_matmul(const boat_variable_t* a, const boat_variable_t* b);
+
+/* Forward through a dense layer ([N, in] input); backward runs boat_dense_layer_backward,
+ * which accumulates the layer's dW and db, and adds dx to the input's gradient
+ * (autodiff.c:563-567, :2640-2672).  The layer stays owned by the caller. */
+BOAT_API boat_variable_t* boat_var_dense(const boat_variable_t* input, const struct boat_dense_layer_t* layer);
 
 /* Forward through `attention` with gradient tracking.  The layer stays owned by the
  * caller: freeing variables never frees the layer (the reference's op-node destructor

@@ -469,3 +469,80 @@ def ref_adam(params, grads_per_step, lr, beta1, beta2, eps):
     for h in hp + hg:
         lib.boat_tensor_unref(h)
     return out
+
+
+# ---- autodiff graphs through the reference library --------------------------------------------------------
+
+def _ref_autodiff():
+    lib = ref()
+    if not getattr(lib, "_autodiff_typed", False):
+        P = C.c_void_p
+        lib.boat_variable_create.restype = P
+        lib.boat_variable_create.argtypes = [P, C.c_bool]
+        for name in ("boat_variable_data", "boat_variable_grad"):
+            getattr(lib, name).restype = P
+            getattr(lib, name).argtypes = [P]
+        lib.boat_variable_backward.argtypes = [P, P]
+        for name in ("boat_var_add", "boat_var_sub", "boat_var_mul", "boat_var_matmul", "boat_var_dense"):
+            getattr(lib, name).restype = P
+            getattr(lib, name).argtypes = [P, P]
+        lib.boat_var_attention.restype = P
+        lib.boat_var_attention.argtypes = [P] * 5
+        lib.boat_dense_layer_create.restype = P
+        lib.boat_dense_layer_create.argtypes = [C.c_size_t, C.c_size_t, C.c_bool]
+        for name in ("weight", "bias", "grad_weight", "grad_bias"):
+            fn = getattr(lib, "boat_dense_layer_get_" + name)
+            fn.restype = P
+            fn.argtypes = [P]
+        lib._autodiff_typed = True
+    return lib
+
+
+def ref_graph_residual_attention(x, w, b, nh, causal, gout):
+    """r = add(attention(x, x, x), x) through the reference's autodiff (boat_var_attention,
+    boat_var_add, boat_variable_backward with upstream gradient gout).  Variables and op nodes are
+    left to the process: the reference's node destructor frees the layer it points at."""
+    lib = _ref_autodiff()
+    x = _f32(x)
+    layer = RefLayer(x.shape[2], nh, causal, w, b)
+    with _quiet_scratch_cwd():
+        vx = lib.boat_variable_create(_ref_new(lib, x), True)
+        vh = lib.boat_var_attention(vx, vx, vx, layer.h, None)
+        vr = lib.boat_var_add(vh, vx)
+        res = {"out": RefTensor(lib, lib.boat_variable_data(vr)).view(x.shape).copy()}
+        lib.boat_variable_backward(vr, _ref_new(lib, _f32(gout)))
+        res["dx"] = RefTensor(lib, lib.boat_variable_grad(vx)).view(x.shape).copy()
+        H = x.shape[2]
+        res["dw"] = [RefTensor(lib, getattr(lib, "boat_attention_get_grad_weight_" + p)(layer.h)).view((H, H)).copy()
+                     for p in "qkvo"]
+        res["db"] = [RefTensor(lib, getattr(lib, "boat_attention_get_grad_bias_" + p)(layer.h)).view((H,)).copy()
+                     for p in "qkvo"]
+    return res
+
+
+def ref_graph_mlp(a, wm, wd, bd, c, m, gout):
+    """z = sub(mul(dense(matmul(a, wm)), m), c) through the reference's autodiff; every leaf
+    requires a gradient."""
+    lib = _ref_autodiff()
+    a, wm, wd, c, m = (_f32(t) for t in (a, wm, wd, c, m))
+    with _quiet_scratch_cwd():
+        dense = lib.boat_dense_layer_create(wd.shape[0], wd.shape[1], bd is not None)
+        RefTensor(lib, lib.boat_dense_layer_get_weight(dense)).view()[:] = wd.ravel()
+        if bd is not None:
+            RefTensor(lib, lib.boat_dense_layer_get_bias(dense)).view()[:] = _f32(bd)
+        va = lib.boat_variable_create(_ref_new(lib, a), True)
+        vw = lib.boat_variable_create(_ref_new(lib, wm), True)
+        vc = lib.boat_variable_create(_ref_new(lib, c), True)
+        vm = lib.boat_variable_create(_ref_new(lib, m), True)
+        v1 = lib.boat_var_matmul(va, vw)
+        v2 = lib.boat_var_dense(v1, dense)
+        v3 = lib.boat_var_mul(v2, vm)
+        vz = lib.boat_var_sub(v3, vc)
+        res = {"out": RefTensor(lib, lib.boat_variable_data(vz)).view(c.shape).copy()}
+        lib.boat_variable_backward(vz, _ref_new(lib, _f32(gout)))
+        for name, v, like in (("da", va, a), ("dwm", vw, wm), ("dc", vc, c), ("dm", vm, m)):
+            res[name] = RefTensor(lib, lib.boat_variable_grad(v)).view(like.shape).copy()
+        res["dwd"] = RefTensor(lib, lib.boat_dense_layer_get_grad_weight(dense)).view(wd.shape).copy()
+        if bd is not None:
+            res["dbd"] = RefTensor(lib, lib.boat_dense_layer_get_grad_bias(dense)).view((wd.shape[1],)).copy()
+    return res

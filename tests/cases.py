@@ -130,3 +130,15 @@ def adam_inputs(shapes=((33, 17), (4096 + 5,), (7,), (64, 64)), steps=6, stream=
             gs.append(g)
         grads.append(gs)
     return params, grads
+
+
+# ---- autodiff graphs: seeded inputs for the golden vectors and tests ---------------------------------------
+
+GRAPH_CASE = Case("graph_residual", B=2, S=24, H=32, nh=4, causal=True, bias_std=0.1)
+
+
+def graph_mlp_inputs(N=19, I=24, M=40, O=16):
+    """z = sub(mul(dense(matmul(a, wm)), m), c): a [N,I], wm [I,M], dense M -> O, m and c [N,O]."""
+    return dict(a=rng.normal(SEED, 60, (N, I)), wm=rng.normal(SEED, 61, (I, M), 0.2), wd=rng.normal(SEED, 62, (M, O), 0.2),
+                bd=rng.normal(SEED, 63, (O,), 0.1), c=rng.normal(SEED, 64, (N, O)), m=rng.normal(SEED, 65, (N, O)),
+                gout=rng.normal(SEED, 66, (N, O)))

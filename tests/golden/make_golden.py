@@ -1,4 +1,5 @@
-"""Regenerate tests/golden/attention_golden.npz and adam_golden.npz from the reference itself.
+"""Regenerate tests/golden/attention_golden.npz, adam_golden.npz and graph_golden.npz from the
+reference itself.
 
 Run in a checkout that has the reference tree (oracle/Makefile builds
 oracle/_ref/libboat_ref.so from it):
@@ -10,6 +11,10 @@ accumulating backward calls) on the seeded inputs of tests/cases.py.
 
 adam_golden.npz holds the parameters after every step of the reference's Adam optimizer
 (boat_adam_optimizer_create / boat_optimizer_step) on cases.adam_inputs().
+
+graph_golden.npz holds outputs and gradients of two graphs run through the reference's
+autodiff (boat_var_attention + boat_var_add; boat_var_matmul, boat_var_dense, boat_var_mul,
+boat_var_sub) with boat_variable_backward.
 
 For every case in tests/cases.py::GOLDEN_CASES the reference's own boat_attention_forward
 and boat_attention_backward are executed on the seeded inputs and every output and gradient
@@ -73,5 +78,25 @@ def main():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def graphs():
+    out = {}
+    case = cases.GRAPH_CASE
+    inp = case.inputs()
+    res = oracle.ref_graph_residual_attention(inp["q"], inp["w"], inp["b"], case.nh, case.causal, inp["dout"])
+    for key in ("out", "dx"):
+        out["residual/" + key] = res[key]
+    for i, p in enumerate("qkvo"):
+        out["residual/dw" + p] = res["dw"][i]
+        out["residual/db" + p] = res["db"][i]
+    g = cases.graph_mlp_inputs()
+    res = oracle.ref_graph_mlp(g["a"], g["wm"], g["wd"], g["bd"], g["c"], g["m"], g["gout"])
+    for key, val in res.items():
+        out["mlp/" + key] = val
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "graph_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     main()
+    graphs()
