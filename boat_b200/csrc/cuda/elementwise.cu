@@ -10,10 +10,13 @@ namespace boatcu {
 static const int kThreads = 256;
 static const int kSMs = 148;
 
+// One CTA per 256 work items, no persistent cap: for these streaming kernels the hardware's
+// CTA scheduler balances better than a grid-stride loop over 8 CTAs per SM (measured on the
+// Adam step: 6.3 TB/s against 5.3 TB/s).  The kernels keep their grid-stride loops, so the
+// limit of the grid's x dimension only matters beyond 2^31 * 256 items.
 static inline int grid_for(int64_t work_items, int per_block) {
     int64_t blocks = ceil_div(work_items, per_block);
-    int64_t cap = (int64_t)kSMs * 8;           // 8 resident CTAs of 256 threads per SM
-    if (blocks > cap) blocks = cap;
+    if (blocks > 0x7fffffffLL) blocks = 0x7fffffffLL;
     if (blocks < 1) blocks = 1;
     return (int)blocks;
 }

@@ -17,11 +17,13 @@
 //   dK  += dS^T . Q                 A = dS^T from shared memory (K-major view)
 //   dQ_i = dS . K                   A = the same shared-memory tile read along M (MN-major view)
 //
-// Tensor memory (512 columns): R0 = S^T / P^T / dP^T (128), dQ (HS), dV (HS), dK (HS).  dP^T
-// shares columns with the scores rather than with dQ, so reading dQ out never holds up the next
-// tile, and S^T of tile t+1 is issued as soon as the softmax warps have loaded dP^T of tile t:
-// it executes while they compute dS^T, and the exponentials of tile t+1 then overlap the dK and
-// dQ MMAs of tile t.  The softmax warps are the critical resource (A, wait for dV and dP^T, B).
+// Tensor memory (512 columns): R0 = S^T / P^T (128), dQ (HS), dV (HS), dK (HS); with head size
+// 128 that is all of it and dP^T shares R0 - with the scores rather than with dQ, so reading dQ
+// out never holds up the next tile - and S^T of tile t+1 is issued as soon as the softmax warps
+// have loaded dP^T of tile t: it executes while they compute dS^T, and the exponentials of tile
+// t+1 then overlap the dK and dQ MMAs of tile t.  The softmax warps are the critical resource
+// (A, wait for dV and dP^T, B).  With head size 64 dP^T has 128 columns of its own, is issued a
+// tile ahead, and the softmax warps go from A straight to B.
 //
 // dQ of a query tile gets one contribution per key tile; CTAs add theirs into an FP32 buffer
 // with TMA reduce-add (cp.reduce.async.bulk.tensor), and a cast kernel turns the sum into the
@@ -47,14 +49,20 @@ struct BwdCfg {
     static constexpr int NBOX = ROWB / 128;
     static constexpr int TILE_BYTES = NBOX * kBoxBytes;       // one 128 x HS BF16 tile
     static constexpr int DS_BYTES = 2 * kBoxBytes;             // dS^T: 128 x 128 BF16
-    static constexpr int Q_STAGES = 2;
+    // Q / dO stages: three when they fit (head size 64), so that the dO tile loaded behind a
+    // dQ read-out is not needed before the tile after next
+    static constexpr int Q_STAGES = HS == 64 ? 3 : 2;
     // K,V + Q,dO stages + dS^T + two (lse, delta) buffers + barriers.  With head size 128 this
     // is 231,680 of the 232,448 bytes a CTA may have, so the base must come 1024-byte aligned
     // from the launch (checked at kernel entry) - there is no room for manual alignment slack.
     static constexpr int SMEM = 2 * TILE_BYTES + Q_STAGES * 2 * TILE_BYTES + DS_BYTES + 2048 + 256;
     // tensor memory columns
-    static constexpr uint32_t COL_S = 0, COL_DP = 0;          // R0: S^T, then P^T, then dP^T
-    static constexpr uint32_t COL_DQ = 128, COL_DV = 128 + HS, COL_DK = 128 + 2 * HS;
+    // R0 (columns 0..127) holds S^T, then P^T.  dP^T goes there too when nothing else is left
+    // (head size 128); with head size 64 it has 128 columns of its own, can be issued a tile
+    // ahead, and the softmax warps never wait for it.
+    static constexpr bool DP_OWN = 256 + 3 * HS <= 512;
+    static constexpr uint32_t COL_S = 0, COL_DP = DP_OWN ? 128 : 0;
+    static constexpr uint32_t COL_DQ = DP_OWN ? 256 : 128, COL_DV = COL_DQ + HS, COL_DK = COL_DQ + 2 * HS;
     static constexpr uint32_t TMEM_COLS = 512;
 };
 
@@ -99,18 +107,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     float* stat_s = (float*)(ds_smem + C::DS_BYTES);                   // [2][-lse*log2e[128], -delta/sqrt(hs)[128]]
     uint64_t* bars = (uint64_t*)(stat_s + 512);
     uint64_t* kv_full = bars;                   // 1
-    uint64_t* q_full = bars + 1;                // [2] Q tile landed
+    uint64_t* q_full = bars + 16;               // [Q_STAGES] Q tile landed
     uint64_t* s_full = bars + 5;                // S^T complete
     uint64_t* ds_full = bars + 6;               // dS^T in smem (256 arrivals)
     uint64_t* dq_full = bars + 7;               // all MMAs of the tile complete
     uint64_t* dq_empty = bars + 8;              // dQ is out of its TMEM columns
     uint64_t* all_done = bars + 9;
     uint64_t* dp_full = bars + 10;              // dP^T complete
-    uint64_t* do_full = bars + 11;              // [2] dO tile landed
-    uint64_t* q_empty = bars + 13;              // [2] S^T and dK of the tile are complete: its Q stage is free
+    uint64_t* do_full = bars + 19;              // [Q_STAGES] dO tile landed
+    uint64_t* q_empty = bars + 22;              // [Q_STAGES] S^T and dK of the tile are complete: its Q stage is free
     uint64_t* p_full = bars + 3;                // P^T in TMEM (256 arrivals)
     uint64_t* r0_free = bars + 4;               // dP^T loaded into registers (256 arrivals)
-    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+    uint32_t* tmem_slot = (uint32_t*)(bars + 25);
     volatile uint32_t* softmax_ok = tmem_slot + 1;     // [2] written by one softmax thread, read by all 256
     volatile uint32_t* drain_ok = tmem_slot + 3;       // same idea for the dQ warps
 
@@ -134,7 +142,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < C::Q_STAGES; ++s) {
             mbar_init(&q_full[s], 1);
             mbar_init(&do_full[s], 1);
             mbar_init(&q_empty[s], 1);
@@ -168,7 +176,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tma_load_2d(k_smem + b * kBoxBytes, &map_k, kv_full, b * 64, row_base + jt * kTile);
                 tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jt * kTile);
             }
-            // dO of the first two query tiles; later ones are loaded by the dQ warps, which stage
+            // dO of the first Q_STAGES query tiles; later ones are loaded by the dQ warps, which stage
             // dQ through the dO buffers and know when one is free again
             for (int t = 0; t < n_q && t < C::Q_STAGES; ++t) {
                 mbar_arrive_expect_tx(&do_full[t], C::TILE_BYTES);
@@ -177,8 +185,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                 row_base + (i_begin + t) * kTile);
             }
             for (int t = 0; t < n_q; ++t) {
-                const int s = t & 1;
-                if (!mbar_wait(&q_empty[s], ((t >> 1) & 1) ^ 1, p.status, kTimeoutProducer)) break;
+                const int s = t % C::Q_STAGES;
+                if (!mbar_wait(&q_empty[s], ((t / C::Q_STAGES) & 1) ^ 1, p.status, kTimeoutProducer)) break;
                 mbar_arrive_expect_tx(&q_full[s], C::TILE_BYTES);
                 for (int b = 0; b < C::NBOX; ++b)
                     tma_load_2d(q_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[s], b * 64,
@@ -193,13 +201,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             constexpr uint32_t idesc_dq = make_idesc(kBF16, true, true, kTile, HS);        // dQ
             const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
             // Issue order on the (in-order) tensor pipe, per tile t:
-            //   dV(t) dP(t) | S(t+1) | dK(t) dQ(t)
-            // dV and dP^T follow phase A; dP^T overwrites P^T in R0, which dV, ahead of it on the
-            // pipe, is the only reader of.  S^T of the next tile overwrites dP^T once the softmax
-            // warps hold it in registers; dK and dQ need dS^T from phase B.
+            //   head size 128:  dV(t) dP(t) | S(t+1) | dK(t) dQ(t)
+            //   head size 64:   dV(t) S(t+1) | dK(t) dQ(t) dP(t+1)
+            // dV follows phase A.  With head size 128 dP^T overwrites P^T in R0, which dV, ahead of
+            // it on the pipe, is the only reader of, and S^T of the next tile overwrites dP^T once
+            // the softmax warps hold it in registers.  With head size 64 dP^T has its own columns
+            // and is ready long before phase B asks for it.  dK and dQ need dS^T from phase B.
             auto issue_s = [&](int t) -> bool {
-                const int s = t & 1;
-                if (!mbar_wait(&q_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) return false;
+                const int s = t % C::Q_STAGES;
+                if (!mbar_wait(&q_full[s], (t / C::Q_STAGES) & 1, p.status, kTimeoutMma)) return false;
                 tc_fence_after_sync();
                 const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
 #pragma unroll
@@ -211,29 +221,43 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 mma_commit(s_full);
                 return true;
             };
-            bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutMma);
-            ok = ok && issue_s(0);
-            for (int t = 0; t < n_q && ok; ++t) {
-                const int s = t & 1;
-                const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
-                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
-                if (!mbar_wait(p_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
-                if (!mbar_wait(&do_full[s], (t >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+            auto issue_dp = [&](int t) -> bool {        // dP^T = V . dO^T
+                const int s = t % C::Q_STAGES;
+                if (!mbar_wait(&do_full[s], (t / C::Q_STAGES) & 1, p.status, kTimeoutMma)) return false;
                 tc_fence_after_sync();
+                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
-                    mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + (kk / 4) * 64 + (kk % 4) * 8,
-                                  smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
-#pragma unroll
-                for (int kk = 0; kk < C::ROWB / 32; ++kk) {  // dP^T = V . dO^T
+                for (int kk = 0; kk < C::ROWB / 32; ++kk) {
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
                     mma_ss<false>(tmem_base + C::COL_DP, smem_desc_sw128(v_addr + off, 16, 1024),
                                   smem_desc_sw128(do_addr + off, 16, 1024), idesc_st, kk > 0);
                 }
                 mma_commit(dp_full);
-                if (t + 1 < n_q) {
-                    if (!mbar_wait(r0_free, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
-                    if (!issue_s(t + 1)) { ok = false; break; }
+                return true;
+            };
+            bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutMma);
+            ok = ok && issue_s(0);
+            if (C::DP_OWN) ok = ok && issue_dp(0);
+            for (int t = 0; t < n_q && ok; ++t) {
+                const int s = t % C::Q_STAGES;
+                const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
+                const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
+                if (!mbar_wait(p_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                if (!mbar_wait(&do_full[s], (t / C::Q_STAGES) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
+                    mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + (kk / 4) * 64 + (kk % 4) * 8,
+                                  smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
+                if (C::DP_OWN) {
+                    // R0 is free as soon as dV, ahead on the pipe, has read P^T
+                    if (t + 1 < n_q && !issue_s(t + 1)) { ok = false; break; }
+                } else {
+                    if (!issue_dp(t)) { ok = false; break; }
+                    if (t + 1 < n_q) {
+                        if (!mbar_wait(r0_free, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                        if (!issue_s(t + 1)) { ok = false; break; }
+                    }
                 }
                 if (!mbar_wait(ds_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 if (t > 0) {
@@ -253,6 +277,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                   smem_desc_mn(k_addr + kk * 2048, kBoxBytes, false), idesc_dq, kk > 0);
                 mma_commit(&q_empty[s]);
                 mma_commit(dq_full);      // also: this tile's dO stage and the dS^T tile are no longer read
+                // dS^T of tile t is in shared memory, so the softmax warps are done with dP^T(t)
+                if (C::DP_OWN && t + 1 < n_q && !issue_dp(t + 1)) { ok = false; break; }
             }
             if (ok) mma_commit(all_done);
         }
@@ -344,8 +370,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0, d0);
                 tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0 + 32, d1);
                 tmem_wait_ld();
-                tc_fence_before_sync();
-                mbar_arrive(r0_free);                        // R0 may take the next tile's scores
+                if (!C::DP_OWN) {
+                    tc_fence_before_sync();
+                    mbar_arrive(r0_free);                    // R0 may take the next tile's scores
+                }
 #pragma unroll
                 for (int half32 = 0; half32 < 2; ++half32) {
 #pragma unroll
@@ -407,7 +435,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
         const int swz = r & 7;
         for (int t = 0; t < n_q; ++t) {
-            const int s = t & 1;
+            const int s = t % C::Q_STAGES;
             if (tid128 == 0) drain_ok[0] = mbar_wait(dq_full, t & 1, p.status, kTimeoutOther) ? 1u : 0u;
             named_barrier_sync(2, 128);
             if (drain_ok[0] == 0u) break;
