@@ -172,6 +172,8 @@ PROTOTYPES = {
     "boat_attention_grad_bucket": (_I, [_P, C.POINTER(C.POINTER(C.c_float)), C.POINTER(_SZ)]),
     "boat_attention_allreduce_grads": (_I, [_P]),
     "boat_attention_add_to_optimizer": (_I, [_P, _P]),
+    "boat_attention_load_safetensors": (_I, [_P, _P, _SZ, C.c_char_p]),
+    "boat_attention_load_safetensors_file": (_I, [_P, C.c_char_p, C.c_char_p]),
     # include/boat/optimizers.h
     "boat_sgd_optimizer_create": (_P, [_F, _F]),
     "boat_adam_optimizer_create": (_P, [_F, _F, _F, _F]),

@@ -166,6 +166,15 @@ class Attention:
     def update(self, lr):
         capi.load().boat_attention_update(self.h, lr)
 
+    def load_safetensors(self, image, prefix=None):
+        """image: bytes of a safetensors file, or a path.  Returns the library's status code."""
+        lib = capi.load()
+        pre = prefix.encode() if prefix else None
+        if isinstance(image, (bytes, bytearray)):
+            buf = (C.c_char * len(image)).from_buffer_copy(image)
+            return lib.boat_attention_load_safetensors(self.h, C.cast(buf, C.c_void_p), len(image), pre)
+        return lib.boat_attention_load_safetensors_file(self.h, str(image).encode(), pre)
+
     def allreduce_grads(self):
         rc = capi.load().boat_attention_allreduce_grads(self.h)
         if rc:

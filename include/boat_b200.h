@@ -50,6 +50,19 @@ BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
  * another device, so call boat_attention_to_device first.  Returns 0 on success. */
 BOAT_API int boat_attention_add_to_optimizer(boat_attention_t* attention, boat_optimizer_t* optimizer);
 
+/* Fill the layer's parameters from a safetensors checkpoint image (or file).  The reference
+ * detects attention tensors by name in src/format/huggingface.c:917-932 and stops there (TODO);
+ * this completes that step with the same name test: among the tensors whose name starts with
+ * `prefix` (NULL or "" for any) and contains "attention", the one containing "query" / "key" /
+ * "value" / "output" with a 2-D ".weight" becomes Wq / Wk / Wv / Wo - transposed, because
+ * checkpoints store [out, in] and Boat [in, out] - and a 1-D ".bias" the matching bias.  F32, BF16
+ * and F16 tensors are accepted.  Missing biases keep their values.  Returns 0, or 1 bad
+ * argument / unreadable file, 2 malformed image, 3 a projection matrix is missing, 4 wrong
+ * shape or type or an ambiguous name match, 5 device error. */
+BOAT_API int boat_attention_load_safetensors(boat_attention_t* attention, const void* image, size_t size,
+                                             const char* prefix);
+BOAT_API int boat_attention_load_safetensors_file(boat_attention_t* attention, const char* path, const char* prefix);
+
 /* alpha*a + beta*b for equal shapes, FP32 or BF16, host or device: one kernel for residual
  * adds, differences and the mean-squared-error gradient 2(o - t)/n. */
 BOAT_API boat_tensor_t* boat_lincomb(const boat_tensor_t* a, float alpha, const boat_tensor_t* b, float beta);
