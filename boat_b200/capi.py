@@ -195,6 +195,10 @@ PROTOTYPES = {
     "boat_cuda_memcpy_h2d": (_I, [_P, _P, _SZ]),
     "boat_cuda_memcpy_d2h": (_I, [_P, _P, _SZ]),
     "boat_cuda_memcpy_d2d": (_I, [_P, _P, _SZ]),
+    "boat_cuda_copies_after_compute": (_I, []),
+    "boat_cuda_upload_async": (_I, [_P, _P, _SZ]),
+    "boat_cuda_join_uploads": (_I, []),
+    "boat_cuda_download_async": (_I, [_P, _P, _SZ]),
     "boat_cuda_memset": (_I, [_P, _I, _SZ]),
     "boat_cuda_host_alloc": (_P, [_SZ]),
     "boat_cuda_host_free": (_I, [_P]),

@@ -185,9 +185,69 @@ int boat_cuda_set_stream(void* s) {
     return 0;
 }
 
+// ---- copies that overlap kernels -----------------------------------------------------------------
+// One extra stream per direction (non-blocking: the library stream may be the legacy default
+// stream).  Ordering against the library stream is by events: the copy streams see buffers
+// allocated or written on the library stream after boat_cuda_copies_after_compute(), uploads
+// become visible to later kernels through boat_cuda_join_uploads(), and a download starts after
+// the kernels launched before it.
+static cudaStream_t g_up = nullptr, g_down = nullptr;
+static cudaEvent_t g_up_done = nullptr, g_compute_done = nullptr;
+static bool g_copy_pending = false;
+
+static int copy_streams() {
+    if (g_up) return 0;
+    BOATCU_CHECK(cudaStreamCreateWithFlags(&g_up, cudaStreamNonBlocking));
+    BOATCU_CHECK(cudaStreamCreateWithFlags(&g_down, cudaStreamNonBlocking));
+    BOATCU_CHECK(cudaEventCreateWithFlags(&g_up_done, cudaEventDisableTiming));
+    BOATCU_CHECK(cudaEventCreateWithFlags(&g_compute_done, cudaEventDisableTiming));
+    return 0;
+}
+
+int boat_cuda_copies_after_compute(void) {
+    if (int rc = ensure_init()) return rc;
+    if (int rc = copy_streams()) return rc;
+    BOATCU_CHECK(cudaEventRecord(g_compute_done, g_stream));
+    BOATCU_CHECK(cudaStreamWaitEvent(g_up, g_compute_done, 0));
+    BOATCU_CHECK(cudaStreamWaitEvent(g_down, g_compute_done, 0));
+    return 0;
+}
+
+int boat_cuda_upload_async(void* dst, const void* src, size_t bytes) {
+    if (bytes == 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    if (int rc = copy_streams()) return rc;
+    BOATCU_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g_up));
+    g_copy_pending = true;
+    return 0;
+}
+
+int boat_cuda_join_uploads(void) {
+    if (!g_up) return 0;
+    BOATCU_CHECK(cudaEventRecord(g_up_done, g_up));
+    BOATCU_CHECK(cudaStreamWaitEvent(g_stream, g_up_done, 0));
+    return 0;
+}
+
+int boat_cuda_download_async(void* dst, const void* src, size_t bytes) {
+    if (bytes == 0) return 0;
+    if (int rc = ensure_init()) return rc;
+    if (int rc = copy_streams()) return rc;
+    BOATCU_CHECK(cudaEventRecord(g_compute_done, g_stream));
+    BOATCU_CHECK(cudaStreamWaitEvent(g_down, g_compute_done, 0));
+    BOATCU_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, g_down));
+    g_copy_pending = true;
+    return 0;
+}
+
 int boat_cuda_sync(void) {
     if (int rc = ensure_init()) return rc;
     BOATCU_CHECK(cudaStreamSynchronize(g_stream));
+    if (g_copy_pending) {
+        BOATCU_CHECK(cudaStreamSynchronize(g_up));
+        BOATCU_CHECK(cudaStreamSynchronize(g_down));
+        g_copy_pending = false;
+    }
     return report_kernel_status("boat_cuda_sync");
 }
 

@@ -216,6 +216,221 @@ fail:
     return false;
 }
 
+
+/* ---- host tensors: transfers overlapped with the arithmetic ------------------------------------
+ * With host tensors a step moves about a gigabyte over PCIe (inputs and parameters up, outputs
+ * and gradients down), more time than the kernels take.  Everything that is computed per token
+ * row or per (batch, head) unit - projections, attention core, input gradients - is therefore
+ * done in chunks of whole batch entries: while chunk c is computed, chunk c+1 is uploaded and
+ * chunk c-1 downloaded, on the copy streams of boat_cuda_upload_async / _download_async.  Only
+ * the weight and bias gradients, which sum over all rows, run once at the end.  The arithmetic
+ * per row is the same as in the one-piece path. */
+enum { MAX_CHUNKS = 8 };
+
+static bool on_host(const boat_tensor_t* t) { return t->device != BOAT_DEVICE_CUDA; }
+
+/* First batch entry of chunk c when B entries are cut into n chunks. */
+static int64_t chunk_begin(int64_t B, int n, int c) { return B * c / n; }
+
+/* Rows [r0, r0+nr) of host tensor `t` (row length H) into the same rows of `dst` (device,
+ * storage `type`): upload, then cast through `raw` (device, the tensor's own storage) when the
+ * types differ, then TF32 rounding when the arithmetic wants it.  Everything after the upload
+ * is ordered behind it on the library stream. */
+static int stage_rows(const boat_tensor_t* t, int mma, int type, void* dst, void* raw, int64_t r0, int64_t nr,
+                      int64_t H) {
+    const int have = storage_of(t->dtype);
+    const size_t hsz = storage_size(have), tsz = storage_size(type);
+    const int64_t n = nr * H;
+    char* d = (char*)dst + (size_t)(r0 * H) * tsz;
+    const char* src = (const char*)t->data + (size_t)(r0 * H) * hsz;
+    int rc;
+    if (have == type) {
+        rc = boat_cuda_upload_async(d, src, (size_t)n * hsz);
+        if (rc == 0) rc = boat_cuda_join_uploads();
+    } else {
+        char* r = (char*)raw + (size_t)(r0 * H) * hsz;
+        rc = boat_cuda_upload_async(r, src, (size_t)n * hsz);
+        if (rc == 0) rc = boat_cuda_join_uploads();
+        if (rc == 0) rc = boat_cuda_cast(d, type, r, have, n);
+    }
+    if (rc == 0 && mma == BOAT_MMA_TF32) rc = boat_cuda_round_tf32((float*)d, (const float*)d, n);
+    return boat_report("chunk upload", rc);
+}
+
+/* Forward for host inputs, B >= 2.  Fills the layer's forward state like the one-piece path. */
+static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t* const in[3], int mma, int type,
+                                        const staged_params_t* p) {
+    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
+    const int64_t hs = (int64_t)a->config.head_size, B = a->B, S = a->S, T = B * S;
+    const size_t tsz = storage_size(type), act_bytes = (size_t)T * (size_t)H * tsz;
+    const int out_type = storage_of(in[0]->dtype);
+    const size_t osz = storage_size(out_type);
+    const int nchunk = (int)(B < MAX_CHUNKS ? B : MAX_CHUNKS);
+    void* raw[3] = {NULL, NULL, NULL};
+    void* d_out = NULL;
+    bool ok = false;
+    boat_tensor_t* result = boat_tensor_create_uninit(in[0]->shape, 3, in[0]->dtype, BOAT_DEVICE_CPU);
+    if (!result) return NULL;
+
+    for (int i = 0; i < 3; ++i) {
+        int same = -1;
+        for (int j = 0; j < i; ++j)
+            if (in[j] == in[i]) same = j;
+        if (same >= 0) {
+            a->d_in[i] = a->d_in[same];
+            a->d_in_owned[i] = false;
+            continue;
+        }
+        a->d_in[i] = dev_alloc(act_bytes);
+        a->d_in_owned[i] = a->d_in[i] != NULL;
+        if (!a->d_in[i]) goto done;
+        if (storage_of(in[i]->dtype) != type) {
+            raw[i] = dev_alloc((size_t)T * (size_t)H * storage_size(storage_of(in[i]->dtype)));
+            if (!raw[i]) goto done;
+        }
+    }
+    for (int i = 0; i < 3; ++i) {
+        a->d_proj[i] = dev_alloc(act_bytes);
+        if (!a->d_proj[i]) goto done;
+    }
+    a->d_ctx = dev_alloc(act_bytes);
+    a->d_lse = (float*)dev_alloc((size_t)B * nh * S * sizeof(float));
+    d_out = dev_alloc((size_t)T * (size_t)H * osz);
+    if (!a->d_ctx || !a->d_lse || !d_out) goto done;
+    if (boat_report("copy streams", boat_cuda_copies_after_compute()) != 0) goto done;
+
+    for (int c = 0; c < nchunk; ++c) {
+        const int64_t b0 = chunk_begin(B, nchunk, c), b1 = chunk_begin(B, nchunk, c + 1);
+        const int64_t r0 = b0 * S, nr = (b1 - b0) * S;
+        const size_t off = (size_t)(r0 * H) * tsz, ooff = (size_t)(r0 * H) * osz;
+        for (int i = 0; i < 3; ++i)
+            if (a->d_in_owned[i] && stage_rows(in[i], mma, type, a->d_in[i], raw[i], r0, nr, H) != 0) goto done;
+        for (int i = 0; i < 3; ++i) {
+            if (boat_report("projection", boat_cuda_gemm(mma, 0, 0, nr, H, H, (char*)a->d_in[i] + off, H, p->w[i], H, type,
+                                                         (char*)a->d_proj[i] + off, H, type, p->b[i])) != 0)
+                goto done;
+            if (settle_tf32(mma, (char*)a->d_proj[i] + off, nr * H) != 0) goto done;
+        }
+        if (boat_report("attention core",
+                        boat_cuda_attn_fwd(mma, (b1 - b0) * nh, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
+                                           (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
+                                           type, (char*)a->d_ctx + off, a->d_lse + b0 * nh * S)) != 0)
+            goto done;
+        if (settle_tf32(mma, (char*)a->d_ctx + off, nr * H) != 0) goto done;
+        if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, nr, H, H, (char*)a->d_ctx + off, H, p->w[WO], H, type,
+                                                            (char*)d_out + ooff, H, out_type, p->b[WO])) != 0)
+            goto done;
+        if (boat_report("chunk download", boat_cuda_download_async((char*)result->data + ooff, (char*)d_out + ooff,
+                                                                   (size_t)(nr * H) * osz)) != 0)
+            goto done;
+    }
+    ok = true;
+done:
+    if (boat_report("forward", boat_cuda_sync()) != 0) ok = false;     /* copies done before anything is freed */
+    for (int i = 0; i < 3; ++i) dev_free(raw[i]);
+    dev_free(d_out);
+    if (!ok) {
+        boat_tensor_free(result);
+        result = NULL;
+    }
+    return result;
+}
+
+
+/* Backward for a host grad_output and host inputs, B >= 2: dOut up, d(ctx), attention core and
+ * the three input gradients per chunk of batch entries, input gradients down while the next
+ * chunk is computed; weight and bias gradients over all rows at the end. */
+static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_output, int mma, int type,
+                               const staged_params_t* p, float* const d_dw[4], float* const d_db[4],
+                               boat_tensor_t* gin[3]) {
+    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
+    const int64_t hs = (int64_t)a->config.head_size, B = a->B, S = a->S, T = B * S;
+    const size_t tsz = storage_size(type), act_bytes = (size_t)T * (size_t)H * tsz;
+    const bool bias = a->param[BQ] != NULL;
+    const int nchunk = (int)(B < MAX_CHUNKS ? B : MAX_CHUNKS);
+    void *d_go = NULL, *raw_go = NULL, *d_dctx = NULL, *scratch = NULL;
+    void *d_dproj[3] = {NULL, NULL, NULL}, *d_dx[3] = {NULL, NULL, NULL};
+    int out_type[3];
+    bool ok = false;
+    size_t scratch_bytes = 0;
+
+    d_go = dev_alloc(act_bytes);
+    d_dctx = dev_alloc(act_bytes);
+    if (!d_go || !d_dctx) goto done;
+    if (storage_of(grad_output->dtype) != type) {
+        raw_go = dev_alloc((size_t)T * (size_t)H * storage_size(storage_of(grad_output->dtype)));
+        if (!raw_go) goto done;
+    }
+    for (int i = 0; i < 3; ++i) {
+        const boat_tensor_t* x = a->cache_in[i];
+        out_type[i] = storage_of(x->dtype);
+        d_dproj[i] = dev_alloc(act_bytes);
+        d_dx[i] = dev_alloc((size_t)T * (size_t)H * storage_size(out_type[i]));
+        gin[i] = boat_tensor_create_uninit(x->shape, 3, x->dtype, BOAT_DEVICE_CPU);
+        if (!d_dproj[i] || !d_dx[i] || !gin[i]) goto done;
+    }
+    for (int c = 0; c < nchunk; ++c) {              /* the largest chunk decides the scratch size */
+        const int64_t nb = chunk_begin(B, nchunk, c + 1) - chunk_begin(B, nchunk, c);
+        const size_t need = boat_cuda_attn_bwd_scratch_bytes(mma, nb * nh, S, hs);
+        if (need > scratch_bytes) scratch_bytes = need;
+    }
+    scratch = dev_alloc(scratch_bytes ? scratch_bytes : 256);
+    if (!scratch) goto done;
+    if (boat_report("copy streams", boat_cuda_copies_after_compute()) != 0) goto done;
+
+    for (int c = 0; c < nchunk; ++c) {
+        const int64_t b0 = chunk_begin(B, nchunk, c), b1 = chunk_begin(B, nchunk, c + 1);
+        const int64_t r0 = b0 * S, nr = (b1 - b0) * S;
+        const size_t off = (size_t)(r0 * H) * tsz;
+        if (stage_rows(grad_output, mma, type, d_go, raw_go, r0, nr, H) != 0) goto done;
+        /* d(ctx) = dOut . Wo^T */
+        if (boat_report("dOut.Wo^T", boat_cuda_gemm(mma, 0, 1, nr, H, H, (char*)d_go + off, H, p->w[WO], H, type,
+                                                    (char*)d_dctx + off, H, type, NULL)) != 0)
+            goto done;
+        if (settle_tf32(mma, (char*)d_dctx + off, nr * H) != 0) goto done;
+        if (boat_report("attention core backward",
+                        boat_cuda_attn_bwd(mma, (b1 - b0) * nh, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
+                                           (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
+                                           (char*)a->d_ctx + off, (char*)d_dctx + off, a->d_lse + b0 * nh * S, type,
+                                           (char*)d_dproj[0] + off, (char*)d_dproj[1] + off, (char*)d_dproj[2] + off,
+                                           scratch, scratch_bytes)) != 0)
+            goto done;
+        for (int i = 0; i < 3; ++i) {
+            const size_t osz = storage_size(out_type[i]), ooff = (size_t)(r0 * H) * osz;
+            if (settle_tf32(mma, (char*)d_dproj[i] + off, nr * H) != 0) goto done;
+            /* dX = dP . W^T */
+            if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, nr, H, H, (char*)d_dproj[i] + off, H, p->w[i], H, type,
+                                                 (char*)d_dx[i] + ooff, H, out_type[i], NULL)) != 0)
+                goto done;
+            if (boat_report("chunk download", boat_cuda_download_async((char*)gin[i]->data + ooff, (char*)d_dx[i] + ooff,
+                                                                       (size_t)(nr * H) * osz)) != 0)
+                goto done;
+        }
+    }
+    /* sums over all rows: dWo = ctx^T . dOut, dbo = colsum(dOut), dW = X^T . dP, db = colsum(dP) */
+    if (boat_report("dWo", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_ctx, H, d_go, H, type, d_dw[WO], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
+    if (bias && boat_report("dbo", boat_cuda_colsum(d_go, type, T, H, d_db[WO])) != 0) goto done;
+    for (int i = 0; i < 3; ++i) {
+        if (boat_report("dW", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_in[i], H, d_dproj[i], H, type, d_dw[i], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
+        if (bias && boat_report("db", boat_cuda_colsum(d_dproj[i], type, T, H, d_db[i])) != 0) goto done;
+    }
+    if (a->device != BOAT_DEVICE_CUDA &&
+        boat_report("gradient download", boat_cuda_download_async(a->grad_bucket->data, d_dw[0], a->grad_bucket->nbytes)) != 0)
+        goto done;
+    ok = true;
+done:
+    if (boat_report("backward", boat_cuda_sync()) != 0) ok = false;    /* copies done before anything is freed */
+    dev_free(scratch);
+    for (int i = 0; i < 3; ++i) {
+        dev_free(d_dproj[i]);
+        dev_free(d_dx[i]);
+    }
+    dev_free(d_dctx);
+    dev_free(raw_go);
+    dev_free(d_go);
+    return ok;
+}
+
 /* ---- create / free ------------------------------------------------------------------------ */
 
 static boat_tensor_t* new_weight(size_t in, size_t out) {
@@ -304,6 +519,11 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
     void* d_out = NULL;
     boat_tensor_t* result = NULL;
     if (!stage_params(a, mma, type, &p)) goto done;
+    if (B >= 2 && on_host(query) && on_host(key) && on_host(value)) {
+        result = forward_pipelined(a, in, mma, type, &p);
+        if (result) a->cached = true;
+        goto done;
+    }
 
     for (int i = 0; i < 3; ++i) {
         int same = -1;
@@ -415,8 +635,6 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
 
     if (!ensure_grads(a)) goto done;
     if (!stage_params(a, mma, type, &p)) goto done;
-    d_go = stage_operand(grad_output, mma, type, &go_owned);
-    if (!d_go) goto done;
     /* gradients are produced in HBM; a host layer receives them with one copy at the end */
     d_bucket = a->device == BOAT_DEVICE_CUDA ? (float*)a->grad_bucket->data
                                              : (float*)dev_alloc(a->grad_bucket->nbytes);
@@ -427,6 +645,13 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         d_dw[i] = d_bucket + (size_t)i * H * H;
         d_db[i] = bias ? d_bucket + (size_t)4 * H * H + (size_t)i * H : NULL;
     }
+    if (B >= 2 && on_host(grad_output) && on_host(a->cache_in[0]) && on_host(a->cache_in[1]) &&
+        on_host(a->cache_in[2])) {
+        ok = backward_pipelined(a, grad_output, mma, type, &p, d_dw, d_db, gin);
+        goto done;
+    }
+    d_go = stage_operand(grad_output, mma, type, &go_owned);
+    if (!d_go) goto done;
 
     /* output projection: d(ctx) = dOut . Wo^T,  dWo = ctx^T . dOut,  dbo = colsum(dOut) */
     d_dctx = dev_alloc(act_bytes);

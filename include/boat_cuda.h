@@ -35,12 +35,25 @@ int         boat_cuda_device_count(void);        /* 0 when no usable GPU / drive
 const char* boat_cuda_last_error(void);
 void*       boat_cuda_stream(void);              /* cudaStream_t the library launches on */
 int         boat_cuda_set_stream(void* stream);
-int         boat_cuda_sync(void);                /* wait for the library stream */
+int         boat_cuda_sync(void);                /* wait for the library stream and the copy streams */
 int         boat_cuda_malloc(void** ptr, size_t bytes);   /* stream-ordered pool allocation */
 int         boat_cuda_free(void* ptr);
 int         boat_cuda_memcpy_h2d(void* dst, const void* src_host, size_t bytes);  /* returns after arrival */
 int         boat_cuda_memcpy_d2h(void* dst_host, const void* src, size_t bytes);  /* returns after arrival */
 int         boat_cuda_memcpy_d2d(void* dst, const void* src, size_t bytes);       /* asynchronous on the stream */
+/* Copies on their own streams, one per direction, so that PCIe traffic overlaps kernels.
+ * copies_after_compute: both copy streams wait for what has been launched (and allocated) on
+ * the library stream so far - call it after allocating the buffers the copies will touch.
+ * upload_async: host -> device on the upload stream, in issue order, overlapping later launches.
+ * join_uploads: every later launch on the library stream waits for the uploads issued so far.
+ * download_async: device -> host on the download stream, after the kernels launched before it.
+ * boat_cuda_sync() also waits for these copies - call it before the host reads a download and
+ * before freeing a buffer a copy may still touch.  Page-locked host memory
+ * (boat_cuda_host_alloc / _register) is needed for real overlap. */
+int         boat_cuda_copies_after_compute(void);
+int         boat_cuda_upload_async(void* dst, const void* src_host, size_t bytes);
+int         boat_cuda_join_uploads(void);
+int         boat_cuda_download_async(void* dst_host, const void* src, size_t bytes);
 int         boat_cuda_memset(void* dst, int value, size_t bytes);
 void*       boat_cuda_host_alloc(size_t bytes);          /* page-locked host block from a re-use pool; NULL on failure */
 int         boat_cuda_host_free(void* ptr);              /* back to the pool (never unlocked until exit) */
