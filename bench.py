@@ -403,6 +403,10 @@ def main():
         "flash_bwd": 8.0 * core_c * B * S * S * d, "attn_bwd_simt": 8.0 * core_c * B * S * S * d,
     }
     kbytes = {"adam_step": 28.0 * (4 * d * d + 4 * d)}     # p, g, m, v read; p, m, v written (FP32)
+    # dram__bytes_read.sum + dram__bytes_write.sum per (batch, head) unit from the ncu capture of
+    # one batch entry of C4 (profiles/flash_kernels_hs128_ncu_full.md: 290.3 MB for 16 units); the
+    # kernel's traffic is proportional to the number of units of that shape
+    ncu_traffic_per_unit = {("flash_bwd", 8192, 128, True): 290.3e6 / 16}
     roofline = None
     if kern:
         top = max((k for k in kern if k in kflops), key=lambda k: kern[k][1], default=None)
@@ -412,8 +416,10 @@ def main():
             # kernels are timed inside a long step: the sustained figure is the denominator;
             # TF32 has no measured entry, half of the BF16 figure stands in for it
             peak = peaks["bf16_sustained"] if bf16 else peaks["bf16_sustained"] / 2
+            per_unit = ncu_traffic_per_unit.get((top, S, d // nh, bool(causal)))
             roofline = dict(bound="tensor", kernel=top, achieved=achieved, peak=peak, unit="TFLOP/s",
-                            frac=achieved / peak, traffic=None, launches=n, avg_ms=ms / n,
+                            frac=achieved / peak, traffic=(per_unit * B * nh) if per_unit else None,
+                            launches=n, avg_ms=ms / n,
                             peak_source=peaks["source"] + (" bf16 sustained" if bf16 else " bf16 sustained / 2 for tf32"),
                             kernels={k: dict(scopes=v[0], ms=round(v[1], 3), share=round(v[1] / sum(x[1] for x in kern.values()), 4))
                                      for k, v in sorted(kern.items(), key=lambda kv: -kv[1][1])})

@@ -120,8 +120,8 @@ static int settle_tf32(int mma, void* buf, int64_t n) {
 }
 
 /* New tensor with the dtype/device of `like`, filled from device buffer `src` (storage
- * `type`, n elements).  `src` may be adopted as the tensor's memory when it already has the
- * right type and place; *adopted tells the caller not to free it then. */
+ * `type`): a cast on the device for a CUDA result, a download (after a cast when the types
+ * differ) for a host result.  `src` stays the caller's. */
 static boat_tensor_t* emit_out(const int64_t* shape, size_t ndim, const boat_tensor_t* like, void* src,
                                int type) {
     boat_tensor_t* out = boat_tensor_create_uninit(shape, ndim, like->dtype, like->device);
