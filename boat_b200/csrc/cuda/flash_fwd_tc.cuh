@@ -190,22 +190,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (!mbar_wait(s_full, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
             tc_fence_after_sync();
             const bool diag = p.causal && j == qt;
-            // pass 1: row maximum of the visible scores (the mask only exists on the diagonal tile)
-            float tmax = -FLT_MAX;
-#pragma unroll 1
-            for (int c = 0; c < kTile / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_s + lane_addr + c * 32, r);
-                tmem_wait_ld();
-                if (diag) {
+            // pass 1: row maximum of the visible scores (the mask only exists on the diagonal tile).
+            // The 32-column chunks are double-buffered in registers: the load of the next chunk is
+            // in flight while this one is reduced, and four running maxima keep the chain short.
+            float tmax;
+            {
+                uint32_t rr[2][32];
+                float t4[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};
+                tmem_ld32(tmem_s + lane_addr, rr[0]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (c * 32 + i <= r_in_tile) tmax = fmaxf(tmax, __uint_as_float(r[i]));
-                } else {
+                for (int c = 0; c < kTile / 32; ++c) {
+                    tmem_wait_ld();
+                    if (c + 1 < kTile / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, rr[(c + 1) & 1]);
+                    const uint32_t(&r)[32] = rr[c & 1];
+                    if (diag) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        tmax = fmaxf(tmax, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i <= r_in_tile) t4[i & 3] = fmaxf(t4[i & 3], __uint_as_float(r[i]));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            t4[(i >> 1) & 3] = fmaxf(t4[(i >> 1) & 3], fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+                    }
                 }
+                tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
             }
             const float m_new = fmaxf(m_ref, tmax);
             const bool need = (j == 0) || (m_new - m_ref) * sl2 > 8.0f;
@@ -230,45 +238,53 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     tmem_wait_st();
                 }
             }
-            // pass 2: P = exp2(s*sl2 - m*sl2), written over S
+            // pass 2: P = exp2(s*sl2 - m*sl2), written over S; same double buffering.  P of chunk c
+            // lands in columns that belong to chunks already loaded (BF16: [16c, 16c+16), TF32: the
+            // chunk's own), never in those of the chunk in flight.
             const float neg_m = -m_ref * sl2;
-            float lsum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < kTile / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_s + lane_addr + c * 32, r);
-                tmem_wait_ld();
-                float pv[32];
-                if (diag) {
+            float lsum;
+            {
+                uint32_t rr[2][32];
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                tmem_ld32(tmem_s + lane_addr, rr[0]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float e = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
-                        pv[i] = (c * 32 + i > r_in_tile) ? 0.f : e;
+                for (int c = 0; c < kTile / 32; ++c) {
+                    tmem_wait_ld();
+                    if (c + 1 < kTile / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, rr[(c + 1) & 1]);
+                    uint32_t(&r)[32] = rr[c & 1];
+                    float pv[32];
+                    if (diag) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            float e = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
+                            pv[i] = (c * 32 + i > r_in_tile) ? 0.f : e;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
                     }
-                } else {
+                    if (TF32) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
+                        for (int i = 0; i < 32; ++i) {
+                            // round to the nearest TF32 value: the MMA would otherwise truncate
+                            uint32_t t32;
+                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t32) : "f"(pv[i]));
+                            l4[i & 3] += __uint_as_float(t32);
+                            r[i] = t32;
+                        }
+                        tmem_st32(tmem_s + lane_addr + c * 32, r);
+                    } else {
+                        uint32_t h[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(pv[2 * i], pv[2 * i + 1]);
+                            l4[i & 3] += pv[2 * i] + pv[2 * i + 1];
+                            h[i] = *reinterpret_cast<uint32_t*>(&b2);
+                        }
+                        tmem_st16(tmem_s + lane_addr + c * 16, h);
+                    }
                 }
-                if (TF32) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        // round to the nearest TF32 value: the MMA would otherwise truncate
-                        uint32_t t32;
-                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t32) : "f"(pv[i]));
-                        lsum += __uint_as_float(t32);
-                        r[i] = t32;
-                    }
-                    tmem_st32(tmem_s + lane_addr + c * 32, r);
-                } else {
-                    uint32_t h[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(pv[2 * i], pv[2 * i + 1]);
-                        lsum += pv[2 * i] + pv[2 * i + 1];
-                        h[i] = *reinterpret_cast<uint32_t*>(&b2);
-                    }
-                    tmem_st16(tmem_s + lane_addr + c * 16, h);
-                }
+                lsum = (l4[0] + l4[1]) + (l4[2] + l4[3]);
             }
             l += lsum;
             tmem_wait_st();
