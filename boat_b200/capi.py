@@ -172,6 +172,10 @@ PROTOTYPES = {
     "boat_attention_grad_bucket": (_I, [_P, C.POINTER(C.POINTER(C.c_float)), C.POINTER(_SZ)]),
     "boat_attention_allreduce_grads": (_I, [_P]),
     "boat_attention_add_to_optimizer": (_I, [_P, _P]),
+    "boat_encoder_block_create": (_P, [_P, _P, _P, _P, _P]),
+    "boat_encoder_block_forward": (_P, [_P, _P]),
+    "boat_encoder_block_backward": (_P, [_P, _P]),
+    "boat_encoder_block_free": (None, [_P]),
     "boat_attention_load_safetensors": (_I, [_P, _P, _SZ, C.c_char_p]),
     "boat_attention_load_safetensors_file": (_I, [_P, C.c_char_p, C.c_char_p]),
     # include/boat/optimizers.h

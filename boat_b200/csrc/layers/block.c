@@ -1,0 +1,104 @@
+/* block.c - one pre-LN transformer encoder block step, composed in C from the layers.
+ *
+ *   y   = x + attention(LN1(x))
+ *   out = y + dense2(GELU(dense1(LN2(y))))
+ *
+ * The reference has the pieces (boat_layernorm_forward src/layers/norm.c:231-317, the dense layer
+ * src/layers/dense.c:135-297, the attention layer) but no block object and no test that chains
+ * them; this is the chaining a caller would write with the layer API, kept inside the library so
+ * that a step is two calls and the sixty-odd kernel launches of a step are issued back to back.
+ * The layers are borrowed: create, fill, place (to_device) and free them with their own API.
+ * Works on host or CUDA tensors like the layers it calls. */
+#include "../core/boat_internal.h"
+#include <boat_b200.h>
+#include <boat/ops.h>
+
+#include <stdlib.h>
+
+struct boat_encoder_block_t {
+    boat_layernorm_t *ln1, *ln2;
+    boat_attention_t* attn;
+    boat_dense_layer_t *fc1, *fc2;
+    boat_tensor_t* u;                 /* dense1 output before GELU, kept for the backward */
+    int64_t shape[3];                 /* [B, S, d] of the last forward */
+};
+
+boat_encoder_block_t* boat_encoder_block_create(boat_layernorm_t* norm1, boat_attention_t* attention,
+                                                boat_layernorm_t* norm2, boat_dense_layer_t* dense1,
+                                                boat_dense_layer_t* dense2) {
+    if (!norm1 || !attention || !norm2 || !dense1 || !dense2) return NULL;
+    boat_encoder_block_t* b = (boat_encoder_block_t*)calloc(1, sizeof *b);
+    if (!b) return NULL;
+    b->ln1 = norm1;
+    b->attn = attention;
+    b->ln2 = norm2;
+    b->fc1 = dense1;
+    b->fc2 = dense2;
+    return b;
+}
+
+void boat_encoder_block_free(boat_encoder_block_t* b) {
+    if (!b) return;
+    if (b->u) boat_tensor_unref(b->u);
+    free(b);
+}
+
+/* Frees `t` (when not NULL) and returns `keep`: lets a chain of temporaries read top to bottom. */
+static boat_tensor_t* drop(boat_tensor_t* t, boat_tensor_t* keep) {
+    if (t) boat_tensor_unref(t);
+    return keep;
+}
+
+boat_tensor_t* boat_encoder_block_forward(boat_encoder_block_t* b, const boat_tensor_t* x) {
+    if (!b || !x || x->ndim != 3) return NULL;
+    const int64_t T = x->shape[0] * x->shape[1], d = x->shape[2];
+    const int64_t flat[2] = {T, d};
+    boat_tensor_t *h1 = NULL, *att = NULL, *r1 = NULL, *h2 = NULL, *h2f = NULL, *u = NULL, *act = NULL, *m = NULL,
+                  *m3 = NULL, *out = NULL;
+    if (b->u) b->u = drop(b->u, NULL);
+    for (int i = 0; i < 3; ++i) b->shape[i] = x->shape[i];
+    h1 = boat_layernorm_forward(b->ln1, x);
+    att = h1 ? boat_attention_forward(b->attn, h1, h1, h1, NULL) : NULL;
+    r1 = att ? boat_lincomb(x, 1.0f, att, 1.0f) : NULL;
+    h2 = r1 ? boat_layernorm_forward(b->ln2, r1) : NULL;
+    h2f = h2 ? boat_tensor_reshape(h2, flat, 2) : NULL;
+    u = h2f ? boat_dense_layer_forward(b->fc1, h2f) : NULL;
+    act = u ? boat_gelu(u) : NULL;
+    m = act ? boat_dense_layer_forward(b->fc2, act) : NULL;
+    m3 = m ? boat_tensor_reshape(m, x->shape, 3) : NULL;
+    out = m3 ? boat_lincomb(r1, 1.0f, m3, 1.0f) : NULL;
+    if (out) {
+        b->u = u;
+        u = NULL;
+    }
+    drop(h1, NULL); drop(att, NULL); drop(r1, NULL); drop(h2f, NULL); drop(h2, NULL); drop(u, NULL);
+    drop(act, NULL); drop(m3, NULL); drop(m, NULL);
+    return out;
+}
+
+boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* b, const boat_tensor_t* grad_output) {
+    if (!b || !grad_output || !b->u) return NULL;
+    const int64_t T = b->shape[0] * b->shape[1], d = b->shape[2];
+    if ((int64_t)grad_output->nelements != T * d) return NULL;
+    const int64_t flat[2] = {T, d};
+    boat_tensor_t *g2 = NULL, *da = NULL, *du = NULL, *dh2 = NULL, *dh2_3 = NULL, *dln2 = NULL, *dr1 = NULL,
+                  *gq = NULL, *gk = NULL, *gv = NULL, *s1 = NULL, *dh1 = NULL, *dln1 = NULL, *dx = NULL;
+    /* MLP branch: out = r1 + dense2(GELU(dense1(LN2(r1)))) */
+    g2 = boat_tensor_reshape(grad_output, flat, 2);
+    da = g2 ? boat_dense_layer_backward(b->fc2, g2) : NULL;
+    du = da ? boat_gelu_backward(da, b->u) : NULL;
+    dh2 = du ? boat_dense_layer_backward(b->fc1, du) : NULL;
+    dh2_3 = dh2 ? boat_tensor_reshape(dh2, b->shape, 3) : NULL;
+    dln2 = dh2_3 ? boat_layernorm_backward(b->ln2, dh2_3) : NULL;
+    dr1 = dln2 ? boat_lincomb(grad_output, 1.0f, dln2, 1.0f) : NULL;
+    /* attention branch: r1 = x + attention(LN1(x)), query = key = value */
+    if (dr1 && boat_attention_backward(b->attn, dr1, &gq, &gk, &gv)) {
+        s1 = boat_lincomb(gq, 1.0f, gk, 1.0f);
+        dh1 = s1 ? boat_lincomb(s1, 1.0f, gv, 1.0f) : NULL;
+        dln1 = dh1 ? boat_layernorm_backward(b->ln1, dh1) : NULL;
+        dx = dln1 ? boat_lincomb(dr1, 1.0f, dln1, 1.0f) : NULL;
+    }
+    drop(g2, NULL); drop(da, NULL); drop(du, NULL); drop(dh2_3, NULL); drop(dh2, NULL); drop(dln2, NULL);
+    drop(dr1, NULL); drop(gq, NULL); drop(gk, NULL); drop(gv, NULL); drop(s1, NULL); drop(dh1, NULL); drop(dln1, NULL);
+    return dx;
+}

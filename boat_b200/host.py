@@ -418,9 +418,8 @@ def lincomb(a, alpha, b, beta):
 
 
 class EncoderBlock:
-    """Pre-LN transformer encoder block composed from the C API, one call per layer:
-    LN -> attention -> +x -> LN -> dense(4d) -> GELU -> dense(d) -> +, mean-squared-error loss.
-    The reference has no block object either; its tests chain layer calls by hand like this."""
+    """Pre-LN transformer encoder block (boat_encoder_block_t over five layers):
+    LN -> attention -> +x -> LN -> dense(4d) -> GELU -> dense(d) -> +, mean-squared-error loss."""
 
     def __init__(self, d, nh, causal=False, device=capi.DEVICE_CUDA, mma=capi.MMA_BF16, params=None):
         p = params or {}
@@ -438,29 +437,21 @@ class EncoderBlock:
         if device == capi.DEVICE_CUDA:
             self.attn.to_device(device)
         self.attn.set_precision(mma)
+        self.h = None
 
     def step(self, x, target):
-        """Forward, MSE gradient, backward.  Returns (out, dx); parameter gradients stay in the layers."""
+        """Forward, MSE gradient, backward through boat_encoder_block_forward / _backward.
+        Returns (out, dx); parameter gradients stay in the layers."""
         lib = capi.load()
         B, S, d = x.shape
-        T = B * S
-        h1 = self.ln1.forward(x)
-        att = self.attn.forward(h1)
-        r1 = lincomb(x, 1.0, att, 1.0)
-        h2 = self.ln2.forward(r1)
-        u = self.fc1.forward(reshape(h2, (T, d)))
-        a = Tensor(lib.boat_gelu(u.h))
-        m = reshape(self.fc2.forward(a), (B, S, d))
-        out = lincomb(r1, 1.0, m, 1.0)
-        scale = 2.0 / float(T * d)
+        if self.h is None:
+            self.h = C.c_void_p(lib.boat_encoder_block_create(self.ln1.h, self.attn.h, self.ln2.h, self.fc1.h, self.fc2.h))
+            if not self.h.value:
+                raise BoatError("boat_encoder_block_create returned NULL")
+        out = Tensor(lib.boat_encoder_block_forward(self.h, x.h))
+        scale = 2.0 / float(B * S * d)
         dout = lincomb(out, scale, target, -scale)
-        da = self.fc2.backward(reshape(dout, (T, d)))
-        du = Tensor(lib.boat_gelu_backward(da.h, u.h))
-        dh2 = self.fc1.backward(du)
-        dr1 = lincomb(dout, 1.0, self.ln2.backward(reshape(dh2, (B, S, d))), 1.0)
-        gq, gk, gv = self.attn.backward(dr1)
-        dh1 = lincomb(lincomb(gq, 1.0, gk, 1.0), 1.0, gv, 1.0)
-        dx = lincomb(dr1, 1.0, self.ln1.backward(dh1), 1.0)
+        dx = Tensor(lib.boat_encoder_block_backward(self.h, dout.h))
         return out, dx
 
     def zero_dense_grads(self):
@@ -470,5 +461,8 @@ class EncoderBlock:
         self.fc2.update(0.0)
 
     def free(self):
+        if self.h is not None:
+            capi.load().boat_encoder_block_free(self.h)
+            self.h = None
         for layer in (self.ln1, self.ln2, self.fc1, self.fc2, self.attn):
             layer.free()

@@ -50,6 +50,20 @@ BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
  * another device, so call boat_attention_to_device first.  Returns 0 on success. */
 BOAT_API int boat_attention_add_to_optimizer(boat_attention_t* attention, boat_optimizer_t* optimizer);
 
+/* A pre-LN transformer encoder block step composed from borrowed layers:
+ *   y = x + attention(LN1(x));  out = y + dense2(GELU(dense1(LN2(y))))
+ * forward returns out for x [B,S,d]; backward takes dL/dout and returns dL/dx, leaving the
+ * parameter gradients in the layers (dense gradients accumulate, as in the reference).  The
+ * reference has the layers but no such composition; this is the chain of layer calls a caller
+ * would write, issued from C.  free() releases the block's own state, not the layers. */
+typedef struct boat_encoder_block_t boat_encoder_block_t;
+BOAT_API boat_encoder_block_t* boat_encoder_block_create(boat_layernorm_t* norm1, boat_attention_t* attention,
+                                                         boat_layernorm_t* norm2, boat_dense_layer_t* dense1,
+                                                         boat_dense_layer_t* dense2);
+BOAT_API boat_tensor_t* boat_encoder_block_forward(boat_encoder_block_t* block, const boat_tensor_t* x);
+BOAT_API boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* block, const boat_tensor_t* grad_output);
+BOAT_API void boat_encoder_block_free(boat_encoder_block_t* block);
+
 /* Fill the layer's parameters from a safetensors checkpoint image (or file).  The reference
  * detects attention tensors by name in src/format/huggingface.c:917-932 and stops there (TODO);
  * this completes that step with the same name test: among the tensors whose name starts with

@@ -138,3 +138,11 @@ def test_compute_without_a_gpu_fails_loudly(lib):
     assert lib.boat_cuda_init(-1) != 0
     lib.boat_tensor_unref(x)
     lib.boat_attention_free(layer)
+
+
+def test_encoder_block_argument_checks(lib):
+    # no layers, no block; NULL blocks are refused without touching a device
+    assert lib.boat_encoder_block_create(None, None, None, None, None) is None
+    assert lib.boat_encoder_block_forward(None, None) is None
+    assert lib.boat_encoder_block_backward(None, None) is None
+    lib.boat_encoder_block_free(None)
