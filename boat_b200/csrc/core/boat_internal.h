@@ -25,6 +25,8 @@ struct boat_tensor_t {
 /* boat_tensor_create without the zero fill, for outputs a kernel overwrites completely. */
 boat_tensor_t* boat_tensor_create_uninit(const int64_t* shape, size_t ndim, boat_dtype_t dtype,
                                          boat_device_t device);
+/* A CUDA tensor around a buffer from boat_cuda_malloc; the tensor owns the buffer from then on. */
+boat_tensor_t* boat_tensor_adopt_device(const int64_t* shape, size_t ndim, boat_dtype_t dtype, void* device_data);
 /* A view of `bytes` bytes starting `offset_bytes` into `parent` with its own shape. */
 boat_tensor_t* boat_tensor_window(boat_tensor_t* parent, size_t offset_bytes, const int64_t* shape,
                                   size_t ndim);

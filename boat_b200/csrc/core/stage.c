@@ -67,6 +67,15 @@ boat_tensor_t* boat_emit_out(const int64_t* shape, size_t ndim, const boat_tenso
     return out;
 }
 
+boat_tensor_t* boat_emit_out_take(const int64_t* shape, size_t ndim, const boat_tensor_t* like, void** src, int type) {
+    if (like->device == BOAT_DEVICE_CUDA && boat_storage_of(like->dtype) == type && *src) {
+        boat_tensor_t* out = boat_tensor_adopt_device(shape, ndim, like->dtype, *src);
+        if (out) *src = NULL;
+        return out;
+    }
+    return boat_emit_out(shape, ndim, like, *src, type);
+}
+
 int boat_default_mma(boat_dtype_t dt) {
     if (dt == BOAT_DTYPE_BFLOAT16) return BOAT_MMA_BF16;
     const char* e = getenv("BOAT_MMA");

@@ -78,6 +78,24 @@ static boat_tensor_t* create_impl(const int64_t* shape, size_t ndim, boat_dtype_
     return t;
 }
 
+boat_tensor_t* boat_tensor_adopt_device(const int64_t* shape, size_t ndim, boat_dtype_t dtype, void* device_data) {
+    if (!device_data || (!shape && ndim > 0) || ndim > BOAT_MAX_DIMS) return NULL;
+    size_t n = 1;
+    for (size_t i = 0; i < ndim; ++i) {
+        if (shape[i] < 0) return NULL;
+        n *= (size_t)shape[i];
+    }
+    boat_tensor_t* t = new_record(shape, ndim);
+    if (!t) return NULL;
+    t->dtype = dtype;
+    t->device = BOAT_DEVICE_CUDA;
+    t->nelements = n;
+    t->nbytes = packed_bytes(dtype, n);
+    t->is_contiguous = true;
+    t->data = device_data;
+    return t;
+}
+
 boat_tensor_t* boat_tensor_create(const int64_t* shape, size_t ndim, boat_dtype_t dtype, boat_device_t device) {
     return create_impl(shape, ndim, dtype, device, true);
 }

@@ -558,12 +558,24 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
      * storage type the GEMM can emit. */
     {
         int out_type = storage_of(query->dtype);
-        d_out = dev_alloc((size_t)T * H * storage_size(out_type));
-        if (!d_out) goto done;
-        if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_ctx, H, p.w[WO], H, type,
-                                                            d_out, H, out_type, p.b[WO])) != 0)
-            goto done;
-        result = emit_out(query->shape, 3, query, d_out, out_type);
+        if (query->device == BOAT_DEVICE_CUDA) {
+            /* a CUDA result is the GEMM's own output buffer: no copy */
+            result = boat_tensor_create_uninit(query->shape, 3, query->dtype, BOAT_DEVICE_CUDA);
+            if (!result) goto done;
+            if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_ctx, H, p.w[WO], H, type,
+                                                                result->data, H, out_type, p.b[WO])) != 0) {
+                boat_tensor_free(result);
+                result = NULL;
+                goto done;
+            }
+        } else {
+            d_out = dev_alloc((size_t)T * H * storage_size(out_type));
+            if (!d_out) goto done;
+            if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_ctx, H, p.w[WO], H, type,
+                                                                d_out, H, out_type, p.b[WO])) != 0)
+                goto done;
+            result = emit_out(query->shape, 3, query, d_out, out_type);
+        }
     }
     if (result) a->cached = true;
 done:
@@ -681,15 +693,26 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     for (int i = 0; i < 3; ++i) {
         const boat_tensor_t* x = a->cache_in[i];
         int out_type = storage_of(x->dtype);
-        d_dx = dev_alloc((size_t)T * H * storage_size(out_type));
-        if (!d_dx) goto done;
-        if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, T, H, H, d_dproj[i], H, p.w[i], H, type, d_dx, H, out_type, NULL)) != 0) goto done;
+        void* dx_target;
+        if (x->device == BOAT_DEVICE_CUDA) {
+            /* a CUDA gradient is the GEMM's own output buffer: no copy */
+            gin[i] = boat_tensor_create_uninit(x->shape, 3, x->dtype, BOAT_DEVICE_CUDA);
+            if (!gin[i]) goto done;
+            dx_target = gin[i]->data;
+        } else {
+            d_dx = dev_alloc((size_t)T * H * storage_size(out_type));
+            if (!d_dx) goto done;
+            dx_target = d_dx;
+        }
+        if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, T, H, H, d_dproj[i], H, p.w[i], H, type, dx_target, H, out_type, NULL)) != 0) goto done;
         if (boat_report("dW", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_in[i], H, d_dproj[i], H, type, d_dw[i], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
         if (bias && boat_report("db", boat_cuda_colsum(d_dproj[i], type, T, H, d_db[i])) != 0) goto done;
-        gin[i] = emit_out(x->shape, 3, x, d_dx, out_type);
-        dev_free(d_dx);
-        d_dx = NULL;
-        if (!gin[i]) goto done;
+        if (x->device != BOAT_DEVICE_CUDA) {
+            gin[i] = emit_out(x->shape, 3, x, d_dx, out_type);
+            dev_free(d_dx);
+            d_dx = NULL;
+            if (!gin[i]) goto done;
+        }
     }
     if (a->device != BOAT_DEVICE_CUDA &&
         boat_report("gradient download", boat_cuda_memcpy_d2h(a->grad_bucket->data, d_bucket, a->grad_bucket->nbytes)) != 0)

@@ -71,7 +71,7 @@ boat_tensor_t* boat_dense_layer_forward(boat_dense_layer_t* l, const boat_tensor
     const int64_t oshape[2] = {N, O};
     if (dx && dw && dy && (!l->bias || db) &&
         boat_report("dense forward", boat_cuda_gemm(mma, 0, 0, N, O, I, dx, I, dw, O, type, dy, O, type, db)) == 0)
-        out = boat_emit_out(oshape, 2, input, dy, type);
+        out = boat_emit_out_take(oshape, 2, input, &dy, type);
     boat_dev_free(dy);
     if (xo) boat_dev_free(dx);
     if (wo) boat_dev_free(dw);
@@ -122,7 +122,7 @@ BOAT_NOINLINE boat_tensor_t* boat_dense_layer_backward(boat_dense_layer_t* l, co
                 boat_dev_free(acc);
             }
         }
-        if (boat_report("dense gradient accumulation", rc) == 0) out = boat_emit_out(x->shape, 2, x, d_dx, type);
+        if (boat_report("dense gradient accumulation", rc) == 0) out = boat_emit_out_take(x->shape, 2, x, &d_dx, type);
     }
     boat_dev_free(d_db);
     boat_dev_free(d_dw);

@@ -91,7 +91,7 @@ boat_tensor_t* boat_layernorm_forward(boat_layernorm_t* n, const boat_tensor_t* 
     if (dx && dy && n->d_mean && n->d_rstd && (!n->weight || dg) && (!n->bias || db) &&
         boat_report("LayerNorm forward", boat_cuda_layernorm_fwd(dx, type, rows, H, dg, db, n->config.eps, dy,
                                                                  n->d_mean, n->d_rstd)) == 0)
-        out = boat_emit_out(input->shape, input->ndim, input, dy, type);
+        out = boat_emit_out_take(input->shape, input->ndim, input, &dy, type);
     boat_dev_free(dy);
     if (xo) boat_dev_free(dx);
     if (go) boat_dev_free(dg);
@@ -131,7 +131,7 @@ boat_tensor_t* boat_layernorm_backward(boat_layernorm_t* n, const boat_tensor_t*
         int rc = 0;
         if (host_params && d_dgamma) rc = boat_cuda_memcpy_d2h(n->grad_weight->data, d_dgamma, (size_t)H * 4);
         if (rc == 0 && host_params && d_dbeta) rc = boat_cuda_memcpy_d2h(n->grad_bias->data, d_dbeta, (size_t)H * 4);
-        if (boat_report("gradient download", rc) == 0) out = boat_emit_out(x->shape, x->ndim, x, dx, type);
+        if (boat_report("gradient download", rc) == 0) out = boat_emit_out_take(x->shape, x->ndim, x, &dx, type);
     }
     if (host_params) {
         boat_dev_free(d_dgamma);

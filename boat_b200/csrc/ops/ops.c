@@ -221,7 +221,7 @@ static boat_tensor_t* gelu_impl(const boat_tensor_t* x, const boat_tensor_t* gra
     if (dx && dy && (!grad || dg)) {
         int rc = grad ? boat_cuda_gelu_bwd(dy, dg, dx, type, (int64_t)x->nelements)
                       : boat_cuda_gelu_fwd(dy, dx, type, (int64_t)x->nelements);
-        if (boat_report("GELU", rc) == 0) out = boat_emit_out(x->shape, x->ndim, x, dy, type);
+        if (boat_report("GELU", rc) == 0) out = boat_emit_out_take(x->shape, x->ndim, x, &dy, type);
     }
     boat_dev_free(dy);
     if (xo) boat_dev_free(dx);
@@ -240,7 +240,7 @@ boat_tensor_t* boat_lincomb(const boat_tensor_t* a, float alpha, const boat_tens
     boat_tensor_t* out = NULL;
     if (da && db && dy &&
         boat_report("lincomb", boat_cuda_lincomb(dy, da, alpha, db, beta, type, (int64_t)a->nelements)) == 0)
-        out = boat_emit_out(a->shape, a->ndim, a, dy, type);
+        out = boat_emit_out_take(a->shape, a->ndim, a, &dy, type);
     boat_dev_free(dy);
     if (ao) boat_dev_free(da);
     if (bo) boat_dev_free(db);
