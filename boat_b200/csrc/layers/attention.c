@@ -229,6 +229,16 @@ enum { MAX_CHUNKS = 8 };
 
 static bool on_host(const boat_tensor_t* t) { return t->device != BOAT_DEVICE_CUDA; }
 
+/* BOAT_HOST_PIPELINE=0 in the environment selects the one-piece path for host tensors too. */
+static bool pipeline_enabled(void) {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("BOAT_HOST_PIPELINE");
+        enabled = !(e && e[0] == '0');
+    }
+    return enabled != 0;
+}
+
 /* First batch entry of chunk c when B entries are cut into n chunks. */
 static int64_t chunk_begin(int64_t B, int n, int c) { return B * c / n; }
 
@@ -519,7 +529,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
     void* d_out = NULL;
     boat_tensor_t* result = NULL;
     if (!stage_params(a, mma, type, &p)) goto done;
-    if (B >= 2 && on_host(query) && on_host(key) && on_host(value)) {
+    if (B >= 2 && pipeline_enabled() && on_host(query) && on_host(key) && on_host(value)) {
         result = forward_pipelined(a, in, mma, type, &p);
         if (result) a->cached = true;
         goto done;
@@ -657,7 +667,7 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         d_dw[i] = d_bucket + (size_t)i * H * H;
         d_db[i] = bias ? d_bucket + (size_t)4 * H * H + (size_t)i * H : NULL;
     }
-    if (B >= 2 && on_host(grad_output) && on_host(a->cache_in[0]) && on_host(a->cache_in[1]) &&
+    if (B >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) && on_host(a->cache_in[1]) &&
         on_host(a->cache_in[2])) {
         ok = backward_pipelined(a, grad_output, mma, type, &p, d_dw, d_db, gin);
         goto done;
