@@ -448,7 +448,8 @@ def main():
 
         es = 2 if bf16 else 4
         n_e2e = max(2, min(args.steps, 5))
-        host_step()
+        for _ in range(2):               # warm-up: page-locked pool growth, copy streams, first-use set-up
+            host_step()
         if dist is not None:
             dist.barrier()
         t0 = time.perf_counter()
