@@ -212,3 +212,27 @@ def test_automatic_precision_uses_tensor_cores_within_tf32_tolerance(gpu_lib):
     ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], 2, False)
     res = gpu_step(inp, 2, False, device=capi.DEVICE_CUDA, precision=-1)
     assert_close(res, ref, TOL_TF32, "auto")
+
+
+# ---- host tensors travel in overlapped chunks of batch entries: same numbers as in one piece --------------
+
+@pytest.mark.parametrize("B,S,H,nh,precision,bf16,self_attn", [
+    (10, 128, 128, 2, capi.MMA_BF16, True, True),      # 10 entries in 8 chunks: uneven chunk sizes
+    (3, 256, 256, 2, capi.MMA_BF16, True, False),      # fewer entries than chunks; distinct q, k, v (three uploads)
+    (9, 128, 128, 2, capi.MMA_TF32, False, True),      # FP32 host tensors, TF32 rounding per chunk
+    (5, 40, 48, 3, capi.MMA_FP32, False, False),       # exact path, ragged shape
+], ids=["bf16_10x128", "bf16_3x256_qkv", "tf32_9x128", "fp32_5x40_qkv"])
+def test_chunked_host_path_equals_the_device_path(gpu_lib, B, S, H, nh, precision, bf16, self_attn):
+    case = cases.Case("chunks", B, S, H, nh, causal=True, self_attn=self_attn, bias_std=0.1)
+    inp = case.inputs(bf16=bf16)
+    host = gpu_step(inp, nh, True, device=capi.DEVICE_CPU, precision=precision, bf16=bf16)
+    dev = gpu_step(inp, nh, True, device=capi.DEVICE_CUDA, precision=precision, bf16=bf16)
+    fh, fd = cases.flatten_result(host), cases.flatten_result(dev)
+    for key in fd:
+        if key.startswith(("dw", "db")):
+            # sums over all rows: computed once over all rows in both paths, but their kernels
+            # combine partial sums with atomics, whose order varies from launch to launch
+            assert np.abs(fh[key] - fd[key]).max() <= 1e-5 * np.abs(fd[key]).max(), key
+        else:
+            # per-row arithmetic is the same in both paths
+            assert np.array_equal(fh[key], fd[key]), key
