@@ -404,7 +404,8 @@ def main():
     }
     kbytes = {"adam_step": 28.0 * (4 * d * d + 4 * d)}     # p, g, m, v read; p, m, v written (FP32)
     # dram__bytes_read.sum + dram__bytes_write.sum per (batch, head) unit from the ncu capture of
-    # one batch entry of C4 (profiles/flash_kernels_hs128_ncu_full.md: 290.3 MB for 16 units); the
+    # one batch entry of C4 (the committed ncu summary of the head-size-128 kernels: 290.3 MB for
+    # 16 units); the
     # kernel's traffic is proportional to the number of units of that shape
     ncu_traffic_per_unit = {("flash_bwd", 8192, 128, True): 290.3e6 / 16}
     roofline = None
