@@ -4,10 +4,11 @@
 // probabilities of the forward and builds four more [B,nh,S,S] tensors.  Here P is rebuilt
 // from the saved log-sum-exp, tile by tile, and nothing of size S x S touches HBM.
 //
-// One CTA owns one 128-row key/value tile of one (batch,head) unit and walks the query
-// tiles that see it (all of them, or those at or below the diagonal when causal).  K and V
-// stay in shared memory, dK and dV accumulate in tensor memory for the whole walk.  Per
-// query tile, with everything transposed so that key rows sit on the TMEM lanes:
+// A walk: one 128-row key/value tile of one (batch,head) unit against the query tiles that see
+// it (all of them, or those at or below the diagonal when causal).  K and V stay in shared
+// memory, dK and dV accumulate in tensor memory for the whole walk.  A CTA does two walks of
+// its unit back to back (when causal, tile j and tile n-1-j: n+1 query tiles for every CTA).
+// Per query tile, with everything transposed so that key rows sit on the TMEM lanes:
 //
 //   S^T  = K . Q^T                                              SS MMA into region R0
 //   P^T  = exp2(S^T*c - lse)        phase A, 8 softmax warps, written over S^T in R0 (BF16)
@@ -118,27 +119,40 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t* q_empty = bars + 22;              // [Q_STAGES] S^T and dK of the tile are complete: its Q stage is free
     uint64_t* p_full = bars + 3;                // P^T in TMEM (256 arrivals)
     uint64_t* r0_free = bars + 4;               // dP^T loaded into registers (256 arrivals)
+    uint64_t* kv_empty = bars + 1;              // the first walk's MMAs are complete: K and V may be replaced
+    uint64_t* acc_free = bars + 2;              // dK, dV of the first walk are stored (256 arrivals)
     uint32_t* tmem_slot = (uint32_t*)(bars + 25);
     volatile uint32_t* softmax_ok = tmem_slot + 1;     // [2] written by one softmax thread, read by all 256
     volatile uint32_t* drain_ok = tmem_slot + 3;       // same idea for the dQ warps
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = p.S / kTile;
-    // CTA order: units in groups of p.group; inside a group the key tile is the slow index.
+    // CTA order: units in groups of p.group; inside a group the key-tile pair is the slow index.
     // The CTAs that run at the same time then belong to a few (batch, head) units, so the FP32 dQ
     // rows they reduce into (S*HS*4 bytes per unit) and the unit's Q and dO stay in L2 - with
     // key tiles as the slow index over all units, the dQ buffer of a large problem (268 MB at 64
-    // units x 8192 x 128) no longer fits and every reduction misses to HBM.  Small jt (the long
-    // walk when causal) comes first, so a group ends with its short CTAs.
-    const int per_group = p.group * n_tiles;
+    // units x 8192 x 128) no longer fits and every reduction misses to HBM.
+    // A CTA walks two key tiles of its unit, one after the other: with a causal mask tile pj and
+    // tile n_tiles-1-pj, whose walks together are n_tiles+1 query tiles for every pj, so all CTAs
+    // carry the same load; without a mask two neighbouring tiles.  Start-up, the last tile's
+    // read-out and the exit of a CTA are paid once per pair, and the second walk starts while the
+    // first one's dQ is still draining.
+    const int n_pairs = (n_tiles + 1) / 2;
+    const int per_group = p.group * n_pairs;
     const int grp = blockIdx.x / per_group;
     const int rem = blockIdx.x - grp * per_group;
     const int in_group = min(p.group, p.units - grp * p.group);
-    const int jt = rem / in_group;
+    const int pj = rem / in_group;
     const int unit = grp * p.group + rem % in_group;
-    const int i_begin = p.causal ? jt : 0;
-    const int n_q = n_tiles - i_begin;
+    const int jtA = p.causal ? pj : 2 * pj;
+    const int jtB = p.causal ? n_tiles - 1 - pj : 2 * pj + 1;
+    const bool has_b = jtB != jtA && jtB < n_tiles;
+    const int ibA = p.causal ? jtA : 0, ibB = p.causal ? jtB : 0;
+    const int nA = n_tiles - ibA;                       // query tiles of the first walk
+    const int n_q = nA + (has_b ? n_tiles - ibB : 0);   // of both
     const int row_base = unit * p.S;
+    // query tile and key tile of step gt of the combined walk
+    auto qtile = [&](int gt) { return gt < nA ? ibA + gt : ibB + gt - nA; };
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
@@ -155,6 +169,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_init(dq_full, 1);
         mbar_init(dq_empty, 1);
         mbar_init(all_done, 1);
+        mbar_init(kv_empty, 1);
+        mbar_init(acc_free, 256);
         fence_barrier_init();
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
@@ -171,26 +187,33 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_arrive_expect_tx(kv_full, 2 * C::TILE_BYTES);
-            for (int b = 0; b < C::NBOX; ++b) {
-                tma_load_2d(k_smem + b * kBoxBytes, &map_k, kv_full, b * 64, row_base + jt * kTile);
-                tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jt * kTile);
-            }
+            auto load_kv = [&](int jt) {
+                mbar_arrive_expect_tx(kv_full, 2 * C::TILE_BYTES);
+                for (int b = 0; b < C::NBOX; ++b) {
+                    tma_load_2d(k_smem + b * kBoxBytes, &map_k, kv_full, b * 64, row_base + jt * kTile);
+                    tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jt * kTile);
+                }
+            };
+            load_kv(jtA);
             // dO of the first Q_STAGES query tiles; later ones are loaded by the dQ warps, which stage
             // dQ through the dO buffers and know when one is free again
             for (int t = 0; t < n_q && t < C::Q_STAGES; ++t) {
                 mbar_arrive_expect_tx(&do_full[t], C::TILE_BYTES);
                 for (int b = 0; b < C::NBOX; ++b)
                     tma_load_2d(do_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_do, &do_full[t], b * 64,
-                                row_base + (i_begin + t) * kTile);
+                                row_base + qtile(t) * kTile);
             }
             for (int t = 0; t < n_q; ++t) {
+                if (t == nA) {                  // second walk: its K and V, once the first walk's MMAs are done
+                    if (!mbar_wait(kv_empty, 0, p.status, kTimeoutProducer)) break;
+                    load_kv(jtB);
+                }
                 const int s = t % C::Q_STAGES;
                 if (!mbar_wait(&q_empty[s], ((t / C::Q_STAGES) & 1) ^ 1, p.status, kTimeoutProducer)) break;
                 mbar_arrive_expect_tx(&q_full[s], C::TILE_BYTES);
                 for (int b = 0; b < C::NBOX; ++b)
                     tma_load_2d(q_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[s], b * 64,
-                                row_base + (i_begin + t) * kTile);
+                                row_base + qtile(t) * kTile);
             }
         }
     } else if (warp == 1) {
@@ -240,21 +263,31 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             if (C::DP_OWN) ok = ok && issue_dp(0);
             for (int t = 0; t < n_q && ok; ++t) {
                 const int s = t % C::Q_STAGES;
+                const bool first = t == 0 || t == nA;           // first tile of a walk: dK, dV start over
+                const bool early_next = t + 1 < n_q && t + 1 != nA;   // the next tile belongs to the same walk
                 const uint32_t q_addr = smem_u32(q_smem + s * C::TILE_BYTES);
                 const uint32_t do_addr = smem_u32(do_smem + s * C::TILE_BYTES);
+                if (t == nA) {
+                    // second walk: wait for its K and V, then the MMAs a walk begins with.  R0 (and with
+                    // head size 64 the dP^T columns) are free: phase B of the previous tile is over.
+                    if (!mbar_wait(kv_full, 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    if (!issue_s(t)) { ok = false; break; }
+                    if (C::DP_OWN && !issue_dp(t)) { ok = false; break; }
+                }
                 if (!mbar_wait(p_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 if (!mbar_wait(&do_full[s], (t / C::Q_STAGES) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                if (t == nA && !mbar_wait(acc_free, 0, p.status, kTimeoutMma)) { ok = false; break; }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
                     mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + (kk / 4) * 64 + (kk % 4) * 8,
-                                  smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
+                                  smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, !first || kk > 0);
                 if (C::DP_OWN) {
                     // R0 is free as soon as dV, ahead on the pipe, has read P^T
-                    if (t + 1 < n_q && !issue_s(t + 1)) { ok = false; break; }
+                    if (early_next && !issue_s(t + 1)) { ok = false; break; }
                 } else {
                     if (!issue_dp(t)) { ok = false; break; }
-                    if (t + 1 < n_q) {
+                    if (early_next) {
                         if (!mbar_wait(r0_free, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
                         if (!issue_s(t + 1)) { ok = false; break; }
                     }
@@ -269,7 +302,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int kk = 0; kk < kTile / 16; ++kk) {    // dK += dS^T . Q
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
                     mma_ss<false>(tmem_base + C::COL_DK, smem_desc_sw128(ds_addr + off, 16, 1024),
-                                  smem_desc_mn(q_addr + kk * 2048, kBoxBytes, false), idesc_acc, t > 0 || kk > 0);
+                                  smem_desc_mn(q_addr + kk * 2048, kBoxBytes, false), idesc_acc, !first || kk > 0);
                 }
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dQ_i = dS . K        (K = 128 key rows)
@@ -277,8 +310,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                   smem_desc_mn(k_addr + kk * 2048, kBoxBytes, false), idesc_dq, kk > 0);
                 mma_commit(&q_empty[s]);
                 mma_commit(dq_full);      // also: this tile's dO stage and the dS^T tile are no longer read
+                if (t == nA - 1 && has_b) {
+                    mma_commit(kv_empty);                   // K and V of the first walk are no longer read
+                    mma_commit(all_done);                   // and its dK, dV are complete
+                }
                 // dS^T of tile t is in shared memory, so the softmax warps are done with dP^T(t)
-                if (C::DP_OWN && t + 1 < n_q && !issue_dp(t + 1)) { ok = false; break; }
+                if (C::DP_OWN && early_next && !issue_dp(t + 1)) { ok = false; break; }
             }
             if (ok) mma_commit(all_done);
         }
@@ -299,9 +336,38 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         bool ok = true;
         // threads 0..127 carry lse of query row (tid & 127), threads 128..255 delta
         const float* stat_src = (tid256 < 128 ? p.lse : p.delta) + row_base + (tid256 & 127);
-        float stat_next = stat_src[(int64_t)i_begin * kTile];
+        float stat_next = stat_src[(int64_t)qtile(0) * kTile];
+        // dK, dV of a finished walk: the first four warps store dV, the other four dK.  One thread
+        // does the bounded wait and publishes the outcome so that all 256 take the same branch.
+        auto store_dkdv = [&](int jt, uint32_t phase) -> bool {
+            if (tid256 == 0) softmax_ok[0] = mbar_wait(all_done, phase, p.status, kTimeoutEpilogue) ? 1u : 0u;
+            named_barrier_sync(1, 256);
+            const bool fine = softmax_ok[0] != 0u;
+            named_barrier_sync(1, 256);                 // everybody has read the flag before it is reused
+            if (!fine) return false;
+            tc_fence_after_sync();
+            const int64_t grow = (int64_t)row_base + (int64_t)jt * kTile + r;
+            __nv_bfloat16* out = (__nv_bfloat16*)(half ? p.dK : p.dV) + grow * HS;
+            const uint32_t col = half ? C::COL_DK : C::COL_DV;
+#pragma unroll 1
+            for (int c = 0; c < HS / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + col + lane_addr + c * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 32; x += 8) {
+                    uint4 o;
+                    o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
+                    o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
+                    o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
+                    o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
+                    *reinterpret_cast<uint4*>(out + c * 32 + x) = o;
+                }
+            }
+            return true;
+        };
         for (int t = 0; t < n_q; ++t) {
-            const int i = i_begin + t;
+            const int i = qtile(t);
             // Stage lse*log2e and delta of this query tile in the buffer of this tile's parity.
             // A thread can only get two tiles ahead of another by passing the barriers of the
             // tile in between, which needs that other thread to have left this tile.
@@ -311,14 +377,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // otherwise sit on the critical path between two tiles); fetch the next one now.
             if (tid256 < 128) lse_s[tid256] = stat_next * -1.4426950408889634f;        // -lse in the log2 domain
             else delta_s[tid256 - 128] = stat_next * -p.scale;                         // -delta / sqrt(hs)
-            if (t + 1 < n_q) stat_next = stat_src[(int64_t)(i + 1) * kTile];
+            if (t + 1 < n_q) stat_next = stat_src[(int64_t)qtile(t + 1) * kTile];
             // One thread does each bounded wait and publishes the outcome, so that all 256 take
             // the same branch and nobody is left alone at a named barrier.
             if (tid256 == 0) softmax_ok[0] = mbar_wait(s_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
             named_barrier_sync(1, 256);
             if (softmax_ok[0] == 0u) { ok = false; break; }
             tc_fence_after_sync();
-            const bool diag = p.causal && i == jt;
+            const bool diag = p.causal && i == (t < nA ? jtA : jtB);
             // ---- phase A: P^T = exp2(S^T*c - lse) for this thread's 64 columns ----
             uint32_t ph[32];                                        // 64 probabilities as BF16 pairs
             {
@@ -400,29 +466,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             fence_proxy_async_smem();
             mbar_arrive(ds_full);
-        }
-        // final: the first four warps store dV, the other four dK
-        if (ok && mbar_wait(all_done, 0, p.status, kTimeoutEpilogue)) {
-            tc_fence_after_sync();
-            const int64_t grow = (int64_t)row_base + (int64_t)jt * kTile + r;
-            __nv_bfloat16* out = (__nv_bfloat16*)(half ? p.dK : p.dV) + grow * HS;
-            const uint32_t col = half ? C::COL_DK : C::COL_DV;
-#pragma unroll 1
-            for (int c = 0; c < HS / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + col + lane_addr + c * 32, v);
-                tmem_wait_ld();
-#pragma unroll
-                for (int x = 0; x < 32; x += 8) {
-                    uint4 o;
-                    o.x = pack_bf16(__uint_as_float(v[x]), __uint_as_float(v[x + 1]));
-                    o.y = pack_bf16(__uint_as_float(v[x + 2]), __uint_as_float(v[x + 3]));
-                    o.z = pack_bf16(__uint_as_float(v[x + 4]), __uint_as_float(v[x + 5]));
-                    o.w = pack_bf16(__uint_as_float(v[x + 6]), __uint_as_float(v[x + 7]));
-                    *reinterpret_cast<uint4*>(out + c * 32 + x) = o;
-                }
+            if (t == nA - 1 && has_b) {
+                // end of the first walk: its dK, dV leave tensor memory before the second walk's first
+                // dV and dK MMAs start them over
+                if (!store_dkdv(jtA, 0u)) { ok = false; break; }
+                tc_fence_before_sync();
+                mbar_arrive(acc_free);
             }
         }
+        // final: dK, dV of the walk that ended last
+        if (ok) store_dkdv(has_b ? jtB : jtA, has_b ? 1u : 0u);
     } else {
         // ---------------- dQ reduction: warps 10..13, thread = query row ----------------
         // The FP32 dQ tile is HS/32 boxes of 128 rows x 128 bytes, twice the size of the tile's dO
@@ -440,7 +493,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             named_barrier_sync(2, 128);
             if (drain_ok[0] == 0u) break;
             tc_fence_after_sync();
-            const int y = row_base + (i_begin + t) * kTile;
+            const int y = row_base + qtile(t) * kTile;
             uint8_t* stage = do_smem + s * C::TILE_BYTES;
             auto stage_half = [&](const uint32_t (&v)[C::NBOX][32]) {
 #pragma unroll
@@ -484,7 +537,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 if (t + C::Q_STAGES < n_q) {
                     mbar_arrive_expect_tx(&do_full[s], C::TILE_BYTES);
                     for (int b = 0; b < C::NBOX; ++b)
-                        tma_load_2d(stage + b * kBoxBytes, &map_do, &do_full[s], b * 64, y + C::Q_STAGES * kTile);
+                        tma_load_2d(stage + b * kBoxBytes, &map_do, &do_full[s], b * 64,
+                                    row_base + qtile(t + C::Q_STAGES) * kTile);
                 }
             }
         }

@@ -99,7 +99,7 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     {
         ProfileScope prof("flash_bwd");
         BOATCU_CHECK(cudaMemsetAsync(dq_accum, 0, n * sizeof(float), stream()));
-        const int64_t grid = units * (S / kTile);
+        const int64_t grid = units * ((S / kTile + 1) / 2);      // a CTA walks two key tiles of a unit
         kern<<<(unsigned)grid, kBwdThreads, C::SMEM, stream()>>>(mq, mk, mv, mdo, mdq, p);
         BOATCU_LAUNCH_OK("flash_bwd");
         // the summed FP32 contributions become the BF16 output
