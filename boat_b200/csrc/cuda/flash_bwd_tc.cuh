@@ -75,6 +75,7 @@ struct BwdParams {
     void* dV;
     int S, units, causal;
     int group;             // units scheduled together, see the kernel
+    int pair;              // 1: a CTA walks two key tiles of its unit, 0: one
     float scale;
     unsigned int* status;
 };
@@ -137,16 +138,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // carry the same load; without a mask two neighbouring tiles.  Start-up, the last tile's
     // read-out and the exit of a CTA are paid once per pair, and the second walk starts while the
     // first one's dQ is still draining.
-    const int n_pairs = (n_tiles + 1) / 2;
+    // (p.pair == 0: one walk per CTA - better when the walks are long or the CTAs few, see the
+    // launcher.)
+    const int n_pairs = p.pair ? (n_tiles + 1) / 2 : n_tiles;
     const int per_group = p.group * n_pairs;
     const int grp = blockIdx.x / per_group;
     const int rem = blockIdx.x - grp * per_group;
     const int in_group = min(p.group, p.units - grp * p.group);
     const int pj = rem / in_group;
     const int unit = grp * p.group + rem % in_group;
-    const int jtA = p.causal ? pj : 2 * pj;
+    const int jtA = !p.pair || p.causal ? pj : 2 * pj;
     const int jtB = p.causal ? n_tiles - 1 - pj : 2 * pj + 1;
-    const bool has_b = jtB != jtA && jtB < n_tiles;
+    const bool has_b = p.pair && jtB != jtA && jtB < n_tiles;
     const int ibA = p.causal ? jtA : 0, ibB = p.causal ? jtB : 0;
     const int nA = n_tiles - ibA;                       // query tiles of the first walk
     const int n_q = nA + (has_b ? n_tiles - ibB : 0);   // of both

@@ -1,6 +1,7 @@
 // flash_tc.cu - host side of the tcgen05 attention-core kernels: shape support, tensor maps,
 // launches.  The kernels themselves are in flash_fwd_tc.cuh and flash_bwd_tc.cuh.
 #include "flash_bwd_tc.cuh"
+#include <stdlib.h>
 
 namespace boatcu {
 
@@ -88,6 +89,22 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     const int64_t unit_bytes = S * HS * 16;
     int64_t group = (64ll << 20) / unit_bytes;
     p.group = (int)(group < 1 ? 1 : (group > units ? units : group));
+    // Two walks per CTA halve what a CTA pays once (start-up, the last tile's read-out, exit) and
+    // equalise the CTAs when causal: 5-10 % at 8- and 16-tile walks.  With equal CTAs the last
+    // wave is a loss that many short CTAs would fill, and at 64-tile walks the per-CTA cost is
+    // small anyway (measured: no gain at 64 tiles, 10 % slower when only 3.5 waves of pairs exist).
+    const int64_t n_tiles = S / kTile;
+    p.pair = (n_tiles <= 32 && units * ((n_tiles + 1) / 2) >= 8 * 148) ? 1 : 0;
+    {
+        // BOAT_BWD_PAIR=0/1 in the environment overrides the rule (the tests force both schedules
+        // on small problems)
+        static int forced = -2;
+        if (forced == -2) {
+            const char* e = getenv("BOAT_BWD_PAIR");
+            forced = (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
+        }
+        if (forced >= 0) p.pair = forced;
+    }
     p.scale = scale;
     p.status = kernel_status_ptr();
     auto kern = flash_bwd_kernel<HS>;
@@ -99,7 +116,7 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     {
         ProfileScope prof("flash_bwd");
         BOATCU_CHECK(cudaMemsetAsync(dq_accum, 0, n * sizeof(float), stream()));
-        const int64_t grid = units * ((S / kTile + 1) / 2);      // a CTA walks two key tiles of a unit
+        const int64_t grid = units * (p.pair ? (S / kTile + 1) / 2 : S / kTile);
         kern<<<(unsigned)grid, kBwdThreads, C::SMEM, stream()>>>(mq, mk, mv, mdo, mdq, p);
         BOATCU_LAUNCH_OK("flash_bwd");
         // the summed FP32 contributions become the BF16 output

@@ -229,3 +229,19 @@ def test_profile_report_lists_kernel_families(gpu_lib):
     check(lib.boat_cuda_profile_enable(0))
     names = {line.split()[0]: float(line.split()[2]) for line in buf.value.decode().splitlines()}
     assert "gemm_tc_nn" in names and names["gemm_tc_nn"] > 0
+
+
+def test_backward_schedules_one_and_two_walks_per_cta():
+    """The tensor-core backward picks one or two key-tile walks per CTA from the problem size;
+    BOAT_BWD_PAIR forces either.  The attention-core and layer parity tests must pass under both
+    (sequence lengths of 1, 2, 3 and 8 tiles cover the unpaired middle tile and the causal pairing)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for forced in ("0", "1"):
+        env = dict(os.environ, BOAT_BWD_PAIR=forced)
+        proc = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "tests/test_kernels_gpu.py", "tests/test_parity_gpu.py",
+                               "-k", "attention_core or bf16_tensor_core or chunked"],
+                              cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
+        assert proc.returncode == 0, "BOAT_BWD_PAIR=%s:\n%s" % (forced, proc.stdout[-3000:])
