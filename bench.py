@@ -214,7 +214,7 @@ def run_reference_arm(args, cfg, rank, world):
     line = dict(impl="reference", metric="attention_fwd_bwd_tokens_per_s", value=value, unit="tokens/s", n_gpus=world,
                 steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * cfg["B"] * cfg["S"] / value,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-                config=workload_config(args.workload, cfg, world), cpu_baseline=base,
+                config=dict(workload_config(args.workload, cfg, world), optimizer=args.optimizer), cpu_baseline=base,
                 e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 sample_seconds_per_step=secs)
     print(json.dumps(line))
