@@ -212,6 +212,7 @@ PROTOTYPES = {
     "boat_cuda_launch_count": (C.c_uint64, []),
     "boat_cuda_profile_enable": (_I, [_I]),
     "boat_cuda_profile_report": (_I, [C.c_char_p, _SZ]),
+    "boat_cuda_selftest_wait_timeout": (_I, [C.c_uint64]),
     "boat_cuda_gemm": (_I, [_I, _I, _I, _I64, _I64, _I64, _P, _I64, _P, _I64, _I, _P, _I64, _I, _P]),
     "boat_cuda_attn_fwd": (_I, [_I, _I64, _I64, _I64, _I, _F, _P, _P, _P, _I, _P, _P]),
     "boat_cuda_attn_bwd_scratch_bytes": (_SZ, [_I, _I64, _I64, _I64]),

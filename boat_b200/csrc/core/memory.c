@@ -18,7 +18,9 @@ typedef struct {
 } block_header_t;
 
 /* Host blocks of this size and above hold tensor data that will be copied to or from the
- * GPU; they are taken page-locked (and re-used) when a GPU is present. */
+ * GPU; they are taken page-locked (and re-used) once the library has been bound to a GPU
+ * (boat_cuda_init, or the first compute call).  A host allocation never starts the GPU by
+ * itself: before that, and without a GPU, the block is ordinary memory. */
 #define BOAT_PINNED_THRESHOLD ((size_t)256 * 1024)
 
 static boat_memory_stats_t g_stats;

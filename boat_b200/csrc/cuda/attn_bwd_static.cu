@@ -26,8 +26,13 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 void* g_scratch_addr[kMaxDevices];
 
 int scratch_address(void** out) {
+    // ensure_init() has made the library's device current for this thread; anything else here
+    // would hand out another GPU's copy of the block.
     int dev = -1;
     BOATCU_CHECK(cudaGetDevice(&dev));
+    if (dev != bound_device())
+        return set_error(40, "boat_cuda_attn_bwd_static: current device %d is not the library's device %d", dev,
+                         bound_device());
     if (dev < 0 || dev >= kMaxDevices) return set_error(40, "device index %d out of range", dev);
     if (!g_scratch_addr[dev]) {
         void* ptr = nullptr;
@@ -54,6 +59,7 @@ int boat_cuda_attn_bwd_static(int mma, int64_t units, int64_t S, int64_t hs, int
     if (!ready())
         return set_error(41, "boat_cuda_attn_bwd_static: call boat_cuda_init first - this entry point never "
                              "initialises the library, because initialising allocates");
+    if (int rc = ensure_init()) return rc;     // already initialised: only makes the bound device current
     if (units < 0 || S < 0 || hs < 0) return set_error(41, "boat_cuda_attn_bwd_static: negative size");
     const size_t need = boat_cuda_attn_bwd_scratch_bytes(mma, units, S, hs);
     if (need > kStaticScratchBytes)

@@ -8,7 +8,6 @@
 namespace boatcu {
 
 static const int kThreads = 256;
-static const int kSMs = 148;
 
 // One CTA per 256 work items, no persistent cap: for these streaming kernels the hardware's
 // CTA scheduler balances better than a grid-stride loop over 8 CTAs per SM (measured on the
@@ -410,7 +409,7 @@ int boat_cuda_colsum(const void* X, int x_type, int64_t rows, int64_t cols, floa
     const bool can_vec = (cols % vec) == 0 && aligned16(X);
     const int cols_per_block = 32 * (can_vec ? vec : 1);
     dim3 grid((unsigned)ceil_div(cols, cols_per_block), 1, 1);
-    int64_t want = (int64_t)kSMs * 8 / grid.x;
+    int64_t want = (int64_t)sm_count() * 8 / grid.x;
     int64_t max_y = ceil_div(rows, 8);
     grid.y = (unsigned)(want < 1 ? 1 : (want > max_y ? max_y : want));
     if (grid.y > 65535) grid.y = 65535;

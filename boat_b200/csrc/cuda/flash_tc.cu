@@ -94,16 +94,12 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     // wave is a loss that many short CTAs would fill, and at 64-tile walks the per-CTA cost is
     // small anyway (measured: no gain at 64 tiles, 10 % slower when only 3.5 waves of pairs exist).
     const int64_t n_tiles = S / kTile;
-    p.pair = (n_tiles <= 32 && units * ((n_tiles + 1) / 2) >= 8 * 148) ? 1 : 0;
+    p.pair = (n_tiles <= 32 && units * ((n_tiles + 1) / 2) >= 8 * (int64_t)sm_count()) ? 1 : 0;
     {
-        // BOAT_BWD_PAIR=0/1 in the environment overrides the rule (the tests force both schedules
-        // on small problems)
-        static int forced = -2;
-        if (forced == -2) {
-            const char* e = getenv("BOAT_BWD_PAIR");
-            forced = (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
-        }
-        if (forced >= 0) p.pair = forced;
+        // BOAT_BWD_PAIR=0/1 in the environment overrides the rule; it is read at every launch so
+        // that one test process can run both schedules on the same problem
+        const char* e = getenv("BOAT_BWD_PAIR");
+        if (e && (e[0] == '0' || e[0] == '1')) p.pair = e[0] - '0';
     }
     p.scale = scale;
     p.status = kernel_status_ptr();

@@ -31,7 +31,6 @@ namespace {
 constexpr int BM = 128;
 constexpr int STAGES = 4;
 constexpr int kThreads = 192;
-constexpr int kSMs = 148;
 
 template <typename T, int BN>
 struct Cfg {
@@ -251,6 +250,7 @@ int launch(int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const vo
     const int m_tiles = (int)ceil_div(M, BM), n_tiles = (int)ceil_div(N, BN);
     const int k_blocks = (int)ceil_div(K, C::BK);
     const int tiles = m_tiles * n_tiles;
+    const int kSMs = sm_count();
     int split_k = 1;
     if (out_type == BOAT_CUDA_F32 && tiles * 2 <= kSMs) {
         // few output tiles (weight gradients): spread K over the idle SMs, at least 8 K-blocks each
@@ -276,7 +276,7 @@ int launch(int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const vo
     p.split_k = split_k;
     p.status = kernel_status_ptr();
     auto kern = gemm_tc_kernel<T, A_MN, B_MN, BN>;
-    static bool configured = false;
+    static bool configured = false;     // per process = per device: the library binds to one device
     if (!configured) {
         BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;

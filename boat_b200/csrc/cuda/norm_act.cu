@@ -468,7 +468,7 @@ static int bwd_warp_launch(const void* dy, const void* x, int64_t rows, const fl
                            const float* rstd, void* dx, float* dgamma, float* dbeta) {
     constexpr int COLS = NV * 32 * (16 / (int)sizeof(T));
     int64_t blocks = ceil_div(rows, kNormThreads / 32);
-    if (blocks > 148 * 4) blocks = 148 * 4;         // persistent: the column sums live in registers across rows
+    if (blocks > sm_count() * 4) blocks = sm_count() * 4;         // persistent: the column sums live in registers across rows
     const size_t smem = (dgamma || dbeta) ? 2 * COLS * sizeof(float) : 0;
     layernorm_bwd_warp_kernel<T, NV><<<(unsigned)blocks, kNormThreads, smem, stream()>>>(
         (const T*)dy, (const T*)x, rows, gamma, mean, rstd, (T*)dx, dgamma, dbeta);
@@ -551,7 +551,7 @@ int boat_cuda_layernorm_bwd(const void* dy, const void* x, int type, int64_t row
     if (dbeta) BOATCU_CHECK(cudaMemsetAsync(dbeta, 0, (size_t)cols * sizeof(float), stream()));
     if (int done = layernorm_bwd_warp(dy, x, type, rows, cols, gamma, mean, rstd, dx, dgamma, dbeta)) return done < 0 ? 0 : done;
     dim3 pgrid((unsigned)ceil_div(cols, 32), 1);
-    int64_t want = 148 * 8 / pgrid.x, max_y = ceil_div(rows, 8);
+    int64_t want = (int64_t)sm_count() * 8 / pgrid.x, max_y = ceil_div(rows, 8);
     pgrid.y = (unsigned)(want < 1 ? 1 : (want > max_y ? max_y : want));
     if (type == BOAT_CUDA_BF16) {
         typedef __nv_bfloat16 bf;

@@ -18,6 +18,8 @@ namespace boatcu {
 static thread_local char g_err[512] = "";
 static std::mutex g_mu;
 static bool g_ready = false;
+static int g_device = -1;                       // the one device this process's library is bound to
+static int g_sm_count = 0;
 static cudaStream_t g_stream = 0;
 static std::atomic<uint64_t> g_launches{0};
 static std::unordered_map<void*, size_t>* g_live = nullptr;
@@ -47,7 +49,13 @@ static int pick_device(int requested) {
 }
 
 static int init_locked(int device) {
-    if (g_ready) return 0;
+    if (g_ready) {
+        // The library serves one device per process (one process per GPU); a later request for
+        // another one is an error, not a silent no-op.
+        if (device >= 0 && device != g_device)
+            return set_error(6, "boat_cuda_init(%d): the library is already bound to device %d", device, g_device);
+        return 0;
+    }
     int n = 0;
     cudaError_t err = cudaGetDeviceCount(&n);
     if (err != cudaSuccess || n == 0) {
@@ -56,7 +64,7 @@ static int init_locked(int device) {
                          err == cudaSuccess ? "device count is 0" : cudaGetErrorString(err));
     }
     int dev = pick_device(device);
-    if (dev >= n) dev = dev % n;
+    if (dev < 0 || dev >= n) return set_error(2, "device index %d out of range: %d device(s) visible", dev, n);
     BOATCU_CHECK(cudaSetDevice(dev));
     cudaDeviceProp prop;
     BOATCU_CHECK(cudaGetDeviceProperties(&prop, dev));
@@ -74,9 +82,14 @@ static int init_locked(int device) {
     BOATCU_CHECK(cudaHostAlloc((void**)&g_status_host, sizeof(unsigned int), cudaHostAllocMapped));
     *g_status_host = 0;
     BOATCU_CHECK(cudaHostGetDevicePointer((void**)&g_status_dev, g_status_host, 0));
+    g_device = dev;
+    g_sm_count = prop.multiProcessorCount;
     g_ready = true;
     return 0;
 }
+
+int bound_device() { return g_device; }
+int sm_count() { return g_sm_count > 0 ? g_sm_count : 1; }
 
 // ---- kernel status word ---------------------------------------------------------------------
 // One 32-bit word in mapped pinned host memory.  Kernels write a code there when a bounded
@@ -150,10 +163,21 @@ ProfileScope::~ProfileScope() {
     if (slot >= 0) cudaEventRecord((*g_profile)[slot].stop, g_stream);
 }
 
+// The current device is a per-thread setting of the CUDA runtime: a thread that enters the
+// library for the first time is switched to the bound device, so that its launches and the
+// pointers it is handed belong to the same GPU.
+static thread_local bool t_on_bound_device = false;
+
 int ensure_init() {
-    if (g_ready) return 0;
-    std::lock_guard<std::mutex> lk(g_mu);
-    return init_locked(-1);
+    if (!g_ready) {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (int rc = init_locked(-1)) return rc;
+    }
+    if (!t_on_bound_device) {
+        BOATCU_CHECK(cudaSetDevice(g_device));
+        t_on_bound_device = true;
+    }
+    return 0;
 }
 
 }  // namespace boatcu
@@ -163,8 +187,11 @@ using namespace boatcu;
 extern "C" {
 
 int boat_cuda_init(int device) {
-    std::lock_guard<std::mutex> lk(g_mu);
-    return init_locked(device);
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (int rc = init_locked(device)) return rc;
+    }
+    return ensure_init();
 }
 
 int boat_cuda_device_count(void) {
@@ -314,11 +341,29 @@ int boat_cuda_memset(void* dst, int value, size_t bytes) {
 // Large host tensors are the source and destination of every upload and download of the
 // host-tensor path.  Page-locked memory makes those copies several times faster, but locking
 // pages costs milliseconds per allocation, so freed blocks are kept and handed out again.
+// Freed blocks stay page-locked for re-use up to a cap (BOAT_PINNED_POOL_MB, default 4096); beyond
+// it a freed block is unlocked and returned to the system at once.
+// A plain host allocation never starts the GPU: before boat_cuda_init (explicit, or implicit in the
+// first compute call) host_alloc declines and the caller uses ordinary memory.
 static std::multimap<size_t, void*>* g_pinned_free = nullptr;
 static std::unordered_map<void*, size_t>* g_pinned_size = nullptr;
+static size_t g_pinned_free_bytes = 0;
+
+static size_t pinned_pool_cap() {
+    static size_t cap = 0;
+    if (cap == 0) {
+        const char* e = getenv("BOAT_PINNED_POOL_MB");
+        long long mb = e && *e ? atoll(e) : 4096;
+        if (mb < 0) mb = 0;
+        cap = (size_t)mb << 20;
+        if (cap == 0) cap = 1;      // "0" = keep nothing
+    }
+    return cap;
+}
 
 void* boat_cuda_host_alloc(size_t bytes) {
-    if (bytes == 0 || ensure_init() != 0) return nullptr;
+    if (bytes == 0 || !g_ready) return nullptr;
+    if (ensure_init() != 0) return nullptr;
     std::lock_guard<std::mutex> lk(g_mu);
     if (!g_pinned_free) {
         g_pinned_free = new std::multimap<size_t, void*>();
@@ -327,6 +372,7 @@ void* boat_cuda_host_alloc(size_t bytes) {
     auto it = g_pinned_free->lower_bound(bytes);
     if (it != g_pinned_free->end() && it->first <= bytes + bytes / 4) {
         void* p = it->second;
+        g_pinned_free_bytes -= it->first;
         g_pinned_free->erase(it);
         return p;
     }
@@ -344,6 +390,12 @@ int boat_cuda_host_free(void* ptr) {
     std::lock_guard<std::mutex> lk(g_mu);
     auto it = g_pinned_size ? g_pinned_size->find(ptr) : std::unordered_map<void*, size_t>::iterator();
     if (!g_pinned_size || it == g_pinned_size->end()) return set_error(5, "boat_cuda_host_free: %p is not a pinned block", ptr);
+    if (g_pinned_free_bytes + it->second > pinned_pool_cap()) {
+        g_pinned_size->erase(it);
+        if (cudaFreeHost(ptr) != cudaSuccess) cudaGetLastError();
+        return 0;
+    }
+    g_pinned_free_bytes += it->second;
     g_pinned_free->insert({it->second, ptr});
     return 0;
 }

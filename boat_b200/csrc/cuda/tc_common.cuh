@@ -31,7 +31,8 @@ static constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
 
 enum StatusCode : unsigned int {
     kOk = 0,
-    kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3, kTimeoutSoftmax = 4, kTimeoutOther = 5
+    kTimeoutProducer = 1, kTimeoutMma = 2, kTimeoutEpilogue = 3, kTimeoutSoftmax = 4, kTimeoutOther = 5,
+    kTimeoutSelfTest = 9
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -69,20 +70,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Bounded wait.  Returns false (after recording `code`) when the limit is reached.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+// Bounded wait.  Returns false (after recording `code`) when `limit_ns` have passed, or when
+// another thread of any kernel has already recorded a give-up in the status word.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code,
+                                                unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     unsigned int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 1023u) == 0) {
-            if (global_ns() - t0 > kWaitLimitNs || *(volatile unsigned int*)status != 0) {
+            if (global_ns() - t0 > limit_ns || *(volatile unsigned int*)status != 0) {
                 atomicCAS(status, 0u, code);
                 return false;
             }
         }
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+    return mbar_wait_limit(bar, parity, status, code, kWaitLimitNs);
 }
 
 // ---- TMA ------------------------------------------------------------------------------------------

@@ -66,6 +66,13 @@ uint64_t    boat_cuda_launch_count(void);        /* kernels of this library laun
 int         boat_cuda_profile_enable(int on);
 int         boat_cuda_profile_report(char* out, size_t out_bytes);
 
+/* Self-test of the kernels' bounded waits (no counterpart in the reference).  Launches a
+ * one-block kernel that waits, for at most limit_ns (<= 1 s), on a barrier nobody completes:
+ * the wait gives up, records role code 9 in the kernel status word and the kernel returns
+ * normally.  The next boat_cuda_sync() / boat_cuda_memcpy_d2h() then fails with status 30 and
+ * clears the word; the call after that succeeds again.  Nothing hangs and nothing faults. */
+int         boat_cuda_selftest_wait_timeout(uint64_t limit_ns);
+
 /* ---- contraction: replaces boat_matmul (src/ops/linear.c:12-170) as used by
  *      linear_projection (src/layers/attention.c:247-308) and
  *      linear_projection_backward (attention.c:1186-1293), including the materialised
@@ -113,7 +120,9 @@ int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal
  * The scratch is a fixed 16 MiB block inside the library image (capacity() returns the
  * size); each GPU that loads the library holds it until the process exits.  Problems whose
  * boat_cuda_attn_bwd_scratch_bytes() exceeds it are refused with a clear error.
- * The call makes no cudaMalloc/cudaFree and no allocating library call.  It never
+ * The call makes no cudaMalloc/cudaFree and no allocating library call - with one exception:
+ * while boat_cuda_profile_enable(1) is in force, the timing scopes create CUDA events, so
+ * keep profiling off where allocation is banned.  It never
  * initialises the library: call boat_cuda_init() once beforehand (that does allocate).
  * The first call on a device looks up the block's device address; make that first call
  * outside any stream capture.  All calls share the one block and it keeps the previous

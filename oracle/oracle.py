@@ -546,3 +546,55 @@ def ref_graph_mlp(a, wm, wd, bd, c, m, gout):
         if bd is not None:
             res["dbd"] = RefTensor(lib, lib.boat_dense_layer_get_grad_bias(dense)).view((wd.shape[1],)).copy()
     return res
+
+
+def ref_ops(inp):
+    """The reference's generic tensor operations (src/ops/linear.c, src/ops/arithmetic.c) on the operands of
+    tests/cases.py::ops_inputs(); returns a dict of FP32 arrays."""
+    lib = ref()
+    P = C.c_void_p
+    lib.boat_transpose.restype = P
+    lib.boat_transpose.argtypes = [P, C.c_int, C.c_int]
+    for name in ("boat_add", "boat_mul", "boat_matmul"):
+        getattr(lib, name).restype = P
+        getattr(lib, name).argtypes = [P, P]
+    lib.boat_mul_scalar.restype = P
+    lib.boat_mul_scalar.argtypes = [P, C.c_double]
+    lib.boat_add_.argtypes = [P, P]
+    lib.boat_sub_.argtypes = [P, P]
+    lib.boat_add_.restype = None
+    lib.boat_sub_.restype = None
+    out = {}
+    made = []
+
+    def new(a):
+        h = _ref_new(lib, _f32(a))
+        made.append(h)
+        return h
+
+    def take(h, shape):
+        assert h, "the reference returned NULL"
+        made.append(h)
+        return RefTensor(lib, h).view(shape).copy()
+
+    with _quiet_scratch_cwd():
+        t4, t4r, t2 = inp["t4"], inp["t4_ragged"], inp["t2"]
+        out["transpose_t4"] = take(lib.boat_transpose(new(t4), 2, 3), t4.shape[:2] + (t4.shape[3], t4.shape[2]))
+        out["transpose_t4_ragged"] = take(lib.boat_transpose(new(t4r), 2, 3), t4r.shape[:2] + (t4r.shape[3], t4r.shape[2]))
+        out["transpose_t2"] = take(lib.boat_transpose(new(t2), 0, 1), t2.shape[::-1])
+        a, b, bias = inp["a"], inp["b"], inp["bias"]
+        out["add"] = take(lib.boat_add(new(a), new(b)), a.shape)
+        out["add_bias"] = take(lib.boat_add(new(a), new(bias)), a.shape)
+        out["mul"] = take(lib.boat_mul(new(a), new(b)), a.shape)
+        out["mul_scalar"] = take(lib.boat_mul_scalar(new(a), float(inp["scalar"])), a.shape)
+        ha = new(a)
+        lib.boat_add_(ha, new(b))
+        out["add_"] = RefTensor(lib, ha).view(a.shape).copy()
+        ha = new(a)
+        lib.boat_sub_(ha, new(b))
+        out["sub_"] = RefTensor(lib, ha).view(a.shape).copy()
+        out["matmul3"] = take(lib.boat_matmul(new(inp["m3a"]), new(inp["m3b"])), (3, 9, 11))
+        out["matmul4"] = take(lib.boat_matmul(new(inp["m4a"]), new(inp["m4b"])), (2, 3, 8, 6))
+        for h in made:
+            lib.boat_tensor_unref(h)
+    return out

@@ -142,3 +142,21 @@ def graph_mlp_inputs(N=19, I=24, M=40, O=16):
     return dict(a=rng.normal(SEED, 60, (N, I)), wm=rng.normal(SEED, 61, (I, M), 0.2), wd=rng.normal(SEED, 62, (M, O), 0.2),
                 bd=rng.normal(SEED, 63, (O,), 0.1), c=rng.normal(SEED, 64, (N, O)), m=rng.normal(SEED, 65, (N, O)),
                 gout=rng.normal(SEED, 66, (N, O)))
+
+
+# ---- generic tensor operations the path exports: seeded inputs for the golden vectors and tests -----------
+
+def ops_inputs():
+    """Operands for boat_transpose (the reference's own 4-D case, tests/unit/test_transpose.c:55-103, and
+    a ragged one), boat_add with a trailing-dimension broadcast (src/ops/arithmetic.c:199-203), boat_mul,
+    boat_mul_scalar, boat_add_ / boat_sub_ and batched boat_matmul."""
+    return dict(
+        t4=(np.arange(2 * 2 * 3 * 4, dtype=np.float32) + np.float32(1.0)).reshape(2, 2, 3, 4),
+        t4_ragged=rng.normal(SEED, 80, (3, 2, 37, 19)),
+        t2=rng.normal(SEED, 81, (45, 70)),
+        a=rng.normal(SEED, 82, (3, 17, 24)),
+        b=rng.normal(SEED, 83, (3, 17, 24)),
+        bias=rng.normal(SEED, 84, (24,)),
+        scalar=-0.37,
+        m3a=rng.normal(SEED, 85, (3, 9, 14)), m3b=rng.normal(SEED, 86, (3, 14, 11)),
+        m4a=rng.normal(SEED, 87, (2, 3, 8, 5)), m4b=rng.normal(SEED, 88, (2, 3, 5, 6)))

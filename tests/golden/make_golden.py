@@ -1,5 +1,5 @@
-"""Regenerate tests/golden/attention_golden.npz, adam_golden.npz and graph_golden.npz from the
-reference itself.
+"""Regenerate tests/golden/attention_golden.npz, adam_golden.npz, graph_golden.npz and
+ops_golden.npz from the reference itself.
 
 Run in a checkout that has the reference tree (oracle/Makefile builds
 oracle/_ref/libboat_ref.so from it):
@@ -15,6 +15,9 @@ adam_golden.npz holds the parameters after every step of the reference's Adam op
 graph_golden.npz holds outputs and gradients of two graphs run through the reference's
 autodiff (boat_var_attention + boat_var_add; boat_var_matmul, boat_var_dense, boat_var_mul,
 boat_var_sub) with boat_variable_backward.
+
+ops_golden.npz holds the reference's boat_transpose, boat_add (equal shapes and bias broadcast),
+boat_mul, boat_mul_scalar, boat_add_, boat_sub_ and batched boat_matmul on cases.ops_inputs().
 
 For every case in tests/cases.py::GOLDEN_CASES the reference's own boat_attention_forward
 and boat_attention_backward are executed on the seeded inputs and every output and gradient
@@ -97,6 +100,14 @@ def graphs():
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def ops():
+    out = oracle.ref_ops(cases.ops_inputs())
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ops_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     main()
     graphs()
+    ops()

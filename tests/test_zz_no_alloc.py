@@ -24,12 +24,16 @@ pytestmark = pytest.mark.gpu
 TOL = {capi.MMA_FP32: 1e-5, capi.MMA_BF16: 2e-2}
 
 
-def backward_both_ways(lib, mma, units, S, hs, causal, seed):
+def backward_both_ways(lib, mma, units, S, hs, causal, seed, numpy_rng=False):
     bf = mma == capi.MMA_BF16
     io = capi.CUDA_BF16 if bf else capi.CUDA_F32
     f = rng.bf16_round if bf else (lambda a: a)
     shape = (units, S, hs)
-    q, k, v, go = (f(rng.normal(seed, i, shape)) for i in range(4))
+    if numpy_rng:        # tens of millions of elements: numpy's generator is much faster than the counter-based one
+        g = np.random.default_rng(seed)
+        q, k, v, go = (g.standard_normal(shape, dtype=np.float32) for _ in range(4))
+    else:
+        q, k, v, go = (f(rng.normal(seed, i, shape)) for i in range(4))
     scale = 1.0 / np.sqrt(hs)
     dq_, dk_, dv_, dgo = (DeviceBuffer.from_numpy(a, bf16=bf) for a in (q, k, v, go))
     es = 2 if bf else 4
@@ -82,3 +86,18 @@ def test_static_scratch_refuses_problems_beyond_its_capacity(gpu_lib):
     assert rc != 0
     msg = lib.boat_cuda_last_error().decode()
     assert "scratch" in msg and str(lib.boat_cuda_attn_bwd_static_capacity()) in msg
+
+
+def test_static_scratch_accepts_a_problem_of_exactly_its_capacity(gpu_lib):
+    """The exact path needs 4 bytes of scratch per (unit, row): 32768 units of 128 rows fill the
+    16 MiB block to the last byte and are served; one unit more is refused."""
+    lib = gpu_lib
+    cap = lib.boat_cuda_attn_bwd_static_capacity()
+    units, S, hs = cap // (128 * 4), 128, 8
+    assert lib.boat_cuda_attn_bwd_scratch_bytes(capi.MMA_FP32, units, S, hs) == cap
+    ref, got = backward_both_ways(lib, capi.MMA_FP32, units, S, hs, True, seed=24, numpy_rng=True)
+    assert_same(ref, got, TOL[capi.MMA_FP32], "problem of exactly the capacity")
+    dummy = DeviceBuffer(256)
+    rc = lib.boat_cuda_attn_bwd_static(capi.MMA_FP32, units + 1, S, hs, 1, C.c_float(0.1), dummy.p, dummy.p, dummy.p,
+                                       dummy.p, dummy.p, dummy.p, capi.CUDA_F32, dummy.p, dummy.p, dummy.p)
+    assert rc != 0 and "scratch" in lib.boat_cuda_last_error().decode()
