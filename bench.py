@@ -74,10 +74,56 @@ def load_peaks():
     return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
 
 
+def measure_tf32_peak(torch):
+    """TF32 tensor-core peak measured the way the BF16 one in MEASURED_PEAKS.json was: torch.matmul
+    of two 8192 x 8192 FP32 matrices with TF32 allowed, 2*N^3 FLOP, CUDA events; best of 10 (burst)
+    and back to back for about 2 s (sustained).  Returns (burst, sustained) in TFLOP/s."""
+    n = 8192
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device="cuda", dtype=torch.float32)
+        b = torch.randn(n, n, device="cuda", dtype=torch.float32)
+        c = torch.empty(n, n, device="cuda", dtype=torch.float32)
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        flop = 2.0 * n ** 3
+        best = 0.0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(10):
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            best = max(best, flop / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        iters = max(20, int(2.0 / (flop / (best * 1e12))))
+        e0.record()
+        for _ in range(iters):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        torch.cuda.synchronize()
+        sustained = iters * flop / (e0.elapsed_time(e1) * 1e-3) / 1e12
+        return best, sustained
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def load_kernel_traffic():
+    """DRAM bytes per launch read from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum),
+    kept as data next to the ncu summaries: a list of {kernel, S, hs, causal, units, dram_bytes}."""
+    path = os.path.join(ROOT, "profiles", "kernel_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)["captures"]
+    except (OSError, ValueError, KeyError):
+        return []
+
+
 # ---- clocks ----------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """nvidia-smi sampled every 100 ms; started before the warm-up (the tool takes a moment
+    """nvidia-smi sampled every 20 ms; started before the warm-up (the tool takes a moment
     to start), only the samples between mark() at the start and at the end of the timed
     region are reported."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -89,7 +135,7 @@ class ClockSampler:
         self.lines = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -212,7 +258,10 @@ def run_reference_arm(args, cfg, rank, world):
     base["value"] = value
     base.pop("seconds", None)
     line = dict(impl="reference", metric="attention_fwd_bwd_tokens_per_s", value=value, unit="tokens/s", n_gpus=world,
-                steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * cfg["B"] * cfg["S"] / value,
+                steps=args.steps, warmup=args.warmup,
+                # a step of this arm is one bounded sample (the full workload would take hours on the
+                # CPU): ms_per_step is what a step really took; `value` extrapolates it to the workload
+                ms_per_step=1e3 * secs, ms_per_workload_step_extrapolated=1e3 * cfg["B"] * cfg["S"] / value,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
                 config=dict(workload_config(args.workload, cfg, world), optimizer=args.optimizer), cpu_baseline=base,
                 e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
@@ -403,25 +452,37 @@ def main():
         "flash_bwd": 8.0 * core_c * B * S * S * d, "attn_bwd_simt": 8.0 * core_c * B * S * S * d,
     }
     kbytes = {"adam_step": 28.0 * (4 * d * d + 4 * d)}     # p, g, m, v read; p, m, v written (FP32)
-    # dram__bytes_read.sum + dram__bytes_write.sum per (batch, head) unit from the ncu capture of
-    # one batch entry of C4 (the committed ncu summary of the head-size-128 kernels: 290.3 MB for
-    # 16 units); the
-    # kernel's traffic is proportional to the number of units of that shape
-    ncu_traffic_per_unit = {("flash_bwd", 8192, 128, True): 290.3e6 / 16}
     roofline = None
     if kern:
         top = max((k for k in kern if k in kflops), key=lambda k: kern[k][1], default=None)
         if top:
             n, ms = kern[top]
             achieved = kflops[top] / (ms / n * 1e-3) / 1e12
-            # kernels are timed inside a long step: the sustained figure is the denominator;
-            # TF32 has no measured entry, half of the BF16 figure stands in for it
-            peak = peaks["bf16_sustained"] if bf16 else peaks["bf16_sustained"] / 2
-            per_unit = ncu_traffic_per_unit.get((top, S, d // nh, bool(causal)))
+            # Denominator: the measured burst figure when the timed region is shorter than a second
+            # (clocks have not settled under the power cap yet), the sustained one otherwise; both
+            # fractions are on the line.  TF32 has no entry in MEASURED_PEAKS.json: it is measured
+            # here, the same way (torch.matmul 8192^3, FP32 storage, TF32 allowed).
+            region_s = ms_per_step * args.steps * 1e-3
+            if bf16:
+                burst, sustained, src = peaks["bf16"], peaks["bf16_sustained"], peaks["source"] + " bf16"
+            else:
+                burst, sustained = measure_tf32_peak(torch)
+                src = "measured live: torch.matmul 8192^3, FP32 storage, TF32 allowed"
+            use_burst = region_s < 1.0
+            peak = burst if use_burst else sustained
+            # DRAM traffic of that kernel from an ncu capture of the same tile shape, scaled by the number
+            # of (batch, head) units (every unit of a shape moves the same bytes)
+            traffic = None
+            for cap in load_kernel_traffic():
+                if (cap["kernel"], cap["S"], cap["hs"], bool(cap["causal"])) == (top, S, d // nh, bool(causal)):
+                    traffic = cap["dram_bytes"] / cap["units"] * B * nh
             roofline = dict(bound="tensor", kernel=top, achieved=achieved, peak=peak, unit="TFLOP/s",
-                            frac=achieved / peak, traffic=(per_unit * B * nh) if per_unit else None,
+                            frac=achieved / peak, traffic=traffic,
                             launches=n, avg_ms=ms / n,
-                            peak_source=peaks["source"] + (" bf16 sustained" if bf16 else " bf16 sustained / 2 for tf32"),
+                            peak_source=src + (" burst" if use_burst else " sustained") +
+                            " (timed region %.2f s)" % region_s,
+                            frac_of_burst=achieved / burst, frac_of_sustained=achieved / sustained,
+                            peak_burst=burst, peak_sustained=sustained,
                             kernels={k: dict(scopes=v[0], ms=round(v[1], 3), share=round(v[1] / sum(x[1] for x in kern.values()), 4))
                                      for k, v in sorted(kern.items(), key=lambda kv: -kv[1][1])})
             for k, nbytes in kbytes.items():
@@ -481,7 +542,7 @@ def main():
                     scaling="weak", vs_baseline=None, dtype="bf16" if bf16 else "tf32", data="synthetic",
                     config=dict(workload_config(args.workload, cfg, world), optimizer=args.optimizer),
                     tflops_per_gpu=tflops_per_gpu,
-                    frac_of_bf16_peak=(tflops_per_gpu / peaks["bf16_sustained"]) if bf16 else None,
+                    frac_of_bf16_peak=(tflops_per_gpu / (peaks["bf16"] if ms_per_step * args.steps < 1e3 else peaks["bf16_sustained"])) if bf16 else None,
                     roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches), clocks=clocks)
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())

@@ -1,7 +1,9 @@
 // dispatch.cu - the extern "C" contraction and attention-core entry points: argument checks
 // and the choice between the tcgen05 kernels and the CUDA-core kernels.  The choice is by
-// shape only - an explicit tensor-core request that the shape cannot satisfy is an error,
-// never a silent change of arithmetic.
+// shape only: a TF32 or BF16 request whose shape the tensor-core kernels do not cover
+// (sequence not a multiple of 128, head size other than 64 / 128, tiny or unaligned GEMMs)
+// runs on the CUDA cores with the same storage types and FP32 FMA arithmetic - at least as
+// accurate as what was asked for, never less.
 #include "common.cuh"
 
 using namespace boatcu;

@@ -155,12 +155,13 @@ static int env_precision(void) {
     return -1;
 }
 
-/* Arithmetic for a call: the explicit setting, else by input type and shape. */
-static int pick_mma(const boat_attention_t* a, const boat_tensor_t* q, int64_t S, int64_t hs) {
+/* Arithmetic for a call: the explicit setting (boat_attention_set_precision, or BOAT_MMA in the
+ * environment at create time), else by the input's storage type alone: BF16 tensors use BF16
+ * tensor cores, FP32 tensors the exact FP32 kernels - the numerics of a reference program never
+ * change with the sequence length.  TF32 is always an explicit choice. */
+static int pick_mma(const boat_attention_t* a, const boat_tensor_t* q) {
     if (a->precision >= 0) return a->precision;
-    if (q->dtype == BOAT_DTYPE_BFLOAT16) return BOAT_MMA_BF16;
-    if (S >= 128 && S % 128 == 0 && (hs == 64 || hs == 128)) return BOAT_MMA_TF32;
-    return BOAT_MMA_FP32;
+    return q->dtype == BOAT_DTYPE_BFLOAT16 ? BOAT_MMA_BF16 : BOAT_MMA_FP32;
 }
 
 static void drop_forward_state(boat_attention_t* a) {
@@ -516,7 +517,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
     drop_forward_state(a);
     for (int i = 0; i < 3; ++i) a->cache_in[i] = (boat_tensor_t*)in[i];
 
-    const int mma = pick_mma(a, query, S, hs);
+    const int mma = pick_mma(a, query);
     const int type = mma == BOAT_MMA_BF16 ? BOAT_CUDA_BF16 : BOAT_CUDA_F32;
     const int64_t T = B * S;
     const size_t act_bytes = (size_t)T * (size_t)H * storage_size(type);

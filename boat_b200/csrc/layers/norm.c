@@ -118,25 +118,30 @@ boat_tensor_t* boat_layernorm_backward(boat_layernorm_t* n, const boat_tensor_t*
     void* dy = boat_stage_in(grad_output, type, &yo);
     float* dg = n->weight ? (float*)boat_stage_in(n->weight, BOAT_CUDA_F32, &go) : NULL;
     void* dx = boat_dev_alloc(x->nelements * boat_storage_size(type));
+    /* Each parameter gradient lives where its parameter lives, and the two need not agree (a
+     * host bias set on a CUDA layer, a bias without a weight): the kernel writes a CUDA
+     * gradient in place and a host gradient through a device temporary that is then copied down. */
     float *d_dgamma = NULL, *d_dbeta = NULL;
-    bool host_params = n->weight && n->weight->device != BOAT_DEVICE_CUDA;
+    bool gamma_tmp = false, beta_tmp = false;
     boat_tensor_t* out = NULL;
-    if (n->weight && grad_like(&n->grad_weight, n->weight))
-        d_dgamma = host_params ? (float*)boat_dev_alloc((size_t)H * 4) : (float*)n->grad_weight->data;
-    if (n->bias && grad_like(&n->grad_bias, n->bias))
-        d_dbeta = host_params ? (float*)boat_dev_alloc((size_t)H * 4) : (float*)n->grad_bias->data;
+    if (n->weight && grad_like(&n->grad_weight, n->weight)) {
+        gamma_tmp = n->grad_weight->device != BOAT_DEVICE_CUDA;
+        d_dgamma = gamma_tmp ? (float*)boat_dev_alloc((size_t)H * 4) : (float*)n->grad_weight->data;
+    }
+    if (n->bias && grad_like(&n->grad_bias, n->bias)) {
+        beta_tmp = n->grad_bias->device != BOAT_DEVICE_CUDA;
+        d_dbeta = beta_tmp ? (float*)boat_dev_alloc((size_t)H * 4) : (float*)n->grad_bias->data;
+    }
     if (dx_in && dy && dx && (!n->weight || (dg && d_dgamma)) && (!n->bias || d_dbeta) &&
         boat_report("LayerNorm backward", boat_cuda_layernorm_bwd(dy, dx_in, type, rows, H, dg, n->d_mean, n->d_rstd,
                                                                   dx, d_dgamma, d_dbeta)) == 0) {
         int rc = 0;
-        if (host_params && d_dgamma) rc = boat_cuda_memcpy_d2h(n->grad_weight->data, d_dgamma, (size_t)H * 4);
-        if (rc == 0 && host_params && d_dbeta) rc = boat_cuda_memcpy_d2h(n->grad_bias->data, d_dbeta, (size_t)H * 4);
+        if (gamma_tmp && d_dgamma) rc = boat_cuda_memcpy_d2h(n->grad_weight->data, d_dgamma, (size_t)H * 4);
+        if (rc == 0 && beta_tmp && d_dbeta) rc = boat_cuda_memcpy_d2h(n->grad_bias->data, d_dbeta, (size_t)H * 4);
         if (boat_report("gradient download", rc) == 0) out = boat_emit_out_take(x->shape, x->ndim, x, &dx, type);
     }
-    if (host_params) {
-        boat_dev_free(d_dgamma);
-        boat_dev_free(d_dbeta);
-    }
+    if (gamma_tmp) boat_dev_free(d_dgamma);
+    if (beta_tmp) boat_dev_free(d_dbeta);
     boat_dev_free(dx);
     if (xo) boat_dev_free(dx_in);
     if (yo) boat_dev_free(dy);

@@ -29,9 +29,24 @@ _FP = C.POINTER(C.c_float)
 _FP4 = _FP * 4
 
 
+def reference_tree():
+    """Where the reference's sources are: BOAT_REFERENCE_TREE, else a directory named
+    "reference" beside the repository; None when neither holds the attention layer."""
+    candidates = [os.environ.get("BOAT_REFERENCE_TREE"),
+                  os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in candidates:
+        if c and os.path.exists(os.path.join(c, "src", "layers", "attention.c")):
+            return c
+    return None
+
+
 def build():
     """Compile liboracle.so and, when the reference tree is present, _ref/libboat_ref.so."""
-    proc = subprocess.run(["make", "-C", _HERE], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    cmd = ["make", "-C", _HERE]
+    tree = reference_tree()
+    if tree:
+        cmd.append("REF=" + tree)
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if proc.returncode != 0:
         raise RuntimeError("building the oracle failed:\n" + proc.stdout[-4000:])
 

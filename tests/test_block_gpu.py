@@ -60,6 +60,39 @@ def test_layernorm_backward_matches_restatement(gpu_lib, shape):
     layer.free()
 
 
+def test_layernorm_backward_with_parameters_on_different_devices(gpu_lib):
+    """A CUDA layer whose bias was replaced by a host tensor (boat_layernorm_set_bias), its mirror
+    image, and a layer created without parameters that was given a bias only: each gradient must
+    land where its parameter lives."""
+    lib = gpu_lib
+    rows_shape, H = (4, 9), 96
+    ln = cases.layernorm_inputs(rows_shape, H)
+    rdx, rdg, rdb = oracle.port_layernorm_backward(ln["dy"], ln["x"], ln["w"], ln["eps"])
+    for w_dev, b_dev in ((capi.DEVICE_CUDA, capi.DEVICE_CPU), (capi.DEVICE_CPU, capi.DEVICE_CUDA)):
+        layer = host.LayerNorm(H, ln["eps"], ln["w"], ln["b"], affine=True, device=w_dev)
+        bias = Tensor.from_numpy(ln["b"], b_dev)
+        lib.boat_layernorm_set_bias(layer.h, bias.h)
+        layer.forward(Tensor.from_numpy(ln["x"], capi.DEVICE_CUDA))
+        dx = layer.backward(Tensor.from_numpy(ln["dy"], capi.DEVICE_CUDA))
+        gw = Tensor(lib.boat_layernorm_get_grad_weight(layer.h), own=False)
+        gb = Tensor(lib.boat_layernorm_get_grad_bias(layer.h), own=False)
+        assert gw.device == w_dev and gb.device == b_dev
+        assert rel(dx.numpy(), rdx) <= 2e-5 and rel(gw.numpy(), rdg) <= 2e-5 and rel(gb.numpy(), rdb) <= 2e-5
+        layer.free()
+    # no weight at all, a host bias set afterwards: dbeta is the column sum of dy
+    layer = host.LayerNorm(H, ln["eps"], affine=False)
+    bias = Tensor.from_numpy(ln["b"], capi.DEVICE_CPU)
+    lib.boat_layernorm_set_bias(layer.h, bias.h)
+    layer.forward(Tensor.from_numpy(ln["x"], capi.DEVICE_CUDA))
+    dx = layer.backward(Tensor.from_numpy(ln["dy"], capi.DEVICE_CUDA))
+    assert dx.h.value
+    assert lib.boat_layernorm_get_grad_weight(layer.h) is None
+    gb = Tensor(lib.boat_layernorm_get_grad_bias(layer.h), own=False)
+    assert gb.device == capi.DEVICE_CPU
+    assert rel(gb.numpy(), ln["dy"].reshape(-1, H).astype(np.float64).sum(0)) <= 2e-5
+    layer.free()
+
+
 def test_layernorm_bf16_storage(gpu_lib):
     ln = cases.layernorm_inputs((4, 64), 256)
     x, dy = rng.bf16_round(ln["x"]), rng.bf16_round(ln["dy"])

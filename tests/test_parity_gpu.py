@@ -206,12 +206,19 @@ def test_fp32_inputs_with_bf16_arithmetic(gpu_lib):
     assert_close(res, ref, TOL_BF16, "mixed")
 
 
-def test_automatic_precision_uses_tensor_cores_within_tf32_tolerance(gpu_lib):
+def test_automatic_precision_keeps_fp32_tensors_exact_at_tensor_core_shapes(gpu_lib):
+    """Without an explicit choice FP32 tensors are computed in exact FP32 even where the shape
+    would suit the tensor cores (S a multiple of 128, head size 64): a reference program's
+    numbers do not change with the sequence length.  BF16 tensors select BF16 arithmetic."""
     case = cases.Case("auto", 1, 256, 128, 2)
     inp = case.inputs()
     ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], 2, False)
     res = gpu_step(inp, 2, False, device=capi.DEVICE_CUDA, precision=-1)
-    assert_close(res, ref, TOL_TF32, "auto")
+    assert_close(res, ref, TOL_FP32, "auto, fp32 tensors")
+    inp = case.inputs(bf16=True)
+    ref = oracle.port_step(inp["q"], inp["k"], inp["v"], inp["w"], inp["b"], inp["dout"], 2, False)
+    res = gpu_step(inp, 2, False, device=capi.DEVICE_CUDA, precision=-1, bf16=True)
+    assert_close(res, ref, TOL_BF16, "auto, bf16 tensors")
 
 
 # ---- host tensors travel in overlapped chunks of batch entries: same numbers as in one piece --------------
