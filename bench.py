@@ -123,19 +123,19 @@ def load_kernel_traffic():
 # ---- clocks ----------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """nvidia-smi sampled every 20 ms; started before the warm-up (the tool takes a moment
+    """nvidia-smi sampled every `interval_ms`; started before the warm-up (the tool takes a moment
     to start), only the samples between mark() at the start and at the end of the timed
     region are reported."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
+    def __init__(self, index, interval_ms=50):
         self.proc = None
         self.lines = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "20"],
+                                          "--format=csv,noheader,nounits", "-lms", str(interval_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -293,6 +293,8 @@ def main():
                     help="adam: every step ends with boat_optimizer_step over the attention parameters")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-tensor end-to-end measurement")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--clock-interval-ms", type=int, default=50,
+                    help="nvidia-smi sampling period; much shorter periods slow down launch-bound workloads")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
     rank = int(os.environ.get("RANK", "0"))
@@ -399,7 +401,7 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(local_rank, args.clock_interval_ms) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     sync_all()

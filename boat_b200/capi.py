@@ -169,8 +169,10 @@ PROTOTYPES = {
     "boat_attention_to_device": (_I, [_P, _I]),
     "boat_attention_set_precision": (_I, [_P, _I]),
     "boat_attention_get_precision": (_I, [_P]),
+    "boat_attention_forward_units": (_P, [_P, _P, _P, _P, _I64]),
     "boat_attention_grad_bucket": (_I, [_P, C.POINTER(C.POINTER(C.c_float)), C.POINTER(_SZ)]),
     "boat_attention_allreduce_grads": (_I, [_P]),
+    "boat_attention_set_grad_overlap": (_I, [_P, _I]),
     "boat_attention_add_to_optimizer": (_I, [_P, _P]),
     "boat_encoder_block_create": (_P, [_P, _P, _P, _P, _P]),
     "boat_encoder_block_forward": (_P, [_P, _P]),
@@ -237,6 +239,9 @@ PROTOTYPES = {
     "boat_cuda_comm_init": (_I, [_I, _I, _P]),
     "boat_cuda_comm_world": (_I, []),
     "boat_cuda_allreduce_sum_f32": (_I, [_P, _I64]),
+    "boat_cuda_allreduce_begin": (_I, [_P, _P, _I]),
+    "boat_cuda_allreduce_join": (_I, []),
+    "boat_cuda_allreduce_pending": (_I, []),
     "boat_cuda_comm_destroy": (_I, []),
 }
 for _name in _ACCESSORS:

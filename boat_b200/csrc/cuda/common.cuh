@@ -17,6 +17,7 @@ int ensure_init();
 bool ready();          // has boat_cuda_init (or a first call) bound the library to a device yet?
 int bound_device();    // index of that device, -1 before
 int sm_count();        // its number of SMs (grid sizing); 1 before the library is bound
+int comm_stream_sync();   // waits for gradient sums still running on the communication stream
 
 // Optional per-kernel timing (boat_cuda_profile_*): while enabled, a scope records a CUDA
 // event pair on the library stream around the launches it encloses.

@@ -275,6 +275,7 @@ int boat_cuda_sync(void) {
         BOATCU_CHECK(cudaStreamSynchronize(g_down));
         g_copy_pending = false;
     }
+    if (int rc = comm_stream_sync()) return rc;
     return report_kernel_status("boat_cuda_sync");
 }
 

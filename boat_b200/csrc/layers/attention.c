@@ -35,12 +35,17 @@ struct boat_attention_t {
     boat_tensor_t* grad_bucket;         /* FP32, on `device`                       */
     boat_device_t  device;              /* where the parameters live               */
     int            precision;           /* -1 automatic, else BOAT_MMA_*           */
+    bool           grad_overlap;        /* backward starts the gradient sums itself */
 
     /* state of the last forward, consumed by backward */
     boat_tensor_t* cache_in[3];         /* query, key, value - referenced          */
     bool           cached;
     int            mma, type;           /* arithmetic and storage type it used     */
-    int64_t        B, S;
+    int64_t        T, S;                /* token rows and sequence length of the call        */
+    int64_t        units;               /* (batch, head) units = T * nh / S                  */
+    int64_t        gran;                /* units per indivisible piece when the work is cut
+                                           into chunks: nh (a whole batch entry) for [B,S,H]
+                                           inputs, 1 for a unit range (see forward_units)    */
     void*          d_in[3];             /* inputs on device in `type`              */
     bool           d_in_owned[3];
     void*          d_proj[3];           /* Qp, Kp, Vp [B*S, H]                     */
@@ -268,19 +273,21 @@ static int stage_rows(const boat_tensor_t* t, int mma, int type, void* dst, void
     return boat_report("chunk upload", rc);
 }
 
-/* Forward for host inputs, B >= 2.  Fills the layer's forward state like the one-piece path. */
+/* Forward for host inputs cut into at least two chunks.  Fills the layer's forward state like the
+ * one-piece path.  A chunk is a run of whole pieces of a->gran units, i.e. of gran*S/nh token rows. */
 static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t* const in[3], int mma, int type,
                                         const staged_params_t* p) {
     const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
-    const int64_t hs = (int64_t)a->config.head_size, B = a->B, S = a->S, T = B * S;
+    const int64_t hs = (int64_t)a->config.head_size, S = a->S, T = a->T;
+    const int64_t G = a->units / a->gran, grows = a->gran * S / nh;      /* pieces, token rows per piece */
     const size_t tsz = storage_size(type), act_bytes = (size_t)T * (size_t)H * tsz;
     const int out_type = storage_of(in[0]->dtype);
     const size_t osz = storage_size(out_type);
-    const int nchunk = (int)(B < MAX_CHUNKS ? B : MAX_CHUNKS);
+    const int nchunk = (int)(G < MAX_CHUNKS ? G : MAX_CHUNKS);
     void* raw[3] = {NULL, NULL, NULL};
     void* d_out = NULL;
     bool ok = false;
-    boat_tensor_t* result = boat_tensor_create_uninit(in[0]->shape, 3, in[0]->dtype, BOAT_DEVICE_CPU);
+    boat_tensor_t* result = boat_tensor_create_uninit(in[0]->shape, in[0]->ndim, in[0]->dtype, BOAT_DEVICE_CPU);
     if (!result) return NULL;
 
     for (int i = 0; i < 3; ++i) {
@@ -305,14 +312,14 @@ static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t
         if (!a->d_proj[i]) goto done;
     }
     a->d_ctx = dev_alloc(act_bytes);
-    a->d_lse = (float*)dev_alloc((size_t)B * nh * S * sizeof(float));
+    a->d_lse = (float*)dev_alloc((size_t)a->units * S * sizeof(float));
     d_out = dev_alloc((size_t)T * (size_t)H * osz);
     if (!a->d_ctx || !a->d_lse || !d_out) goto done;
     if (boat_report("copy streams", boat_cuda_copies_after_compute()) != 0) goto done;
 
     for (int c = 0; c < nchunk; ++c) {
-        const int64_t b0 = chunk_begin(B, nchunk, c), b1 = chunk_begin(B, nchunk, c + 1);
-        const int64_t r0 = b0 * S, nr = (b1 - b0) * S;
+        const int64_t b0 = chunk_begin(G, nchunk, c), b1 = chunk_begin(G, nchunk, c + 1);
+        const int64_t r0 = b0 * grows, nr = (b1 - b0) * grows;
         const size_t off = (size_t)(r0 * H) * tsz, ooff = (size_t)(r0 * H) * osz;
         for (int i = 0; i < 3; ++i)
             if (a->d_in_owned[i] && stage_rows(in[i], mma, type, a->d_in[i], raw[i], r0, nr, H) != 0) goto done;
@@ -323,9 +330,9 @@ static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t
             if (settle_tf32(mma, (char*)a->d_proj[i] + off, nr * H) != 0) goto done;
         }
         if (boat_report("attention core",
-                        boat_cuda_attn_fwd(mma, (b1 - b0) * nh, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
+                        boat_cuda_attn_fwd(mma, (b1 - b0) * a->gran, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
                                            (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
-                                           type, (char*)a->d_ctx + off, a->d_lse + b0 * nh * S)) != 0)
+                                           type, (char*)a->d_ctx + off, a->d_lse + b0 * a->gran * S)) != 0)
             goto done;
         if (settle_tf32(mma, (char*)a->d_ctx + off, nr * H) != 0) goto done;
         if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, nr, H, H, (char*)a->d_ctx + off, H, p->w[WO], H, type,
@@ -348,17 +355,18 @@ done:
 }
 
 
-/* Backward for a host grad_output and host inputs, B >= 2: dOut up, d(ctx), attention core and
- * the three input gradients per chunk of batch entries, input gradients down while the next
+/* Backward for a host grad_output and host inputs in at least two chunks: dOut up, d(ctx),
+ * attention core and the three input gradients per chunk, input gradients down while the next
  * chunk is computed; weight and bias gradients over all rows at the end. */
 static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_output, int mma, int type,
                                const staged_params_t* p, float* const d_dw[4], float* const d_db[4],
                                boat_tensor_t* gin[3]) {
     const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
-    const int64_t hs = (int64_t)a->config.head_size, B = a->B, S = a->S, T = B * S;
+    const int64_t hs = (int64_t)a->config.head_size, S = a->S, T = a->T;
+    const int64_t G = a->units / a->gran, grows = a->gran * S / nh;
     const size_t tsz = storage_size(type), act_bytes = (size_t)T * (size_t)H * tsz;
     const bool bias = a->param[BQ] != NULL;
-    const int nchunk = (int)(B < MAX_CHUNKS ? B : MAX_CHUNKS);
+    const int nchunk = (int)(G < MAX_CHUNKS ? G : MAX_CHUNKS);
     void *d_go = NULL, *raw_go = NULL, *d_dctx = NULL, *scratch = NULL;
     void *d_dproj[3] = {NULL, NULL, NULL}, *d_dx[3] = {NULL, NULL, NULL};
     int out_type[3];
@@ -377,12 +385,12 @@ static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_ou
         out_type[i] = storage_of(x->dtype);
         d_dproj[i] = dev_alloc(act_bytes);
         d_dx[i] = dev_alloc((size_t)T * (size_t)H * storage_size(out_type[i]));
-        gin[i] = boat_tensor_create_uninit(x->shape, 3, x->dtype, BOAT_DEVICE_CPU);
+        gin[i] = boat_tensor_create_uninit(x->shape, x->ndim, x->dtype, BOAT_DEVICE_CPU);
         if (!d_dproj[i] || !d_dx[i] || !gin[i]) goto done;
     }
     for (int c = 0; c < nchunk; ++c) {              /* the largest chunk decides the scratch size */
-        const int64_t nb = chunk_begin(B, nchunk, c + 1) - chunk_begin(B, nchunk, c);
-        const size_t need = boat_cuda_attn_bwd_scratch_bytes(mma, nb * nh, S, hs);
+        const int64_t nb = chunk_begin(G, nchunk, c + 1) - chunk_begin(G, nchunk, c);
+        const size_t need = boat_cuda_attn_bwd_scratch_bytes(mma, nb * a->gran, S, hs);
         if (need > scratch_bytes) scratch_bytes = need;
     }
     scratch = dev_alloc(scratch_bytes ? scratch_bytes : 256);
@@ -390,8 +398,8 @@ static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_ou
     if (boat_report("copy streams", boat_cuda_copies_after_compute()) != 0) goto done;
 
     for (int c = 0; c < nchunk; ++c) {
-        const int64_t b0 = chunk_begin(B, nchunk, c), b1 = chunk_begin(B, nchunk, c + 1);
-        const int64_t r0 = b0 * S, nr = (b1 - b0) * S;
+        const int64_t b0 = chunk_begin(G, nchunk, c), b1 = chunk_begin(G, nchunk, c + 1);
+        const int64_t r0 = b0 * grows, nr = (b1 - b0) * grows;
         const size_t off = (size_t)(r0 * H) * tsz;
         if (stage_rows(grad_output, mma, type, d_go, raw_go, r0, nr, H) != 0) goto done;
         /* d(ctx) = dOut . Wo^T */
@@ -400,9 +408,9 @@ static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_ou
             goto done;
         if (settle_tf32(mma, (char*)d_dctx + off, nr * H) != 0) goto done;
         if (boat_report("attention core backward",
-                        boat_cuda_attn_bwd(mma, (b1 - b0) * nh, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
+                        boat_cuda_attn_bwd(mma, (b1 - b0) * a->gran, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
                                            (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
-                                           (char*)a->d_ctx + off, (char*)d_dctx + off, a->d_lse + b0 * nh * S, type,
+                                           (char*)a->d_ctx + off, (char*)d_dctx + off, a->d_lse + b0 * a->gran * S, type,
                                            (char*)d_dproj[0] + off, (char*)d_dproj[1] + off, (char*)d_dproj[2] + off,
                                            scratch, scratch_bytes)) != 0)
             goto done;
@@ -496,20 +504,13 @@ void boat_attention_free(boat_attention_t* a) {
 
 /* ---- forward ------------------------------------------------------------------------------- */
 
-boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* query, const boat_tensor_t* key,
-                                      const boat_tensor_t* value, const boat_tensor_t* attention_mask) {
-    (void)attention_mask;                       /* ignored, as in the reference (attention.c:1022-1025) */
-    if (!a || !query || !key || !value) return NULL;
+/* The step itself, for T token rows holding `units` (batch, head) units of sequence length S; `gran`
+ * units form one indivisible piece when host tensors are moved in chunks.  Inputs are [.., H]
+ * tensors of T*H elements each; the result has the query's shape. */
+static boat_tensor_t* forward_rows(boat_attention_t* a, const boat_tensor_t* query, const boat_tensor_t* key,
+                                   const boat_tensor_t* value, int64_t T, int64_t S, int64_t units, int64_t gran) {
     const boat_tensor_t* in[3] = {query, key, value};
-    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
-    const int64_t hs = (int64_t)a->config.head_size;
-    if (query->ndim != 3 || nh * hs != H) return NULL;
-    const int64_t B = query->shape[0], S = query->shape[1];
-    for (int i = 0; i < 3; ++i) {
-        if (!dtype_ok(in[i]->dtype) || in[i]->ndim != 3 || in[i]->shape[0] != B || in[i]->shape[1] != S ||
-            in[i]->shape[2] != H)
-            return NULL;
-    }
+    const int64_t H = (int64_t)a->config.hidden_size, hs = (int64_t)a->config.head_size;
     if (boat_report("CUDA start-up", boat_cuda_init(-1)) != 0) return NULL;
 
     /* Take the new inputs before releasing the old ones: they may be the same tensors. */
@@ -519,18 +520,19 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
 
     const int mma = pick_mma(a, query);
     const int type = mma == BOAT_MMA_BF16 ? BOAT_CUDA_BF16 : BOAT_CUDA_F32;
-    const int64_t T = B * S;
     const size_t act_bytes = (size_t)T * (size_t)H * storage_size(type);
     a->mma = mma;
     a->type = type;
-    a->B = B;
+    a->T = T;
     a->S = S;
+    a->units = units;
+    a->gran = gran;
 
     staged_params_t p;
     void* d_out = NULL;
     boat_tensor_t* result = NULL;
     if (!stage_params(a, mma, type, &p)) goto done;
-    if (B >= 2 && pipeline_enabled() && on_host(query) && on_host(key) && on_host(value)) {
+    if (units / gran >= 2 && pipeline_enabled() && on_host(query) && on_host(key) && on_host(value)) {
         result = forward_pipelined(a, in, mma, type, &p);
         if (result) a->cached = true;
         goto done;
@@ -557,10 +559,10 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
         if (settle_tf32(mma, a->d_proj[i], T * H) != 0) goto done;
     }
     a->d_ctx = dev_alloc(act_bytes);
-    a->d_lse = (float*)dev_alloc((size_t)B * nh * S * sizeof(float));
+    a->d_lse = (float*)dev_alloc((size_t)units * S * sizeof(float));
     if (!a->d_ctx || !a->d_lse) goto done;
     /* [B,S,H] viewed as [B*nh, S, hs]: the head split is a reshape (attention.c:393-397). */
-    if (boat_report("attention core", boat_cuda_attn_fwd(mma, B * nh, S, hs, a->config.causal_mask,
+    if (boat_report("attention core", boat_cuda_attn_fwd(mma, units, S, hs, a->config.causal_mask,
                                                          1.0f / sqrtf((float)hs), a->d_proj[0], a->d_proj[1],
                                                          a->d_proj[2], type, a->d_ctx, a->d_lse)) != 0)
         goto done;
@@ -571,7 +573,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
         int out_type = storage_of(query->dtype);
         if (query->device == BOAT_DEVICE_CUDA) {
             /* a CUDA result is the GEMM's own output buffer: no copy */
-            result = boat_tensor_create_uninit(query->shape, 3, query->dtype, BOAT_DEVICE_CUDA);
+            result = boat_tensor_create_uninit(query->shape, query->ndim, query->dtype, BOAT_DEVICE_CUDA);
             if (!result) goto done;
             if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_ctx, H, p.w[WO], H, type,
                                                                 result->data, H, out_type, p.b[WO])) != 0) {
@@ -585,7 +587,7 @@ boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* 
             if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_ctx, H, p.w[WO], H, type,
                                                                 d_out, H, out_type, p.b[WO])) != 0)
                 goto done;
-            result = emit_out(query->shape, 3, query, d_out, out_type);
+            result = emit_out(query->shape, query->ndim, query, d_out, out_type);
         }
     }
     if (result) a->cached = true;
@@ -601,6 +603,48 @@ done:
         for (int i = 0; i < 3; ++i) a->cache_in[i] = keep[i];
     }
     return result;
+}
+
+boat_tensor_t* boat_attention_forward(boat_attention_t* a, const boat_tensor_t* query, const boat_tensor_t* key,
+                                      const boat_tensor_t* value, const boat_tensor_t* attention_mask) {
+    (void)attention_mask;                       /* ignored, as in the reference (attention.c:1022-1025) */
+    if (!a || !query || !key || !value) return NULL;
+    const boat_tensor_t* in[3] = {query, key, value};
+    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
+    const int64_t hs = (int64_t)a->config.head_size;
+    if (query->ndim != 3 || nh * hs != H) return NULL;
+    const int64_t B = query->shape[0], S = query->shape[1];
+    for (int i = 0; i < 3; ++i) {
+        if (!dtype_ok(in[i]->dtype) || in[i]->ndim != 3 || in[i]->shape[0] != B || in[i]->shape[1] != S ||
+            in[i]->shape[2] != H)
+            return NULL;
+    }
+    return forward_rows(a, query, key, value, B * S, S, B * nh, nh);
+}
+
+/* A contiguous range of (batch, head) units of a larger [B,S,H] problem, given only the token rows
+ * that range touches.  The head split is a reshape (reference attention.c:393-397): with nh
+ * dividing S, unit u of the flattened [B*S, H] input is exactly its token rows
+ * [u*S/nh, (u+1)*S/nh), so n consecutive units are n*S/nh consecutive rows, and the projections
+ * (row-wise maps) shard the same way. */
+boat_tensor_t* boat_attention_forward_units(boat_attention_t* a, const boat_tensor_t* query, const boat_tensor_t* key,
+                                            const boat_tensor_t* value, int64_t seq_len) {
+    if (!a || !query || !key || !value || seq_len <= 0) return NULL;
+    const boat_tensor_t* in[3] = {query, key, value};
+    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
+    const int64_t hs = (int64_t)a->config.head_size;
+    if (nh * hs != H) return NULL;
+    if (seq_len % nh != 0) {
+        fprintf(stderr, "boat_attention_forward_units: the sequence length (%lld) must be a multiple of the head "
+                        "count (%lld) for units to own whole token rows\n", (long long)seq_len, (long long)nh);
+        return NULL;
+    }
+    const int64_t unit_rows = seq_len / nh;
+    if (query->ndim != 2 || query->shape[1] != H || query->shape[0] <= 0 || query->shape[0] % unit_rows != 0) return NULL;
+    const int64_t R = query->shape[0];
+    for (int i = 0; i < 3; ++i)
+        if (!dtype_ok(in[i]->dtype) || in[i]->ndim != 2 || in[i]->shape[0] != R || in[i]->shape[1] != H) return NULL;
+    return forward_rows(a, query, key, value, R, seq_len, R / unit_rows, 1);
 }
 
 /* ---- backward ------------------------------------------------------------------------------ */
@@ -639,8 +683,8 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         printf("[ERROR] boat_attention_backward: missing cached tensors\n");
         return false;
     }
-    const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
-    const int64_t hs = (int64_t)a->config.head_size, B = a->B, S = a->S, T = B * S;
+    const int64_t H = (int64_t)a->config.hidden_size;
+    const int64_t hs = (int64_t)a->config.head_size, S = a->S, T = a->T, units = a->units;
     if (!dtype_ok(grad_output->dtype) || (int64_t)grad_output->nelements != T * H) {
         printf("[ERROR] boat_attention_backward: grad_output does not match the cached forward\n");
         return false;
@@ -657,6 +701,9 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     size_t scratch_bytes;
 
     if (!ensure_grads(a)) goto done;
+    /* gradient sums of the previous step still on the communication stream read the bucket
+     * this step is about to overwrite */
+    if (boat_cuda_allreduce_pending() && boat_report("gradient all-reduce", boat_cuda_allreduce_join()) != 0) goto done;
     if (!stage_params(a, mma, type, &p)) goto done;
     /* gradients are produced in HBM; a host layer receives them with one copy at the end */
     d_bucket = a->device == BOAT_DEVICE_CUDA ? (float*)a->grad_bucket->data
@@ -668,7 +715,7 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         d_dw[i] = d_bucket + (size_t)i * H * H;
         d_db[i] = bias ? d_bucket + (size_t)4 * H * H + (size_t)i * H : NULL;
     }
-    if (B >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) && on_host(a->cache_in[1]) &&
+    if (units / a->gran >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) && on_host(a->cache_in[1]) &&
         on_host(a->cache_in[2])) {
         ok = backward_pipelined(a, grad_output, mma, type, &p, d_dw, d_db, gin);
         goto done;
@@ -683,31 +730,49 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     if (settle_tf32(mma, d_dctx, T * H) != 0) goto done;
     if (boat_report("dWo", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_ctx, H, d_go, H, type, d_dw[WO], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
     if (bias && boat_report("dbo", boat_cuda_colsum(d_go, type, T, H, d_db[WO])) != 0) goto done;
+    /* Data parallel with overlap: dWo and dbo are final here, long before the step ends - their
+     * sum over the ranks runs under the attention-core backward. */
+    const bool overlap = a->grad_overlap && a->device == BOAT_DEVICE_CUDA && boat_cuda_comm_world() > 1;
+    if (overlap) {
+        float* piece[2] = {d_dw[WO], d_db[WO]};
+        const int64_t count[2] = {H * H, bias ? H : 0};
+        if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 2)) != 0) goto done;
+    }
 
     /* attention core */
     for (int i = 0; i < 3; ++i) {
         d_dproj[i] = dev_alloc(act_bytes);
         if (!d_dproj[i]) goto done;
     }
-    scratch_bytes = boat_cuda_attn_bwd_scratch_bytes(mma, B * nh, S, hs);
+    scratch_bytes = boat_cuda_attn_bwd_scratch_bytes(mma, units, S, hs);
     scratch = dev_alloc(scratch_bytes);
     if (!scratch) goto done;
     if (boat_report("attention core backward",
-                    boat_cuda_attn_bwd(mma, B * nh, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
+                    boat_cuda_attn_bwd(mma, units, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
                                        a->d_proj[0], a->d_proj[1], a->d_proj[2], a->d_ctx, d_dctx, a->d_lse, type,
                                        d_dproj[0], d_dproj[1], d_dproj[2], scratch, scratch_bytes)) != 0)
         goto done;
     for (int i = 0; i < 3; ++i)
         if (settle_tf32(mma, d_dproj[i], T * H) != 0) goto done;
 
-    /* input projections: dX = dP . W^T,  dW = X^T . dP,  db = colsum(dP) */
+    /* input projections: dW = X^T . dP and db = colsum(dP) first - with overlap their sum over
+     * the ranks then runs under the three dX = dP . W^T GEMMs that follow */
+    for (int i = 0; i < 3; ++i) {
+        if (boat_report("dW", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_in[i], H, d_dproj[i], H, type, d_dw[i], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
+        if (bias && boat_report("db", boat_cuda_colsum(d_dproj[i], type, T, H, d_db[i])) != 0) goto done;
+    }
+    if (overlap) {
+        float* piece[2] = {d_dw[WQ], d_db[WQ]};            /* dWq|dWk|dWv and dbq|dbk|dbv are contiguous */
+        const int64_t count[2] = {3 * H * H, bias ? 3 * H : 0};
+        if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 2)) != 0) goto done;
+    }
     for (int i = 0; i < 3; ++i) {
         const boat_tensor_t* x = a->cache_in[i];
         int out_type = storage_of(x->dtype);
         void* dx_target;
         if (x->device == BOAT_DEVICE_CUDA) {
             /* a CUDA gradient is the GEMM's own output buffer: no copy */
-            gin[i] = boat_tensor_create_uninit(x->shape, 3, x->dtype, BOAT_DEVICE_CUDA);
+            gin[i] = boat_tensor_create_uninit(x->shape, x->ndim, x->dtype, BOAT_DEVICE_CUDA);
             if (!gin[i]) goto done;
             dx_target = gin[i]->data;
         } else {
@@ -716,10 +781,8 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
             dx_target = d_dx;
         }
         if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, T, H, H, d_dproj[i], H, p.w[i], H, type, dx_target, H, out_type, NULL)) != 0) goto done;
-        if (boat_report("dW", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_in[i], H, d_dproj[i], H, type, d_dw[i], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
-        if (bias && boat_report("db", boat_cuda_colsum(d_dproj[i], type, T, H, d_db[i])) != 0) goto done;
         if (x->device != BOAT_DEVICE_CUDA) {
-            gin[i] = emit_out(x->shape, 3, x, d_dx, out_type);
+            gin[i] = emit_out(x->shape, x->ndim, x, d_dx, out_type);
             dev_free(d_dx);
             d_dx = NULL;
             if (!gin[i]) goto done;
@@ -944,8 +1007,16 @@ int boat_attention_grad_bucket(const boat_attention_t* a, float** data, size_t* 
     return 0;
 }
 
+int boat_attention_set_grad_overlap(boat_attention_t* a, int on) {
+    if (!a) return 1;
+    a->grad_overlap = on != 0;
+    return 0;
+}
+
 int boat_attention_allreduce_grads(boat_attention_t* a) {
     if (!a || !a->grad_bucket) return 1;
+    /* sums started by the backward itself: the library stream only has to wait for them */
+    if (boat_cuda_allreduce_pending()) return boat_report("gradient all-reduce", boat_cuda_allreduce_join());
     if (boat_cuda_comm_world() <= 1) return 0;
     if (a->device != BOAT_DEVICE_CUDA) {
         fprintf(stderr, "boat: gradient all-reduce needs the layer on BOAT_DEVICE_CUDA\n");

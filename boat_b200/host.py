@@ -155,6 +155,13 @@ class Attention:
                             (capi.load().boat_cuda_last_error() or b"").decode())
         return Tensor(out)
 
+    def forward_units(self, q, seq_len, k=None, v=None):
+        """boat_attention_forward_units: q (k, v) are [R, H] tensors holding the token rows of a
+        contiguous range of (batch, head) units of a problem with sequence length seq_len."""
+        k = k if k is not None else q
+        v = v if v is not None else q
+        return Tensor(capi.load().boat_attention_forward_units(self.h, q.h, k.h, v.h, seq_len))
+
     def backward(self, grad_output):
         gq, gk, gv = C.c_void_p(), C.c_void_p(), C.c_void_p()
         ok = capi.load().boat_attention_backward(self.h, grad_output.h, C.byref(gq), C.byref(gk), C.byref(gv))
@@ -174,6 +181,10 @@ class Attention:
             buf = (C.c_char * len(image)).from_buffer_copy(image)
             return lib.boat_attention_load_safetensors(self.h, C.cast(buf, C.c_void_p), len(image), pre)
         return lib.boat_attention_load_safetensors_file(self.h, str(image).encode(), pre)
+
+    def set_grad_overlap(self, on=True):
+        if capi.load().boat_attention_set_grad_overlap(self.h, int(bool(on))):
+            raise BoatError("boat_attention_set_grad_overlap failed")
 
     def allreduce_grads(self):
         rc = capi.load().boat_attention_allreduce_grads(self.h)

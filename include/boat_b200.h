@@ -25,11 +25,28 @@ BOAT_API int boat_attention_to_device(boat_attention_t* attention, boat_device_t
 
 /* Choose the arithmetic: BOAT_MMA_FP32 (exact CUDA-core path, any shape), BOAT_MMA_TF32
  * or BOAT_MMA_BF16 (tcgen05 tensor-core paths; need seq_len % 128 == 0 and head size 64 or
- * 128), or -1 for automatic: BF16 inputs -> BF16, FP32 inputs -> TF32 when the shape
- * allows it and FP32 otherwise.  The default is taken from the environment variable
- * BOAT_MMA (fp32 | tf32 | bf16 | auto), else automatic.  Returns 0 on success. */
+ * 128, other shapes run on the CUDA cores with the same storage), or -1 for automatic:
+ * BF16 tensors -> BF16, FP32 tensors -> exact FP32 whatever the shape, so that a reference
+ * program's numbers never depend on the sequence length; TF32 is always an explicit choice.
+ * The default is taken from the environment variable BOAT_MMA (fp32 | tf32 | bf16 | auto),
+ * else automatic.  Returns 0 on success. */
 BOAT_API int boat_attention_set_precision(boat_attention_t* attention, int mma);
 BOAT_API int boat_attention_get_precision(const boat_attention_t* attention);
+
+/* Forward for a contiguous range of (batch, head) units of a larger [B, seq_len, H] problem,
+ * given only the token rows that range owns - the entry that lets one problem be split over
+ * GPUs by batch x heads.  Boat's head split is a reshape (src/layers/attention.c:393-397), so
+ * with the head count dividing seq_len, unit u = b*heads + h of the flattened [B*seq_len, H]
+ * input is exactly its rows [u*seq_len/heads, (u+1)*seq_len/heads): n consecutive units are
+ * n*seq_len/heads consecutive rows and need nothing else.  query, key, value: [R, H] with R a
+ * multiple of seq_len/heads; returns [R, H] - the same rows of the full problem's output.
+ * boat_attention_backward then takes the [R, H] upstream gradient of those rows and returns
+ * their [R, H] input gradients; the parameter gradients it leaves are this range's share, and
+ * their sum over all ranges (boat_attention_allreduce_grads) is the full problem's gradient.
+ * NULL when seq_len is not a multiple of the head count or the shapes do not fit. */
+BOAT_API boat_tensor_t* boat_attention_forward_units(boat_attention_t* attention, const boat_tensor_t* query,
+                                                     const boat_tensor_t* key, const boat_tensor_t* value,
+                                                     int64_t seq_len);
 
 /* The layer keeps its eight gradients back to back in one FP32 buffer, in the order
  * dWq dWk dWv dWo dbq dbk dbv dbo; the accessor tensors are windows into it.  Gives its
@@ -41,6 +58,14 @@ BOAT_API int boat_attention_grad_bucket(const boat_attention_t* attention, float
  * boat_cuda_comm_init (data-parallel training: every rank holds the same weights and a
  * different slice of the batch).  No-op with a single rank.  Returns 0 on success. */
 BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
+
+/* Overlap that sum with the backward: with on != 0 (and a CUDA layer, more than one rank),
+ * boat_attention_backward itself starts the sum of dWo | dbo as soon as the output projection's
+ * gradients are final - it then runs under the attention-core backward - and the sum of
+ * dWq dWk dWv | dbq dbk dbv before the three input-gradient GEMMs, on a communication stream.
+ * boat_attention_allreduce_grads then only joins: call it, as before, after the backward and
+ * before anything reads or updates the gradients.  Off by default. */
+BOAT_API int boat_attention_set_grad_overlap(boat_attention_t* attention, int on);
 
 /* Register the layer's parameters with an optimizer (boat/optimizers.h), each with its
  * gradient tensor.  The reference's layer makes new gradient tensors on every backward

@@ -188,11 +188,27 @@ int boat_cuda_adam_step(int count, float* const* params, const float* const* gra
 /* ---- gradient exchange between GPUs (nothing in the reference: it is single-process) ---
  * One process per GPU.  Rank 0 makes an id (128 bytes) and hands it to the others by any
  * host channel; every rank then calls comm_init.  allreduce sums an FP32 buffer in place
- * across ranks on the library stream. */
+ * across ranks on the library stream.
+ *
+ * allreduce_begin / _join overlap the sums with later kernels: begin starts the in-place sums of
+ * `pieces` buffers (bufs[i], counts[i] floats) on a communication stream of the library, ordered
+ * after everything launched on the library stream so far; join makes the library stream wait
+ * for all sums begun since the last join.  Nothing may write the pieces in between.
+ *
+ * Failures end in an error status, not in a stuck host thread: the communicator is
+ * non-blocking, every NCCL call is polled under a deadline (BOAT_COMM_INIT_TIMEOUT_S, default
+ * 120 s, for joining; BOAT_COMM_TIMEOUT_S, default 30 s, for a collective to be accepted), and
+ * on a deadline or an NCCL error the communicator is aborted (status 23 / 2000+ncclResult) and
+ * comm_world() is 1 again.  Before the first sum of a given length the ranks agree on that
+ * length through the communicator; a rank with another bucket size gets status 25.
+ * BOAT_NCCL_LIB names the NCCL library to load (default libnccl.so.2). */
 int boat_cuda_comm_unique_id(void* id_out_host_128B);
 int boat_cuda_comm_init(int rank, int world, const void* id_host_128B);
 int boat_cuda_comm_world(void);                 /* 1 when no communicator exists */
 int boat_cuda_allreduce_sum_f32(float* buf, int64_t n);
+int boat_cuda_allreduce_begin(float* const* bufs, const int64_t* counts, int pieces);
+int boat_cuda_allreduce_join(void);
+int boat_cuda_allreduce_pending(void);          /* 1 between a begin and its join */
 int boat_cuda_comm_destroy(void);
 
 #pragma GCC visibility pop

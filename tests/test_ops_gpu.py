@@ -84,9 +84,11 @@ def test_elementwise_ops_mix_host_and_cuda_operands(gpu_lib, ops_golden):
 def test_batched_matmul_matches_reference(gpu_lib, ops_golden, device):
     lib, inp = gpu_lib, cases.ops_inputs()
     for ka, kb, key in (("m3a", "m3b", "matmul3"), ("m4a", "m4b", "matmul4")):
-        out = call(lib, "boat_matmul", Tensor.from_numpy(inp[ka], device).h, Tensor.from_numpy(inp[kb], device).h)
+        a, b = Tensor.from_numpy(inp[ka], device), Tensor.from_numpy(inp[kb], device)
+        out = call(lib, "boat_matmul", a.h, b.h)
         want = ops_golden[key]
         assert out.shape == want.shape and out.device == device
         assert cases.rel_err(out.numpy(), want) <= 1e-5, key
     # batch dimensions must match exactly (src/ops/linear.c:32-36)
-    assert not lib.boat_matmul(Tensor.from_numpy(inp["m3a"], device).h, Tensor.from_numpy(inp["m4b"], device).h)
+    a, b = Tensor.from_numpy(inp["m3a"], device), Tensor.from_numpy(inp["m4b"], device)
+    assert not lib.boat_matmul(a.h, b.h)
