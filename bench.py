@@ -360,6 +360,10 @@ def main():
             layer.param("weight_" + p).set(w_host[i])
         layer.to_device(capi.DEVICE_CUDA)
         layer.set_precision(mma)
+    if world > 1:
+        # the backward itself starts the gradient sums (dWo | dbo under the attention-core backward,
+        # the rest under the input-gradient GEMMs); allreduce_grads() then only joins them
+        layer.set_grad_overlap(True)
     adam = None
     if args.optimizer == "adam":
         from boat_b200.host import Adam
@@ -374,7 +378,7 @@ def main():
     def block_step():
         out, dx = block.step(x, g)
         if world > 1:
-            layer.allreduce_grads()      # attention bucket; the MLP and LayerNorm gradients are not reduced yet
+            block.allreduce_grads()      # attention bucket, both LayerNorms, both dense layers
         block.zero_dense_grads()
         out.free()
         dx.free()
@@ -439,6 +443,53 @@ def main():
     tokens_per_s = world * T / (ms_per_step * 1e-3)
     flops = block_flops(B, S, d, causal) if is_block else algorithmic_flops(B, S, d, causal)
     tflops_per_gpu = flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- strong scaling: the SAME problem (global batch = the per-GPU batch of the weak run) split over the
+    # ranks by (batch, head) units, each rank holding only the token rows of its units ----
+    strong = None
+    if world > 1 and not is_block and (B * nh) % world == 0 and S % nh == 0:
+        u = shard.head_unit_range(B, nh, world, rank)
+        r0, r1 = shard.unit_rows(u, S, nh)
+        xr = Tensor.from_numpy(rnd(rng.normal(SEED, rng.X, (r1 - r0, d), offset=r0 * d)), capi.DEVICE_CUDA, bf16=bf16)
+        gr = Tensor.from_numpy(rnd(rng.normal(SEED, rng.DOUT, (r1 - r0, d), offset=r0 * d)), capi.DEVICE_CUDA, bf16=bf16)
+
+        def strong_step():
+            out = layer.forward_units(xr, S)
+            gq, gk, gv = layer.backward(gr)
+            layer.allreduce_grads()
+            for tt in (out, gq, gk, gv):
+                tt.free()
+
+        def timed(fn, n):
+            for _ in range(3):
+                fn()
+            sync_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            sync_all()
+            tt = torch.tensor([e0.elapsed_time(e1) / n], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item())
+
+        strong_ms = timed(strong_step, args.steps)
+
+        def single_gpu_step():          # the whole problem on one GPU, no exchange: what N=1 does
+            out = layer.forward(x, x, x)
+            gq, gk, gv = layer.backward(g)
+            for tt in (out, gq, gk, gv):
+                tt.free()
+
+        layer.set_grad_overlap(False)
+        n1_ms = timed(single_gpu_step, max(3, min(args.steps, 10)))
+        layer.set_grad_overlap(True)
+        strong = dict(workload="the %s problem at GLOBAL batch %d split by (batch, head) units: %d units = %d token rows per GPU" %
+                      (args.workload, B, u[1] - u[0], r1 - r0), global_batch=B, units_per_gpu=u[1] - u[0],
+                      rows_per_gpu=r1 - r0, ms_per_step=strong_ms, tokens_per_s=T / (strong_ms * 1e-3),
+                      n1_ms_per_step=n1_ms, speedup_vs_n1=n1_ms / strong_ms,
+                      note="n1_ms_per_step: the whole problem on one GPU without exchange, timed in this run on every rank (max)")
 
     # ---- roofline of the dominant kernel family ----
     peaks = load_peaks()
@@ -546,6 +597,8 @@ def main():
                     tflops_per_gpu=tflops_per_gpu,
                     frac_of_bf16_peak=(tflops_per_gpu / (peaks["bf16"] if ms_per_step * args.steps < 1e3 else peaks["bf16_sustained"])) if bf16 else None,
                     roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches), clocks=clocks)
+        if strong:
+            line["strong"] = strong
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:

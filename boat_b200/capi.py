@@ -14,7 +14,7 @@ _LIB = None
 DTYPE_FLOAT64, DTYPE_FLOAT32, DTYPE_FLOAT16 = 0, 1, 2
 DTYPE_BFLOAT16 = 11
 DEVICE_CPU, DEVICE_CUDA = 0, 1
-CUDA_F32, CUDA_BF16 = 0, 1
+CUDA_F32, CUDA_BF16, CUDA_F32_TF32 = 0, 1, 2
 MMA_FP32, MMA_TF32, MMA_BF16 = 0, 1, 2
 
 
@@ -178,6 +178,7 @@ PROTOTYPES = {
     "boat_encoder_block_forward": (_P, [_P, _P]),
     "boat_encoder_block_backward": (_P, [_P, _P]),
     "boat_encoder_block_free": (None, [_P]),
+    "boat_encoder_block_allreduce_grads": (_I, [_P]),
     "boat_attention_load_safetensors": (_I, [_P, _P, _SZ, C.c_char_p]),
     "boat_attention_load_safetensors_file": (_I, [_P, C.c_char_p, C.c_char_p]),
     # include/boat/optimizers.h

@@ -53,6 +53,16 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 
 inline size_t type_size(int t) { return t == BOAT_CUDA_BF16 ? 2 : 4; }
 
+// FP32 value rounded to the nearest TF32 number (ties away from zero), still an FP32 bit pattern.
+__device__ __forceinline__ float round_to_tf32(float v) {
+    uint32_t t;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t) : "f"(v));
+    return __uint_as_float(t);
+}
+// Output element of BOAT_CUDA_F32_TF32: stored as float, rounded on conversion.
+struct f32_tf32 { float v; };
+template <> __device__ __forceinline__ f32_tf32 from_f32<f32_tf32>(float v) { return f32_tf32{round_to_tf32(v)}; }
+
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // out[r] = sum_d A[r,d]*B[r,d] over [rows, cols] row-major buffers of storage type `type`.

@@ -20,9 +20,10 @@ int attn_bwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float
 
 static int check_types(const char* who, int mma, int in_type) {
     if (mma < BOAT_MMA_FP32 || mma > BOAT_MMA_BF16) return set_error(10, "%s: unknown arithmetic %d", who, mma);
-    if (in_type != BOAT_CUDA_F32 && in_type != BOAT_CUDA_BF16) return set_error(10, "%s: unknown storage type %d", who, in_type);
+    if (in_type != BOAT_CUDA_F32 && in_type != BOAT_CUDA_BF16 && in_type != BOAT_CUDA_F32_TF32)
+        return set_error(10, "%s: unknown storage type %d", who, in_type);
     if (mma == BOAT_MMA_BF16 && in_type != BOAT_CUDA_BF16) return set_error(10, "%s: BF16 arithmetic needs BF16 storage", who);
-    if (mma == BOAT_MMA_TF32 && in_type != BOAT_CUDA_F32) return set_error(10, "%s: TF32 arithmetic needs FP32 storage", who);
+    if (mma == BOAT_MMA_TF32 && in_type == BOAT_CUDA_BF16) return set_error(10, "%s: TF32 arithmetic needs FP32 storage", who);
     return 0;
 }
 
@@ -31,6 +32,8 @@ extern "C" {
 int boat_cuda_gemm(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                    const void* B, int64_t ldb, int in_type, void* C, int64_t ldc, int out_type, const float* bias) {
     if (int rc = check_types("boat_cuda_gemm", mma, in_type)) return rc;
+    if (in_type == BOAT_CUDA_F32_TF32) in_type = BOAT_CUDA_F32;          // rounded or not, the storage is FP32
+    if (out_type < BOAT_CUDA_F32 || out_type > BOAT_CUDA_F32_TF32) return set_error(10, "boat_cuda_gemm: unknown output type %d", out_type);
     if (M < 0 || N < 0 || K < 0) return set_error(11, "boat_cuda_gemm: negative size");
     if (M == 0 || N == 0) return 0;
     if (!A || !B || !C) return set_error(11, "boat_cuda_gemm: NULL operand");
@@ -47,13 +50,19 @@ int boat_cuda_gemm(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, con
 int boat_cuda_attn_fwd(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q,
                        const void* K, const void* V, int io_type, void* O, float* lse) {
     if (int rc = check_types("boat_cuda_attn_fwd", mma, io_type)) return rc;
+    if (io_type == BOAT_CUDA_F32_TF32) io_type = BOAT_CUDA_F32;
     if (units < 0 || S < 0 || hs < 0) return set_error(11, "boat_cuda_attn_fwd: negative size");
     if (units == 0 || S == 0 || hs == 0) return 0;
     if (!Q || !K || !V || !O || !lse) return set_error(11, "boat_cuda_attn_fwd: NULL operand");
     if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type))
         return attn_fwd_tc(mma, units, S, hs, causal, scale, Q, K, V, io_type, O, lse);
-    ProfileScope prof("attn_fwd_simt");
-    return attn_fwd_simt(units, S, hs, causal, scale, Q, K, V, io_type, O, lse);
+    {
+        ProfileScope prof("attn_fwd_simt");
+        if (int rc = attn_fwd_simt(units, S, hs, causal, scale, Q, K, V, io_type, O, lse)) return rc;
+    }
+    // TF32 contract: O is TF32-valued whichever kernel produced it
+    if (mma == BOAT_MMA_TF32) return boat_cuda_round_tf32((float*)O, (const float*)O, units * S * hs);
+    return 0;
 }
 
 size_t boat_cuda_attn_bwd_scratch_bytes(int mma, int64_t units, int64_t S, int64_t hs) {
@@ -69,6 +78,7 @@ int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal
                        const void* K, const void* V, const void* O, const void* dO, const float* lse,
                        int io_type, void* dQ, void* dK, void* dV, void* scratch, size_t scratch_bytes) {
     if (int rc = check_types("boat_cuda_attn_bwd", mma, io_type)) return rc;
+    if (io_type == BOAT_CUDA_F32_TF32) io_type = BOAT_CUDA_F32;
     if (units < 0 || S < 0 || hs < 0) return set_error(11, "boat_cuda_attn_bwd: negative size");
     if (units == 0 || S == 0 || hs == 0) return 0;
     if (!Q || !K || !V || !O || !dO || !lse || !dQ || !dK || !dV) return set_error(11, "boat_cuda_attn_bwd: NULL operand");
@@ -85,8 +95,17 @@ int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal
     if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type))
         return attn_bwd_tc(mma, units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV,
                            (char*)scratch + delta_bytes, scratch_bytes - delta_bytes);
-    ProfileScope prof("attn_bwd_simt");
-    return attn_bwd_simt(units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV);
+    {
+        ProfileScope prof("attn_bwd_simt");
+        if (int rc = attn_bwd_simt(units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV)) return rc;
+    }
+    if (mma == BOAT_MMA_TF32) {
+        const int64_t n = units * S * hs;
+        if (int rc = boat_cuda_round_tf32((float*)dQ, (const float*)dQ, n)) return rc;
+        if (int rc = boat_cuda_round_tf32((float*)dK, (const float*)dK, n)) return rc;
+        return boat_cuda_round_tf32((float*)dV, (const float*)dV, n);
+    }
+    return 0;
 }
 
 }  // extern "C"

@@ -304,10 +304,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_wait_ld();
                 if (TF32) {
 #pragma unroll
+                    // TF32-valued output: it feeds the TF32 output projection
                     for (int i = 0; i < 32; i += 4)
                         *reinterpret_cast<float4*>((float*)out + c * 32 + i) =
-                            make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
-                                        __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                            make_float4(round_to_tf32(__uint_as_float(r[i]) * inv), round_to_tf32(__uint_as_float(r[i + 1]) * inv),
+                                        round_to_tf32(__uint_as_float(r[i + 2]) * inv), round_to_tf32(__uint_as_float(r[i + 3]) * inv));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {

@@ -1,6 +1,8 @@
 // flash_tc.cu - host side of the tcgen05 attention-core kernels: shape support, tensor maps,
-// launches.  The kernels themselves are in flash_fwd_tc.cuh and flash_bwd_tc.cuh.
+// launches.  The kernels themselves are in flash_fwd_tc.cuh, flash_bwd_tc.cuh (BF16 storage) and
+// attn_bwd_tf32_tc.cuh (FP32 storage).
 #include "flash_bwd_tc.cuh"
+#include "attn_bwd_tf32_tc.cuh"
 #include <stdlib.h>
 
 namespace boatcu {
@@ -121,6 +123,49 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     return 0;
 }
 
+// FP32 storage, TF32 arithmetic, head size 64: a dQ kernel over query tiles and a dK/dV kernel over
+// key tiles; no scratch beyond delta.
+int launch_bwd_tf32(int64_t units, int64_t S, int causal, float scale, const void* Q, const void* K, const void* V,
+                    const void* dO, const float* lse, const float* delta, void* dQ, void* dK, void* dV) {
+    using C = Bwd32Cfg;
+    constexpr int HS = kBwd32HS;
+    CUtensorMap mq, mq_mn, mk, mk_mn, mv, mdo, mdo_mn;
+    const uint64_t rows = (uint64_t)units * (uint64_t)S;
+    // the same matrices with both shared-memory layouts: 16-byte swizzle units for operands read
+    // along hs, 32-byte units for operands read along their rows
+    if (int rc = make_tensor_map_2d(&mq, Q, 4, rows, HS, HS, kTile, 32)) return rc;
+    if (int rc = make_tensor_map_2d(&mq_mn, Q, 4, rows, HS, HS, kTile, 32, true)) return rc;
+    if (int rc = make_tensor_map_2d(&mk, K, 4, rows, HS, HS, kTile, 32)) return rc;
+    if (int rc = make_tensor_map_2d(&mk_mn, K, 4, rows, HS, HS, kTile, 32, true)) return rc;
+    if (int rc = make_tensor_map_2d(&mv, V, 4, rows, HS, HS, kTile, 32)) return rc;
+    if (int rc = make_tensor_map_2d(&mdo, dO, 4, rows, HS, HS, kTile, 32)) return rc;
+    if (int rc = make_tensor_map_2d(&mdo_mn, dO, 4, rows, HS, HS, kTile, 32, true)) return rc;
+    Bwd32Params p;
+    p.lse = lse;
+    p.delta = delta;
+    p.dQ = (float*)dQ;
+    p.dK = (float*)dK;
+    p.dV = (float*)dV;
+    p.S = (int)S;
+    p.units = (int)units;
+    p.causal = causal;
+    p.scale = scale;
+    p.status = kernel_status_ptr();
+    static bool configured = false;     // per process = per device: the library binds to one device
+    if (!configured) {
+        BOATCU_CHECK(cudaFuncSetAttribute(attn_bwd_dq_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_DQ));
+        BOATCU_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_DKV));
+        configured = true;
+    }
+    const unsigned grid = (unsigned)(units * (S / kTile));
+    ProfileScope prof("flash_bwd");
+    attn_bwd_dkv_tf32_kernel<<<grid, kBwd32Threads, C::SMEM_DKV, stream()>>>(mq, mq_mn, mk, mv, mdo, mdo_mn, p);
+    BOATCU_LAUNCH_OK("attn_bwd_dkv_tf32");
+    attn_bwd_dq_tf32_kernel<<<grid, kBwd32Threads, C::SMEM_DQ, stream()>>>(mq, mk, mk_mn, mv, mdo, p);
+    BOATCU_LAUNCH_OK("attn_bwd_dq_tf32");
+    return 0;
+}
+
 }  // namespace
 
 // Scratch of the tensor-core backward: the FP32 accumulation buffer of dQ.
@@ -140,9 +185,8 @@ int attn_bwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float
             return launch_bwd<64>(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV, (float*)scratch);
         return launch_bwd<128>(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV, (float*)scratch);
     }
-    // FP32 storage: the backward of the TF32 path still runs on the CUDA cores
-    ProfileScope prof("attn_bwd_simt");
-    return attn_bwd_simt(units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV);
+    (void)io_type;
+    return launch_bwd_tf32(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV);
 }
 
 }  // namespace boatcu

@@ -77,9 +77,13 @@ int gemm_simt(int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, in
     if (grid.y > 65535) return set_error(7, "gemm_simt: M=%lld too large for this kernel", (long long)M);
     cudaStream_t s = stream();
     typedef __nv_bfloat16 bf;
-    if (in_type == BOAT_CUDA_F32 && out_type == BOAT_CUDA_F32)
+    if (in_type != BOAT_CUDA_BF16 && out_type == BOAT_CUDA_F32_TF32)
+        gemm_simt_kernel<float, f32_tf32><<<grid, 256, 0, s>>>(ta, tb, M, N, K, (const float*)A, lda, (const float*)B, ldb, (f32_tf32*)C, ldc, bias);
+    else if (out_type == BOAT_CUDA_F32_TF32)
+        gemm_simt_kernel<bf, f32_tf32><<<grid, 256, 0, s>>>(ta, tb, M, N, K, (const bf*)A, lda, (const bf*)B, ldb, (f32_tf32*)C, ldc, bias);
+    else if (in_type != BOAT_CUDA_BF16 && out_type == BOAT_CUDA_F32)
         gemm_simt_kernel<float, float><<<grid, 256, 0, s>>>(ta, tb, M, N, K, (const float*)A, lda, (const float*)B, ldb, (float*)C, ldc, bias);
-    else if (in_type == BOAT_CUDA_F32)
+    else if (in_type != BOAT_CUDA_BF16)
         gemm_simt_kernel<float, bf><<<grid, 256, 0, s>>>(ta, tb, M, N, K, (const float*)A, lda, (const float*)B, ldb, (bf*)C, ldc, bias);
     else if (out_type == BOAT_CUDA_F32)
         gemm_simt_kernel<bf, float><<<grid, 256, 0, s>>>(ta, tb, M, N, K, (const bf*)A, lda, (const bf*)B, ldb, (float*)C, ldc, bias);

@@ -197,7 +197,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (col0 + j < p.N) atomicAdd(dst + j, v[j]);
-                    } else if (p.out_type == BOAT_CUDA_F32) {
+                    } else if (p.out_type != BOAT_CUDA_BF16) {
+                        if (p.out_type == BOAT_CUDA_F32_TF32) {        // feeds another TF32 contraction
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
+                        }
                         float* dst = (float*)p.C + (int64_t)row * p.ldc + col0;
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)

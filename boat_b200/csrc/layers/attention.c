@@ -118,11 +118,10 @@ static void* stage_operand(const boat_tensor_t* t, int mma, int type, bool* owne
     return dst;
 }
 
-/* Values a kernel produced that feed another TF32 contraction: round in place. */
-static int settle_tf32(int mma, void* buf, int64_t n) {
-    if (mma != BOAT_MMA_TF32) return 0;
-    return boat_report("TF32 rounding", boat_cuda_round_tf32((float*)buf, (const float*)buf, n));
-}
+/* Output type for a GEMM whose result feeds another contraction of arithmetic `mma`: in TF32 mode
+ * the epilogue rounds to TF32 (the attention kernels do the same for their outputs), so no
+ * separate rounding pass runs between kernels. */
+static int feed_type(int mma, int type) { return mma == BOAT_MMA_TF32 ? BOAT_CUDA_F32_TF32 : type; }
 
 /* New tensor with the dtype/device of `like`, filled from device buffer `src` (storage
  * `type`): a cast on the device for a CUDA result, a download (after a cast when the types
@@ -325,16 +324,14 @@ static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t
             if (a->d_in_owned[i] && stage_rows(in[i], mma, type, a->d_in[i], raw[i], r0, nr, H) != 0) goto done;
         for (int i = 0; i < 3; ++i) {
             if (boat_report("projection", boat_cuda_gemm(mma, 0, 0, nr, H, H, (char*)a->d_in[i] + off, H, p->w[i], H, type,
-                                                         (char*)a->d_proj[i] + off, H, type, p->b[i])) != 0)
+                                                         (char*)a->d_proj[i] + off, H, feed_type(mma, type), p->b[i])) != 0)
                 goto done;
-            if (settle_tf32(mma, (char*)a->d_proj[i] + off, nr * H) != 0) goto done;
         }
         if (boat_report("attention core",
                         boat_cuda_attn_fwd(mma, (b1 - b0) * a->gran, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
                                            (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
                                            type, (char*)a->d_ctx + off, a->d_lse + b0 * a->gran * S)) != 0)
             goto done;
-        if (settle_tf32(mma, (char*)a->d_ctx + off, nr * H) != 0) goto done;
         if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, nr, H, H, (char*)a->d_ctx + off, H, p->w[WO], H, type,
                                                             (char*)d_out + ooff, H, out_type, p->b[WO])) != 0)
             goto done;
@@ -404,9 +401,8 @@ static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_ou
         if (stage_rows(grad_output, mma, type, d_go, raw_go, r0, nr, H) != 0) goto done;
         /* d(ctx) = dOut . Wo^T */
         if (boat_report("dOut.Wo^T", boat_cuda_gemm(mma, 0, 1, nr, H, H, (char*)d_go + off, H, p->w[WO], H, type,
-                                                    (char*)d_dctx + off, H, type, NULL)) != 0)
+                                                    (char*)d_dctx + off, H, feed_type(mma, type), NULL)) != 0)
             goto done;
-        if (settle_tf32(mma, (char*)d_dctx + off, nr * H) != 0) goto done;
         if (boat_report("attention core backward",
                         boat_cuda_attn_bwd(mma, (b1 - b0) * a->gran, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
                                            (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
@@ -416,7 +412,6 @@ static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_ou
             goto done;
         for (int i = 0; i < 3; ++i) {
             const size_t osz = storage_size(out_type[i]), ooff = (size_t)(r0 * H) * osz;
-            if (settle_tf32(mma, (char*)d_dproj[i] + off, nr * H) != 0) goto done;
             /* dX = dP . W^T */
             if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, nr, H, H, (char*)d_dproj[i] + off, H, p->w[i], H, type,
                                                  (char*)d_dx[i] + ooff, H, out_type[i], NULL)) != 0)
@@ -554,9 +549,8 @@ static boat_tensor_t* forward_rows(boat_attention_t* a, const boat_tensor_t* que
         a->d_proj[i] = dev_alloc(act_bytes);
         if (!a->d_proj[i]) goto done;
         if (boat_report("projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_in[i], H, p.w[i], H, type,
-                                                     a->d_proj[i], H, type, p.b[i])) != 0)
+                                                     a->d_proj[i], H, feed_type(mma, type), p.b[i])) != 0)
             goto done;
-        if (settle_tf32(mma, a->d_proj[i], T * H) != 0) goto done;
     }
     a->d_ctx = dev_alloc(act_bytes);
     a->d_lse = (float*)dev_alloc((size_t)units * S * sizeof(float));
@@ -566,7 +560,6 @@ static boat_tensor_t* forward_rows(boat_attention_t* a, const boat_tensor_t* que
                                                          1.0f / sqrtf((float)hs), a->d_proj[0], a->d_proj[1],
                                                          a->d_proj[2], type, a->d_ctx, a->d_lse)) != 0)
         goto done;
-    if (settle_tf32(mma, a->d_ctx, T * H) != 0) goto done;
     /* The output projection writes the caller's dtype directly when that is a device
      * storage type the GEMM can emit. */
     {
@@ -726,8 +719,7 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     /* output projection: d(ctx) = dOut . Wo^T,  dWo = ctx^T . dOut,  dbo = colsum(dOut) */
     d_dctx = dev_alloc(act_bytes);
     if (!d_dctx) goto done;
-    if (boat_report("dOut.Wo^T", boat_cuda_gemm(mma, 0, 1, T, H, H, d_go, H, p.w[WO], H, type, d_dctx, H, type, NULL)) != 0) goto done;
-    if (settle_tf32(mma, d_dctx, T * H) != 0) goto done;
+    if (boat_report("dOut.Wo^T", boat_cuda_gemm(mma, 0, 1, T, H, H, d_go, H, p.w[WO], H, type, d_dctx, H, feed_type(mma, type), NULL)) != 0) goto done;
     if (boat_report("dWo", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_ctx, H, d_go, H, type, d_dw[WO], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
     if (bias && boat_report("dbo", boat_cuda_colsum(d_go, type, T, H, d_db[WO])) != 0) goto done;
     /* Data parallel with overlap: dWo and dbo are final here, long before the step ends - their
@@ -752,8 +744,6 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
                                        a->d_proj[0], a->d_proj[1], a->d_proj[2], a->d_ctx, d_dctx, a->d_lse, type,
                                        d_dproj[0], d_dproj[1], d_dproj[2], scratch, scratch_bytes)) != 0)
         goto done;
-    for (int i = 0; i < 3; ++i)
-        if (settle_tf32(mma, d_dproj[i], T * H) != 0) goto done;
 
     /* input projections: dW = X^T . dP and db = colsum(dP) first - with overlap their sum over
      * the ranks then runs under the three dX = dP . W^T GEMMs that follow */

@@ -102,3 +102,37 @@ boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* b, const boat_t
     drop(dr1, NULL); drop(gq, NULL); drop(gk, NULL); drop(gv, NULL); drop(s1, NULL); drop(dh1, NULL); drop(dln1, NULL);
     return dx;
 }
+
+/* Data-parallel step: every rank holds the same parameters and its own rows.  Sums all parameter
+ * gradients of the block over the ranks - the attention layer's bucket, both LayerNorms' and both
+ * dense layers' weight and bias gradients - as one group of in-place sums, and makes the library
+ * stream wait for them. */
+int boat_encoder_block_allreduce_grads(boat_encoder_block_t* b) {
+    if (!b) return 1;
+    if (boat_cuda_comm_world() <= 1) return 0;
+    /* sums the attention backward started itself are joined with the rest below */
+    boat_tensor_t* t[8] = {boat_layernorm_get_grad_weight(b->ln1), boat_layernorm_get_grad_bias(b->ln1),
+                           boat_layernorm_get_grad_weight(b->ln2), boat_layernorm_get_grad_bias(b->ln2),
+                           boat_dense_layer_get_grad_weight(b->fc1), boat_dense_layer_get_grad_bias(b->fc1),
+                           boat_dense_layer_get_grad_weight(b->fc2), boat_dense_layer_get_grad_bias(b->fc2)};
+    float* piece[8];
+    int64_t count[8];
+    int n = 0;
+    for (int i = 0; i < 8; ++i) {
+        if (!t[i]) continue;
+        if (t[i]->device != BOAT_DEVICE_CUDA || t[i]->dtype != BOAT_DTYPE_FLOAT32) {
+            fprintf(stderr, "boat: gradient all-reduce needs the block's layers on BOAT_DEVICE_CUDA\n");
+            return 2;
+        }
+        piece[n] = (float*)t[i]->data;
+        count[n++] = (int64_t)t[i]->nelements;
+    }
+    /* the attention bucket: already on its way when the backward started the sums itself,
+     * otherwise summed now on the library stream (which also checks that the layer is on CUDA) */
+    if (!boat_cuda_allreduce_pending()) {
+        int rc = boat_attention_allreduce_grads(b->attn);
+        if (rc != 0) return rc;
+    }
+    if (boat_report("block gradient all-reduce", boat_cuda_allreduce_begin(piece, count, n)) != 0) return 3;
+    return boat_report("block gradient all-reduce", boat_cuda_allreduce_join());
+}

@@ -465,6 +465,11 @@ class EncoderBlock:
         dx = Tensor(lib.boat_encoder_block_backward(self.h, dout.h))
         return out, dx
 
+    def allreduce_grads(self):
+        rc = capi.load().boat_encoder_block_allreduce_grads(self.h)
+        if rc:
+            raise BoatError("boat_encoder_block_allreduce_grads failed (%d)" % rc)
+
     def zero_dense_grads(self):
         """Dense gradients accumulate across backward calls (as in the reference); a training loop
         clears them with the update step - lr 0 leaves the weights alone."""

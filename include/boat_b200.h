@@ -88,6 +88,11 @@ BOAT_API boat_encoder_block_t* boat_encoder_block_create(boat_layernorm_t* norm1
 BOAT_API boat_tensor_t* boat_encoder_block_forward(boat_encoder_block_t* block, const boat_tensor_t* x);
 BOAT_API boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* block, const boat_tensor_t* grad_output);
 BOAT_API void boat_encoder_block_free(boat_encoder_block_t* block);
+/* Data-parallel training of the block: sum every parameter gradient it left in its layers (the
+ * attention bucket, both LayerNorms, both dense layers) over the ranks of the communicator, in
+ * place; joins sums the attention backward started itself (boat_attention_set_grad_overlap).
+ * The layers must be on BOAT_DEVICE_CUDA.  Returns 0 on success. */
+BOAT_API int boat_encoder_block_allreduce_grads(boat_encoder_block_t* block);
 
 /* Fill the layer's parameters from a safetensors checkpoint image (or file).  The reference
  * detects attention tensors by name in src/format/huggingface.c:917-932 and stops there (TODO);

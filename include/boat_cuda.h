@@ -19,8 +19,12 @@ extern "C" {
 #endif
 #pragma GCC visibility push(default)
 
-/* Storage type of a device buffer. */
-enum { BOAT_CUDA_F32 = 0, BOAT_CUDA_BF16 = 1 };
+/* Storage type of a device buffer.  BOAT_CUDA_F32_TF32 is FP32 storage whose values have been
+ * rounded to the nearest TF32 number (10 mantissa bits): accepted as the OUTPUT type of
+ * boat_cuda_gemm for results that feed another TF32 contraction - the tensor core truncates
+ * FP32 operands, so rounding in the producing epilogue keeps the pipeline unbiased without a
+ * separate rounding pass.  As an input type it is the same as BOAT_CUDA_F32. */
+enum { BOAT_CUDA_F32 = 0, BOAT_CUDA_BF16 = 1, BOAT_CUDA_F32_TF32 = 2 };
 
 /* Arithmetic used by the contraction kernels.
  *   FP32: CUDA-core FMA, any shape (the exact path; reference numerics are IEEE FP32).
@@ -94,7 +98,8 @@ int boat_cuda_gemm(int mma, int trans_a, int trans_b, int64_t M, int64_t N, int6
  * u*S*hs - the reference's reshape-only head split (attention.c:393-397).
  * O = softmax(scale * Q K^T, causal: j>i masked) V.  The S x S probabilities are never
  * stored; lse[units*S] (FP32) receives max + log(sum exp) of the scaled scores per row,
- * which is all the backward needs. */
+ * which is all the backward needs.  With mma = BOAT_MMA_TF32 the values of O are rounded to
+ * TF32 (they feed the TF32 output projection); likewise dQ, dK, dV of the backward. */
 int boat_cuda_attn_fwd(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale,
                        const void* Q, const void* K, const void* V, int io_type,
                        void* O, float* lse);

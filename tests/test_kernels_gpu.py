@@ -62,6 +62,22 @@ def test_gemm_bf16_output_and_no_bias(gpu_lib, layout):
     assert rel(got, ref) <= TOL[capi.MMA_BF16]
 
 
+def test_gemm_can_round_its_output_to_tf32_for_the_next_contraction(gpu_lib):
+    """Output type BOAT_CUDA_F32_TF32: the same numbers as an FP32 output followed by boat_cuda_round_tf32,
+    on the tensor-core kernel and on the CUDA-core kernel."""
+    lib = gpu_lib
+    for (M, N, K) in ((256, 256, 128), (37, 24, 19)):
+        A, B = rng.normal(5, 0, (M, K)), rng.normal(5, 1, (K, N), std=1.0 / np.sqrt(K))
+        dA, dB = DeviceBuffer.from_numpy(A), DeviceBuffer.from_numpy(B)
+        plain, rounded = DeviceBuffer(M * N * 4), DeviceBuffer(M * N * 4)
+        for out, typ in ((plain, capi.CUDA_F32), (rounded, capi.CUDA_F32_TF32)):
+            check(lib.boat_cuda_gemm(capi.MMA_TF32, 0, 0, M, N, K, dA.p, K, dB.p, N, capi.CUDA_F32, out.p, N, typ, None))
+        check(lib.boat_cuda_round_tf32(plain.p, plain.p, M * N))
+        got, want = rounded.numpy((M, N)), plain.numpy((M, N))
+        assert not (got.view(np.uint32) & np.uint32(0x1FFF)).any()
+        assert np.array_equal(got, want), (M, N, K)
+
+
 def test_weight_gradient_shape_uses_split_k(gpu_lib):
     """dW = X^T dY: 512 x 512 outputs, K = 16384 rows - few tiles, long K."""
     for mma in (capi.MMA_BF16, capi.MMA_TF32):
