@@ -19,12 +19,12 @@
 //   dQ_i = dS . K                   A = the same shared-memory tile read along M (MN-major view)
 //
 // Tensor memory (512 columns): R0 = S^T / P^T (128), dQ (HS), dV (HS), dK (HS); with head size
-// 128 that is all of it and dP^T shares R0 - with the scores rather than with dQ, so reading dQ
-// out never holds up the next tile - and S^T of tile t+1 is issued as soon as the softmax warps
-// have loaded dP^T of tile t: it executes while they compute dS^T, and the exponentials of tile
-// t+1 then overlap the dK and dQ MMAs of tile t.  The softmax warps are the critical resource
-// (A, wait for dV and dP^T, B).  With head size 64 dP^T has 128 columns of its own, is issued a
-// tile ahead, and the softmax warps go from A straight to B.
+// 128 that is all of it and dP^T borrows the dQ columns: the dQ warps take a tile's dQ into
+// registers and shared memory within a few hundred cycles of its completion, and the next dQ
+// product only comes after the softmax warps have consumed dP^T.  With head size 64 dP^T has 128
+// columns of its own.  In both cases dP^T is issued a tile ahead, S^T of tile t+1 follows dV of
+// tile t on the pipe, and the softmax warps - the critical resource - go from the exponentials
+// (A) straight to dS^T (B) without waiting for the tensor pipe.
 //
 // dQ of a query tile gets one contribution per key tile; CTAs add theirs into an FP32 buffer
 // with TMA reduce-add (cp.reduce.async.bulk.tensor), and a cast kernel turns the sum into the
@@ -58,12 +58,16 @@ struct BwdCfg {
     // from the launch (checked at kernel entry) - there is no room for manual alignment slack.
     static constexpr int SMEM = 2 * TILE_BYTES + Q_STAGES * 2 * TILE_BYTES + DS_BYTES + 2048 + 256;
     // tensor memory columns
-    // R0 (columns 0..127) holds S^T, then P^T.  dP^T goes there too when nothing else is left
-    // (head size 128); with head size 64 it has 128 columns of its own, can be issued a tile
-    // ahead, and the softmax warps never wait for it.
+    // R0 (columns 0..127) holds S^T, then P^T.  With head size 64 dP^T has 128 columns of its
+    // own.  With head size 128 nothing is left (R0 + dQ + dV + dK = 512), and dP^T borrows the dQ
+    // columns: they are idle from the moment the dQ warps hold a tile's dQ in registers and
+    // shared memory until the next tile's dQ product, which needs dS^T and therefore comes after
+    // the softmax warps have read dP^T anyway.  Either way dP^T of a tile is issued before the
+    // softmax warps ask for it, and they go from the exponentials straight on to dS^T.
     static constexpr bool DP_OWN = 256 + 3 * HS <= 512;
-    static constexpr uint32_t COL_S = 0, COL_DP = DP_OWN ? 128 : 0;
+    static constexpr uint32_t COL_S = 0;
     static constexpr uint32_t COL_DQ = DP_OWN ? 256 : 128, COL_DV = COL_DQ + HS, COL_DK = COL_DQ + 2 * HS;
+    static constexpr uint32_t COL_DP = DP_OWN ? 128 : COL_DQ;
     static constexpr uint32_t TMEM_COLS = 512;
 };
 
@@ -119,7 +123,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t* do_full = bars + 19;              // [Q_STAGES] dO tile landed
     uint64_t* q_empty = bars + 22;              // [Q_STAGES] S^T and dK of the tile are complete: its Q stage is free
     uint64_t* p_full = bars + 3;                // P^T in TMEM (256 arrivals)
-    uint64_t* r0_free = bars + 4;               // dP^T loaded into registers (256 arrivals)
     uint64_t* kv_empty = bars + 1;              // the first walk's MMAs are complete: K and V may be replaced
     uint64_t* acc_free = bars + 2;              // dK, dV of the first walk are stored (256 arrivals)
     uint32_t* tmem_slot = (uint32_t*)(bars + 25);
@@ -167,7 +170,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_init(s_full, 1);
         mbar_init(ds_full, 256);
         mbar_init(p_full, 256);
-        mbar_init(r0_free, 256);
         mbar_init(dp_full, 1);
         mbar_init(dq_full, 1);
         mbar_init(dq_empty, 1);
@@ -227,12 +229,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             constexpr uint32_t idesc_dq = make_idesc(kBF16, true, true, kTile, HS);        // dQ
             const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
             // Issue order on the (in-order) tensor pipe, per tile t:
-            //   head size 128:  dV(t) dP(t) | S(t+1) | dK(t) dQ(t)
-            //   head size 64:   dV(t) S(t+1) | dK(t) dQ(t) dP(t+1)
-            // dV follows phase A.  With head size 128 dP^T overwrites P^T in R0, which dV, ahead of
-            // it on the pipe, is the only reader of, and S^T of the next tile overwrites dP^T once
-            // the softmax warps hold it in registers.  With head size 64 dP^T has its own columns
-            // and is ready long before phase B asks for it.  dK and dQ need dS^T from phase B.
+            //   dV(t) S(t+1) | dK(t) dQ(t) | dP(t+1)
+            // dV follows phase A; S^T of the next tile overwrites R0 right behind it (dV, ahead on
+            // the pipe, is the only reader of P^T).  dK and dQ need dS^T from phase B.  dP^T of the
+            // next tile follows them: into its own columns (head size 64), or into the dQ columns
+            // once the dQ warps have taken this tile's dQ out of them (head size 128) - in both
+            // cases long before phase B of the next tile asks for it.
             auto issue_s = [&](int t) -> bool {
                 const int s = t % C::Q_STAGES;
                 if (!mbar_wait(&q_full[s], (t / C::Q_STAGES) & 1, p.status, kTimeoutMma)) return false;
@@ -263,7 +265,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             };
             bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutMma);
             ok = ok && issue_s(0);
-            if (C::DP_OWN) ok = ok && issue_dp(0);
+            ok = ok && issue_dp(0);
             for (int t = 0; t < n_q && ok; ++t) {
                 const int s = t % C::Q_STAGES;
                 const bool first = t == 0 || t == nA;           // first tile of a walk: dK, dV start over
@@ -275,7 +277,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     // head size 64 the dP^T columns) are free: phase B of the previous tile is over.
                     if (!mbar_wait(kv_full, 1, p.status, kTimeoutMma)) { ok = false; break; }
                     if (!issue_s(t)) { ok = false; break; }
-                    if (C::DP_OWN && !issue_dp(t)) { ok = false; break; }
+                    // the first walk's last dQ must be out of the columns dP^T borrows
+                    if (!C::DP_OWN && !mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    if (!issue_dp(t)) { ok = false; break; }
                 }
                 if (!mbar_wait(p_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 if (!mbar_wait(&do_full[s], (t / C::Q_STAGES) & 1, p.status, kTimeoutMma)) { ok = false; break; }
@@ -285,16 +289,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int kk = 0; kk < kTile / 16; ++kk)      // dV += P^T . dO      (K = 128 query rows)
                     mma_ts<false>(tmem_base + C::COL_DV, tmem_base + C::COL_S + (kk / 4) * 64 + (kk % 4) * 8,
                                   smem_desc_mn(do_addr + kk * 2048, kBoxBytes, false), idesc_acc, !first || kk > 0);
-                if (C::DP_OWN) {
-                    // R0 is free as soon as dV, ahead on the pipe, has read P^T
-                    if (early_next && !issue_s(t + 1)) { ok = false; break; }
-                } else {
-                    if (!issue_dp(t)) { ok = false; break; }
-                    if (early_next) {
-                        if (!mbar_wait(r0_free, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
-                        if (!issue_s(t + 1)) { ok = false; break; }
-                    }
-                }
+                // R0 is free as soon as dV, ahead on the pipe, has read P^T
+                if (early_next && !issue_s(t + 1)) { ok = false; break; }
                 if (!mbar_wait(ds_full, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 if (t > 0) {
                     // the previous dQ must have left its TMEM columns
@@ -318,7 +314,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     mma_commit(all_done);                   // and its dK, dV are complete
                 }
                 // dS^T of tile t is in shared memory, so the softmax warps are done with dP^T(t)
-                if (C::DP_OWN && early_next && !issue_dp(t + 1)) { ok = false; break; }
+                if (early_next) {
+                    // borrowed columns: this tile's dQ, just issued, has to complete and leave them first
+                    if (!C::DP_OWN && !mbar_wait(dq_empty, t & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                    if (!issue_dp(t + 1)) { ok = false; break; }
+                }
             }
             if (ok) mma_commit(all_done);
         }
@@ -439,10 +439,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0, d0);
                 tmem_ld32(tmem_base + C::COL_DP + lane_addr + col0 + 32, d1);
                 tmem_wait_ld();
-                if (!C::DP_OWN) {
-                    tc_fence_before_sync();
-                    mbar_arrive(r0_free);                    // R0 may take the next tile's scores
-                }
 #pragma unroll
                 for (int half32 = 0; half32 < 2; ++half32) {
 #pragma unroll
@@ -527,9 +523,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 tmem_ld32(tmem_base + C::COL_DQ + lane_addr + (C::NBOX + b) * 32, v[b]);
             tmem_wait_ld();
             tc_fence_before_sync();
-            if (tid128 == 0) tma_wait_group_read0();
-            named_barrier_sync(2, 128);                     // all loads done; the stage has been read
-            if (tid128 == 0) mbar_arrive(dq_empty);
+            named_barrier_sync(2, 128);                     // everybody holds the second half
+            if (tid128 == 0) {
+                mbar_arrive(dq_empty);                      // the dQ columns are free - before the wait below
+                tma_wait_group_read0();
+            }
+            named_barrier_sync(2, 128);                     // the stage has been read
             stage_half(v);
             named_barrier_sync(2, 128);
             if (tid128 == 0) {
