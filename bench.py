@@ -269,6 +269,18 @@ def run_reference_arm(args, cfg, rank, world):
     print(json.dumps(line))
 
 
+def l2_policy(cfg):
+    """(flush, text).  A step reads and writes at least 14 activation-sized tensors (X, three projections, the
+    attention output, the layer output, dOut, d(ctx), three projection gradients, three input gradients).
+    When that stream is several times the 126 MB L2, nothing of one step survives into the next and steps
+    are timed back to back; otherwise a 256 MB fill runs between separately timed steps."""
+    es = 2 if cfg["mma"] == "bf16" else 4
+    stream = 14.0 * cfg["B"] * cfg["S"] * cfg["d"] * es
+    if stream > 3 * 126e6:
+        return False, "inputs larger than L2: a step streams %.0f MB of activations through the 126 MB L2" % (stream / 1e6)
+    return True, "L2 flushed between steps by a 256 MB fill"
+
+
 def workload_config(name, cfg, world):
     return dict(workload="%s: attention fwd+bwd, batch=%d per GPU, seq=%d, d_model=%d, heads=%d (head_dim %d), %s, %s" %
                 (name, cfg["B"], cfg["S"], cfg["d"], cfg["nh"], cfg["d"] // cfg["nh"],
@@ -276,8 +288,7 @@ def workload_config(name, cfg, world):
                  "BF16 storage, FP32 accumulate" if cfg["mma"] == "bf16" else "FP32 storage, TF32 MMA"),
                 batch_per_gpu=cfg["B"], global_batch=cfg["B"] * world, seq_len=cfg["S"], d_model=cfg["d"],
                 heads=cfg["nh"], causal=cfg["causal"], parallelism="dp%d over batch x heads units" % world,
-                l2="inputs larger than L2: activations of one step exceed 126 MB" if
-                cfg["B"] * cfg["S"] * cfg["d"] * 2 > 126e6 else "L2 flushed between steps by a 256 MB fill")
+                l2=l2_policy(cfg)[1])
 
 
 # ---- our arm -------------------------------------------------------------------------------------------------
@@ -372,7 +383,7 @@ def main():
     x = Tensor.from_numpy(x_host, capi.DEVICE_CUDA, bf16=bf16)
     g = Tensor.from_numpy(g_host, capi.DEVICE_CUDA, bf16=bf16)    # upstream gradient (attention) or MSE target (block)
     flush = None
-    if T * d * 2 <= 126e6:
+    if l2_policy(cfg)[0]:
         flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def block_step():
@@ -501,8 +512,8 @@ def main():
     kflops = {   # algorithmic FLOPs per launch scope
         "gemm_tc_nn": 2.0 * T * d * d, "gemm_tc_nt": 2.0 * T * d * d, "gemm_tc_tn": 2.0 * T * d * d,
         "gemm_simt": 2.0 * T * d * d,
-        "flash_fwd": 4.0 * core_c * B * S * S * d, "attn_fwd_simt": 4.0 * core_c * B * S * S * d,
-        "flash_bwd": 8.0 * core_c * B * S * S * d, "attn_bwd_simt": 8.0 * core_c * B * S * S * d,
+        "attn_fwd_tc": 4.0 * core_c * B * S * S * d, "attn_fwd_simt": 4.0 * core_c * B * S * S * d,
+        "attn_bwd_tc": 8.0 * core_c * B * S * S * d, "attn_bwd_simt": 8.0 * core_c * B * S * S * d,
     }
     kbytes = {"adam_step": 28.0 * (4 * d * d + 4 * d)}     # p, g, m, v read; p, m, v written (FP32)
     roofline = None

@@ -1,4 +1,4 @@
-// flash_bwd_tc.cuh - fused attention backward on tcgen05 (BF16 storage, FP32 accumulation).
+// attn_bwd_tc.cuh - fused attention backward on tcgen05 (BF16 storage, FP32 accumulation).
 //
 // Replaces attention_backward (reference src/layers/attention.c:1421-1526), which keeps the
 // probabilities of the forward and builds four more [B,nh,S,S] tensors.  Here P is rebuilt
@@ -37,10 +37,10 @@
 // Warp 0: TMA producer (K, V, Q), warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store
 // (two warps per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.
 #pragma once
-#include "flash_fwd_tc.cuh"
+#include "attn_fwd_tc.cuh"
 
 namespace boatcu {
-namespace flash {
+namespace attn_tc {
 
 constexpr int kBwdThreads = 448;
 
@@ -95,7 +95,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 
 template <int HS>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                  const __grid_constant__ CUtensorMap map_dq, const BwdParams p) {
     using C = BwdCfg<HS>;
@@ -554,5 +554,5 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 }
 
-}  // namespace flash
+}  // namespace attn_tc
 }  // namespace boatcu

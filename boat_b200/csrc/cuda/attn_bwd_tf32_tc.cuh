@@ -31,10 +31,10 @@
 // once per tensor map; the second copy comes from L2.
 // Warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: softmax and epilogue.
 #pragma once
-#include "flash_bwd_tc.cuh"
+#include "attn_bwd_tc.cuh"
 
 namespace boatcu {
-namespace flash {
+namespace attn_tc {
 
 constexpr int kBwd32Threads = 192;
 constexpr int kBwd32HS = 64;
@@ -432,5 +432,5 @@ attn_bwd_dkv_tf32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
 }
 
-}  // namespace flash
+}  // namespace attn_tc
 }  // namespace boatcu

@@ -1,4 +1,4 @@
-// flash_fwd_tc.cuh - fused attention forward on tcgen05: scaled QK^T, causal mask, online
+// attn_fwd_tc.cuh - fused attention forward on tcgen05: scaled QK^T, causal mask, online
 // softmax and PV in one kernel; the S x S matrix lives only in tensor memory, only the
 // log-sum-exp per row is saved for the backward.
 //
@@ -23,7 +23,7 @@
 #include <float.h>
 
 namespace boatcu {
-namespace flash {
+namespace attn_tc {
 
 using namespace tc;
 
@@ -66,7 +66,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 template <typename T, int HS>
 __global__ void __launch_bounds__(kFwdThreads, 2)
-flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
     using C = FwdCfg<T, HS>;
     constexpr bool TF32 = C::TF32;
@@ -336,5 +336,5 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 }
 
-}  // namespace flash
+}  // namespace attn_tc
 }  // namespace boatcu

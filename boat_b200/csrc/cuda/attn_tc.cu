@@ -1,13 +1,13 @@
-// flash_tc.cu - host side of the tcgen05 attention-core kernels: shape support, tensor maps,
-// launches.  The kernels themselves are in flash_fwd_tc.cuh, flash_bwd_tc.cuh (BF16 storage) and
+// attn_tc.cu - host side of the tcgen05 attention-core kernels: shape support, tensor maps,
+// launches.  The kernels themselves are in attn_fwd_tc.cuh, attn_bwd_tc.cuh (BF16 storage) and
 // attn_bwd_tf32_tc.cuh (FP32 storage).
-#include "flash_bwd_tc.cuh"
+#include "attn_bwd_tc.cuh"
 #include "attn_bwd_tf32_tc.cuh"
 #include <stdlib.h>
 
 namespace boatcu {
 
-using namespace flash;
+using namespace attn_tc;
 
 namespace {
 
@@ -30,16 +30,16 @@ int launch_fwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     p.causal = causal;
     p.scale = scale;
     p.status = kernel_status_ptr();
-    auto kern = flash_fwd_kernel<T, HS>;
+    auto kern = attn_fwd_tc_kernel<T, HS>;
     static bool configured = false;
     if (!configured) {
         BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
     const int64_t grid = units * (S / kTile);
-    ProfileScope prof("flash_fwd");
+    ProfileScope prof("attn_fwd_tc");
     kern<<<(unsigned)grid, kFwdThreads, C::SMEM, stream()>>>(mq, mk, mv, p);
-    BOATCU_LAUNCH_OK("flash_fwd");
+    BOATCU_LAUNCH_OK("attn_fwd_tc");
     return 0;
 }
 
@@ -105,18 +105,18 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     }
     p.scale = scale;
     p.status = kernel_status_ptr();
-    auto kern = flash_bwd_kernel<HS>;
+    auto kern = attn_bwd_tc_kernel<HS>;
     static bool configured = false;
     if (!configured) {
         BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
     {
-        ProfileScope prof("flash_bwd");
+        ProfileScope prof("attn_bwd_tc");
         BOATCU_CHECK(cudaMemsetAsync(dq_accum, 0, n * sizeof(float), stream()));
         const int64_t grid = units * (p.pair ? (S / kTile + 1) / 2 : S / kTile);
         kern<<<(unsigned)grid, kBwdThreads, C::SMEM, stream()>>>(mq, mk, mv, mdo, mdq, p);
-        BOATCU_LAUNCH_OK("flash_bwd");
+        BOATCU_LAUNCH_OK("attn_bwd_tc");
         // the summed FP32 contributions become the BF16 output
         if (int rc = boat_cuda_cast(dQ, BOAT_CUDA_BF16, dq_accum, BOAT_CUDA_F32, (int64_t)n)) return rc;
     }
@@ -158,7 +158,7 @@ int launch_bwd_tf32(int64_t units, int64_t S, int causal, float scale, const voi
         configured = true;
     }
     const unsigned grid = (unsigned)(units * (S / kTile));
-    ProfileScope prof("flash_bwd");
+    ProfileScope prof("attn_bwd_tc");
     attn_bwd_dkv_tf32_kernel<<<grid, kBwd32Threads, C::SMEM_DKV, stream()>>>(mq, mq_mn, mk, mv, mdo, mdo_mn, p);
     BOATCU_LAUNCH_OK("attn_bwd_dkv_tf32");
     attn_bwd_dq_tf32_kernel<<<grid, kBwd32Threads, C::SMEM_DQ, stream()>>>(mq, mk, mk_mn, mv, mdo, p);
