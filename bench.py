@@ -493,13 +493,30 @@ def main():
             for tt in (out, gq, gk, gv):
                 tt.free()
 
+        def bucket_to_host():
+            ptr, n = C.POINTER(C.c_float)(), C.c_size_t()
+            check(lib.boat_attention_grad_bucket(layer.h, C.byref(ptr), C.byref(n)), "grad_bucket")
+            host = np.empty(n.value, np.float32)
+            check(lib.boat_cuda_memcpy_d2h(host.ctypes.data_as(C.c_void_p), C.cast(ptr, C.c_void_p), host.nbytes), "d2h")
+            return host
+
+        # numbers, outside the timed regions: the bucket summed over the unit ranges must be the gradient of
+        # the whole problem.  Rank 0's own (weak-scaling) batch IS that problem, so it can compute the latter alone.
+        strong_step()
+        sync_all()
+        reduced = bucket_to_host()
         layer.set_grad_overlap(False)
         n1_ms = timed(single_gpu_step, max(3, min(args.steps, 10)))
+        whole = bucket_to_host()
         layer.set_grad_overlap(True)
+        grad_err = float(np.abs(reduced.astype(np.float64) - whole).max() / np.abs(whole).max()) if rank == 0 else None
         strong = dict(workload="the %s problem at GLOBAL batch %d split by (batch, head) units: %d units = %d token rows per GPU" %
                       (args.workload, B, u[1] - u[0], r1 - r0), global_batch=B, units_per_gpu=u[1] - u[0],
                       rows_per_gpu=r1 - r0, ms_per_step=strong_ms, tokens_per_s=T / (strong_ms * 1e-3),
                       n1_ms_per_step=n1_ms, speedup_vs_n1=n1_ms / strong_ms,
+                      grad_check=dict(rel_err=grad_err, tolerance=2e-2 if bf16 else 5e-3,
+                                      what="max|sum over ranks of the unit-range gradient buckets - single-GPU bucket of "
+                                           "the whole problem| / max|single-GPU bucket|, on rank 0"),
                       note="n1_ms_per_step: the whole problem on one GPU without exchange, timed in this run on every rank (max)")
 
     # ---- roofline of the dominant kernel family ----

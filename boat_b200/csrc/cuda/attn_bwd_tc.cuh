@@ -34,7 +34,11 @@
 // gets reductions out at only about 20 bytes per clock (measured alike for TMA reduce-add and
 // for red.global.add.v4.f32, which also stalls the softmax warps' shared memory traffic), so
 // the read-out of a tile takes most of a tile period - off the critical path.
-// Warp 0: TMA producer (K, V, Q), warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store
+// The softmax warps synchronise only through the mbarriers of the pipeline - no barrier among
+// themselves inside a walk: the per-row statistics of a query tile (-lse*log2e and
+// -delta/sqrt(hs), pre-scaled by a small kernel) are brought in by the producer with two bulk
+// copies per tile.
+// Warp 0: TMA producer (K, V, Q, statistics), warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store
 // (two warps per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.
 #pragma once
 #include "attn_fwd_tc.cuh"
@@ -72,8 +76,8 @@ struct BwdCfg {
 };
 
 struct BwdParams {
-    const float* lse;      // [units*S]
-    const float* delta;    // [units*S]
+    const float* lse2;     // [units*S]  -lse * log2(e): the exponent offset in the log2 domain
+    const float* delta2;   // [units*S]  -delta / sqrt(hs)
     float* dq_accum;       // [units*S, hs] FP32, zeroed before the launch
     void* dK;
     void* dV;
@@ -125,8 +129,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint64_t* p_full = bars + 3;                // P^T in TMEM (256 arrivals)
     uint64_t* kv_empty = bars + 1;              // the first walk's MMAs are complete: K and V may be replaced
     uint64_t* acc_free = bars + 2;              // dK, dV of the first walk are stored (256 arrivals)
+    uint64_t* stat_full = bars + 11;            // [2] the tile's statistics landed
+    uint64_t* stat_empty = bars + 13;           // [2] phase B of the tile is over (256 arrivals)
     uint32_t* tmem_slot = (uint32_t*)(bars + 25);
-    volatile uint32_t* softmax_ok = tmem_slot + 1;     // [2] written by one softmax thread, read by all 256
     volatile uint32_t* drain_ok = tmem_slot + 3;       // same idea for the dQ warps
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -176,6 +181,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_init(all_done, 1);
         mbar_init(kv_empty, 1);
         mbar_init(acc_free, 256);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&stat_full[b], 1);
+            mbar_init(&stat_empty[b], 256);
+        }
         fence_barrier_init();
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
@@ -219,6 +228,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int b = 0; b < C::NBOX; ++b)
                     tma_load_2d(q_smem + s * C::TILE_BYTES + b * kBoxBytes, &map_q, &q_full[s], b * 64,
                                 row_base + qtile(t) * kTile);
+                // the tile's 128 exponent offsets and 128 deltas, into the buffer of its parity once
+                // the tile before last has left it
+                if (!mbar_wait(&stat_empty[t & 1], ((t >> 1) & 1) ^ 1, p.status, kTimeoutProducer)) break;
+                mbar_arrive_expect_tx(&stat_full[t & 1], 1024);
+                bulk_load_1d(stat_s + (t & 1) * 256, p.lse2 + row_base + qtile(t) * kTile, 512, &stat_full[t & 1]);
+                bulk_load_1d(stat_s + (t & 1) * 256 + 128, p.delta2 + row_base + qtile(t) * kTile, 512, &stat_full[t & 1]);
             }
         }
     } else if (warp == 1) {
@@ -330,24 +345,19 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int lane_group = warp & 3;
         const int half = w >> 2;
         const int r = lane_group * 32 + lane;                       // key row inside the tile
-        const int tid256 = w * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
         const uint32_t col0 = 64u * half;                           // first query column of this thread
         const float sl2 = p.scale * 1.4426950408889634f;
         uint8_t* ds_row = ds_smem + half * kBoxBytes + r * 128;     // box `half` holds query columns 64h..64h+63
         const int swz = r & 7;
         bool ok = true;
-        // threads 0..127 carry lse of query row (tid & 127), threads 128..255 delta
-        const float* stat_src = (tid256 < 128 ? p.lse : p.delta) + row_base + (tid256 & 127);
-        float stat_next = stat_src[(int64_t)qtile(0) * kTile];
-        // dK, dV of a finished walk: the first four warps store dV, the other four dK.  One thread
-        // does the bounded wait and publishes the outcome so that all 256 take the same branch.
+        // Every thread does its own (bounded) waits; there is no barrier among the softmax warps
+        // inside the walk, so a thread that is done with a tile moves on at once.  When a wait
+        // gives up, the thread leaves the loop; the others see the status word at their next wait
+        // and follow.
+        // dK, dV of a finished walk: the first four warps store dV, the other four dK.
         auto store_dkdv = [&](int jt, uint32_t phase) -> bool {
-            if (tid256 == 0) softmax_ok[0] = mbar_wait(all_done, phase, p.status, kTimeoutEpilogue) ? 1u : 0u;
-            named_barrier_sync(1, 256);
-            const bool fine = softmax_ok[0] != 0u;
-            named_barrier_sync(1, 256);                 // everybody has read the flag before it is reused
-            if (!fine) return false;
+            if (!mbar_wait_warp(all_done, phase, p.status, kTimeoutEpilogue)) return false;
             tc_fence_after_sync();
             const int64_t grow = (int64_t)row_base + (int64_t)jt * kTile + r;
             __nv_bfloat16* out = (__nv_bfloat16*)(half ? p.dK : p.dV) + grow * HS;
@@ -371,21 +381,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         };
         for (int t = 0; t < n_q; ++t) {
             const int i = qtile(t);
-            // Stage lse*log2e and delta of this query tile in the buffer of this tile's parity.
-            // A thread can only get two tiles ahead of another by passing the barriers of the
-            // tile in between, which needs that other thread to have left this tile.
-            float* lse_s = stat_s + (t & 1) * 256;
-            float* delta_s = lse_s + 128;
-            // The value was fetched from global memory one tile earlier (a cold line would
-            // otherwise sit on the critical path between two tiles); fetch the next one now.
-            if (tid256 < 128) lse_s[tid256] = stat_next * -1.4426950408889634f;        // -lse in the log2 domain
-            else delta_s[tid256 - 128] = stat_next * -p.scale;                         // -delta / sqrt(hs)
-            if (t + 1 < n_q) stat_next = stat_src[(int64_t)qtile(t + 1) * kTile];
-            // One thread does each bounded wait and publishes the outcome, so that all 256 take
-            // the same branch and nobody is left alone at a named barrier.
-            if (tid256 == 0) softmax_ok[0] = mbar_wait(s_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
-            named_barrier_sync(1, 256);
-            if (softmax_ok[0] == 0u) { ok = false; break; }
+            // -lse*log2e and -delta/sqrt(hs) of this query tile, put into the buffer of this tile's
+            // parity by the producer
+            const float* lse_s = stat_s + (t & 1) * 256;
+            const float* delta_s = lse_s + 128;
+            if (!mbar_wait_warp(&stat_full[t & 1], (t >> 1) & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
+            if (!mbar_wait_warp(s_full, t & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
             tc_fence_after_sync();
             const bool diag = p.causal && i == (t < nA ? jtA : jtB);
             // ---- phase A: P^T = exp2(S^T*c - lse) for this thread's 64 columns ----
@@ -430,9 +431,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tc_fence_before_sync();
             mbar_arrive(p_full);
             // ---- phase B: dS^T = P^T * (dP^T - delta) / sqrt(hs) ----
-            if (tid256 == 0) softmax_ok[1] = mbar_wait(dp_full, t & 1, p.status, kTimeoutSoftmax) ? 1u : 0u;
-            named_barrier_sync(1, 256);
-            if (softmax_ok[1] == 0u) { ok = false; break; }
+            if (!mbar_wait_warp(dp_full, t & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
             tc_fence_after_sync();
             {
                 uint32_t d0[32], d1[32];
@@ -465,6 +464,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             fence_proxy_async_smem();
             mbar_arrive(ds_full);
+            mbar_arrive(&stat_empty[t & 1]);                 // this tile's statistics are no longer read
             if (t == nA - 1 && has_b) {
                 // end of the first walk: its dK, dV leave tensor memory before the second walk's first
                 // dV and dK MMAs start them over

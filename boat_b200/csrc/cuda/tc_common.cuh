@@ -91,6 +91,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
     return mbar_wait_limit(bar, parity, status, code, kWaitLimitNs);
 }
 
+// The same for a whole warp: true only when every lane's wait succeeded, so that the warp stays
+// converged for the warp-collective tensor-memory instructions that follow.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code) ? 1 : 0) != 0;
+}
+
 // ---- TMA ------------------------------------------------------------------------------------------
 // Tile load global -> shared (no multicast), completion counted in bytes on `bar`.
 // x = innermost (contiguous) coordinate in elements, y = row.
@@ -99,6 +105,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
+}
+// Untiled bulk copy global -> shared (no multicast): `bytes` (a multiple of 16) from a 16-byte
+// aligned global address to a 16-byte aligned shared address, completion counted on `bar`.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
 }
 // Tile reduction shared -> global: adds the box at `smem_src` (laid out as a TMA load of the
 // same map would leave it) into the tensor at (x, y).  Completion is tracked by bulk groups.
