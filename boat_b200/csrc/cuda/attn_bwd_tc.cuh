@@ -244,7 +244,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             constexpr uint32_t idesc_dq = make_idesc(kBF16, true, true, kTile, HS);        // dQ
             const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
             // Issue order on the (in-order) tensor pipe, per tile t:
-            //   dV(t) S(t+1) | dK(t) dQ(t) | dP(t+1)
+            //   dV(t) S(t+1) | dQ(t) dK(t) | dP(t+1)
             // dV follows phase A; S^T of the next tile overwrites R0 right behind it (dV, ahead on
             // the pipe, is the only reader of P^T).  dK and dQ need dS^T from phase B.  dP^T of the
             // next tile follows them: into its own columns (head size 64), or into the dQ columns
@@ -312,18 +312,22 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     if (!mbar_wait(dq_empty, (t - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
                 }
                 tc_fence_after_sync();
+                // dQ first: its completion starts the read-out, whose first step (tensor memory ->
+                // registers) gates the next tile's dP^T when that borrows the dQ columns; dK runs
+                // on the pipe meanwhile.  This tile's dO stage was last read by dV and dP^T, which
+                // are ahead of dQ on the pipe, so it is free for the read-out's staging at dq_full.
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)      // dQ_i = dS . K        (K = 128 key rows)
+                    mma_ss<false>(tmem_base + C::COL_DQ, smem_desc_mn(ds_addr + kk * 2048, kBoxBytes, false),
+                                  smem_desc_mn(k_addr + kk * 2048, kBoxBytes, false), idesc_dq, kk > 0);
+                mma_commit(dq_full);
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk) {    // dK += dS^T . Q
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
                     mma_ss<false>(tmem_base + C::COL_DK, smem_desc_sw128(ds_addr + off, 16, 1024),
                                   smem_desc_mn(q_addr + kk * 2048, kBoxBytes, false), idesc_acc, !first || kk > 0);
                 }
-#pragma unroll
-                for (int kk = 0; kk < kTile / 16; ++kk)      // dQ_i = dS . K        (K = 128 key rows)
-                    mma_ss<false>(tmem_base + C::COL_DQ, smem_desc_mn(ds_addr + kk * 2048, kBoxBytes, false),
-                                  smem_desc_mn(k_addr + kk * 2048, kBoxBytes, false), idesc_dq, kk > 0);
-                mma_commit(&q_empty[s]);
-                mma_commit(dq_full);      // also: this tile's dO stage and the dS^T tile are no longer read
+                mma_commit(&q_empty[s]);  // also: the dS^T tile is no longer read
                 if (t == nA - 1 && has_b) {
                     mma_commit(kv_empty);                   // K and V of the first walk are no longer read
                     mma_commit(all_done);                   // and its dK, dV are complete
@@ -477,15 +481,23 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (ok) store_dkdv(has_b ? jtB : jtA, has_b ? 1u : 0u);
     } else {
         // ---------------- dQ reduction: warps 10..13, thread = query row ----------------
-        // The FP32 dQ tile is HS/32 boxes of 128 rows x 128 bytes, twice the size of the tile's dO
-        // stage, which is idle once the tile's MMAs are complete: two passes through it, the
-        // second half waiting in registers meanwhile.  After the second pass the same thread
-        // loads the dO tile two steps ahead into the stage.
+        // The FP32 dQ tile is HS/32 boxes of 128 rows x 128 bytes (16 KB each), twice what the tile's
+        // dO stage holds - the stage is idle once the tile's MMAs are complete and serves as the
+        // staging area, one box per slot.  The first half of the boxes goes straight through their
+        // slots; the second half is taken into registers at once (which frees the tensor-memory
+        // columns) and follows box by box, each as soon as the reduction that used its slot has
+        // been read out - so the TMA unit always has the next box queued behind the one it is
+        // reading.  The dO tile two steps ahead is then loaded slot by slot on the same terms.
         const int lane_group = warp & 3;
         const int r = lane_group * 32 + lane;
         const int tid128 = (warp - 10) * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
         const int swz = r & 7;
+        // all but the most recent n reduction groups of this thread have been read out of shared memory
+        auto wait_read = [](int n) {
+            if (n == 0) tma_wait_group_read0();
+            else tma_wait_group_read1();
+        };
         for (int t = 0; t < n_q; ++t) {
             const int s = t % C::Q_STAGES;
             if (tid128 == 0) drain_ok[0] = mbar_wait(dq_full, t & 1, p.status, kTimeoutOther) ? 1u : 0u;
@@ -494,53 +506,54 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tc_fence_after_sync();
             const int y = row_base + qtile(t) * kTile;
             uint8_t* stage = do_smem + s * C::TILE_BYTES;
-            auto stage_half = [&](const uint32_t (&v)[C::NBOX][32]) {
+            auto stage_box = [&](const uint32_t (&v)[32], int slot) {
+                uint8_t* row = stage + slot * kBoxBytes + r * 128;
 #pragma unroll
-                for (int b = 0; b < C::NBOX; ++b) {
-                    uint8_t* row = stage + b * kBoxBytes + r * 128;
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        *reinterpret_cast<uint4*>(row + ((u ^ swz) << 4)) =
-                            make_uint4(v[b][4 * u], v[b][4 * u + 1], v[b][4 * u + 2], v[b][4 * u + 3]);
-                }
-                fence_proxy_async_smem();
+                for (int u = 0; u < 8; ++u)
+                    *reinterpret_cast<uint4*>(row + ((u ^ swz) << 4)) = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
             };
             uint32_t v[C::NBOX][32];
-            // first half: tensor memory -> registers -> stage -> TMA reduce-add
+            // boxes 0 .. NBOX-1: tensor memory -> registers -> their slots -> one reduction group each
 #pragma unroll
             for (int b = 0; b < C::NBOX; ++b) tmem_ld32(tmem_base + C::COL_DQ + lane_addr + b * 32, v[b]);
             tmem_wait_ld();
-            stage_half(v);
+#pragma unroll
+            for (int b = 0; b < C::NBOX; ++b) stage_box(v[b], b);
+            fence_proxy_async_smem();
             named_barrier_sync(2, 128);
             if (tid128 == 0) {
-                for (int b = 0; b < C::NBOX; ++b) tma_reduce_add_2d(&map_dq, stage + b * kBoxBytes, b * 32, y);
-                tma_commit_group();
+                for (int b = 0; b < C::NBOX; ++b) {
+                    tma_reduce_add_2d(&map_dq, stage + b * kBoxBytes, b * 32, y);
+                    tma_commit_group();
+                }
             }
-            // second half waits in registers while the TMA unit reads the first; the TMEM columns
-            // are free as soon as it is loaded
+            // boxes NBOX .. 2*NBOX-1 wait in registers; the TMEM columns are free as soon as they are loaded
 #pragma unroll
             for (int b = 0; b < C::NBOX; ++b)
                 tmem_ld32(tmem_base + C::COL_DQ + lane_addr + (C::NBOX + b) * 32, v[b]);
             tmem_wait_ld();
             tc_fence_before_sync();
             named_barrier_sync(2, 128);                     // everybody holds the second half
-            if (tid128 == 0) {
-                mbar_arrive(dq_empty);                      // the dQ columns are free - before the wait below
-                tma_wait_group_read0();
-            }
-            named_barrier_sync(2, 128);                     // the stage has been read
-            stage_half(v);
-            named_barrier_sync(2, 128);
-            if (tid128 == 0) {
-                for (int b = 0; b < C::NBOX; ++b)
+            if (tid128 == 0) mbar_arrive(dq_empty);         // the dQ columns are free
+#pragma unroll
+            for (int b = 0; b < C::NBOX; ++b) {
+                // slot b was last used by the group issued NBOX groups ago
+                if (tid128 == 0) wait_read(C::NBOX - 1);
+                named_barrier_sync(2, 128);                 // slot b has been read
+                stage_box(v[b], b);
+                fence_proxy_async_smem();
+                named_barrier_sync(2, 128);
+                if (tid128 == 0) {
                     tma_reduce_add_2d(&map_dq, stage + b * kBoxBytes, (C::NBOX + b) * 32, y);
-                tma_commit_group();
-                tma_wait_group_read0();
-                if (t + C::Q_STAGES < n_q) {
-                    mbar_arrive_expect_tx(&do_full[s], C::TILE_BYTES);
-                    for (int b = 0; b < C::NBOX; ++b)
-                        tma_load_2d(stage + b * kBoxBytes, &map_do, &do_full[s], b * 64,
-                                    row_base + qtile(t + C::Q_STAGES) * kTile);
+                    tma_commit_group();
+                }
+            }
+            if (tid128 == 0 && t + C::Q_STAGES < n_q) {
+                mbar_arrive_expect_tx(&do_full[s], C::TILE_BYTES);
+                for (int b = 0; b < C::NBOX; ++b) {
+                    wait_read(C::NBOX - 1 - b);             // the last group that used slot b has been read
+                    tma_load_2d(stage + b * kBoxBytes, &map_do, &do_full[s], b * 64,
+                                row_base + qtile(t + C::Q_STAGES) * kTile);
                 }
             }
         }
