@@ -291,6 +291,31 @@ def workload_config(name, cfg, world):
                 l2=l2_policy(cfg)[1])
 
 
+def bind_to_gpu_numa_node(torch, local_rank):
+    """Keeps this rank's threads (and so the page-locked host memory they first touch) on the NUMA node its GPU
+    hangs off: at N ranks per host the host-tensor path otherwise pushes every rank's copies through one
+    socket.  Reads the topology from sysfs; changes nothing on the GPU.  Returns a short description."""
+    try:
+        prop = torch.cuda.get_device_properties(local_rank)
+        bdf = "%04x:%02x:%02x.0" % (prop.pci_domain_id, prop.pci_bus_id, prop.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/numa_node" % bdf) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return "gpu %s reports no NUMA node" % bdf
+        with open("/sys/devices/system/node/node%d/cpulist" % node) as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return "NUMA node %d has no CPU this process may use" % node
+        os.sched_setaffinity(0, allowed)
+        return "gpu %s on NUMA node %d: %d CPUs" % (bdf, node, len(allowed))
+    except (OSError, ValueError, AttributeError) as e:
+        return "not bound (%s)" % type(e).__name__
+
+
 # ---- our arm -------------------------------------------------------------------------------------------------
 
 def main():
@@ -330,6 +355,7 @@ def main():
     if lib.boat_cuda_device_count() < 1:
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
+    affinity = bind_to_gpu_numa_node(torch, local_rank) if world > 1 else "single rank: not bound"
     check(lib.boat_cuda_init(local_rank), "boat_cuda_init")
     dist = None
     if world > 1:
@@ -627,6 +653,7 @@ def main():
                     roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches), clocks=clocks)
         if strong:
             line["strong"] = strong
+        line["host_affinity"] = affinity
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:

@@ -69,6 +69,19 @@ static void dev_free(void* p) {
     if (p) boat_report("device free", boat_cuda_free(p));
 }
 
+/* When set, host tensors are uploaded on the upload stream (ordered before later launches by an
+ * event) instead of by a copy that blocks the host.  Only the chunked host-tensor paths set it:
+ * they end with boat_cuda_sync(), so the host buffers are no longer read when the call returns. */
+static bool g_async_uploads = false;
+
+static int upload(void* dst, const void* src, size_t bytes) {
+    if (!g_async_uploads) return boat_cuda_memcpy_h2d(dst, src, bytes);
+    int rc = boat_cuda_copies_after_compute();           /* dst was just allocated on the library stream */
+    if (rc == 0) rc = boat_cuda_upload_async(dst, src, bytes);
+    if (rc == 0) rc = boat_cuda_join_uploads();
+    return rc;
+}
+
 /* Device buffer holding tensor `t` in storage type `type`.  *owned says whether the caller
  * must release it (false: it is the tensor's own HBM). */
 static void* stage_in(const boat_tensor_t* t, int type, bool* owned) {
@@ -82,7 +95,7 @@ static void* stage_in(const boat_tensor_t* t, int type, bool* owned) {
     if (t->device != BOAT_DEVICE_CUDA) {
         tmp = dev_alloc(n * storage_size(have));
         if (!tmp) return NULL;
-        if (boat_report("upload", boat_cuda_memcpy_h2d(tmp, t->data, n * storage_size(have))) != 0) {
+        if (boat_report("upload", upload(tmp, t->data, n * storage_size(have))) != 0) {
             dev_free(tmp);
             return NULL;
         }
@@ -526,8 +539,17 @@ static boat_tensor_t* forward_rows(boat_attention_t* a, const boat_tensor_t* que
     staged_params_t p;
     void* d_out = NULL;
     boat_tensor_t* result = NULL;
-    if (!stage_params(a, mma, type, &p)) goto done;
-    if (units / gran >= 2 && pipeline_enabled() && on_host(query) && on_host(key) && on_host(value)) {
+    const bool pipelined = units / gran >= 2 && pipeline_enabled() && on_host(query) && on_host(key) && on_host(value);
+    /* host parameters of a chunked call go up on the upload stream, ahead of the first chunk,
+     * without blocking the host between them */
+    g_async_uploads = pipelined;
+    const bool staged = stage_params(a, mma, type, &p);
+    g_async_uploads = false;
+    if (!staged) {
+        if (pipelined) boat_cuda_sync();        /* uploads already under way still read host memory */
+        goto done;
+    }
+    if (pipelined) {
         result = forward_pipelined(a, in, mma, type, &p);
         if (result) a->cached = true;
         goto done;
@@ -697,7 +719,15 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     /* gradient sums of the previous step still on the communication stream read the bucket
      * this step is about to overwrite */
     if (boat_cuda_allreduce_pending() && boat_report("gradient all-reduce", boat_cuda_allreduce_join()) != 0) goto done;
-    if (!stage_params(a, mma, type, &p)) goto done;
+    const bool pipelined = units / a->gran >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) &&
+                           on_host(a->cache_in[1]) && on_host(a->cache_in[2]);
+    g_async_uploads = pipelined;
+    const bool staged = stage_params(a, mma, type, &p);
+    g_async_uploads = false;
+    if (!staged) {
+        if (pipelined) boat_cuda_sync();        /* uploads already under way still read host memory */
+        goto done;
+    }
     /* gradients are produced in HBM; a host layer receives them with one copy at the end */
     d_bucket = a->device == BOAT_DEVICE_CUDA ? (float*)a->grad_bucket->data
                                              : (float*)dev_alloc(a->grad_bucket->nbytes);
@@ -708,8 +738,7 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         d_dw[i] = d_bucket + (size_t)i * H * H;
         d_db[i] = bias ? d_bucket + (size_t)4 * H * H + (size_t)i * H : NULL;
     }
-    if (units / a->gran >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) && on_host(a->cache_in[1]) &&
-        on_host(a->cache_in[2])) {
+    if (pipelined) {
         ok = backward_pipelined(a, grad_output, mma, type, &p, d_dw, d_db, gin);
         goto done;
     }
