@@ -216,5 +216,12 @@ def test_pre_ln_encoder_block_training_step(gpu_lib, bf16, B, S, d, nh, tol):
     got = block_gpu(gpu_lib, inp, nh, False, bf16)
     assert abs(got["loss"] - ref["loss"]) <= tol * ref["loss"]
     worst = {k: rel(got[k], ref[k]) for k in ref if k != "loss"}
-    bad = {k: v for k, v in worst.items() if v > tol}
+    print("encoder block, relative error per tensor:", {k: "%.2e" % v for k, v in worst.items()})
+    # BF16: every tensor is held to the 2e-2 of the attention path except the three that sit at the end of
+    # the longest chains of BF16 roundings (measured 1.8e-2, 3.6e-2, 2.7e-2): the block output (LN, attention,
+    # residual, LN, two GEMMs, GELU, residual, each stored in BF16), dx (all of that again, backwards) and dWq
+    bound = dict.fromkeys(worst, min(tol, 2e-2) if bf16 else tol)
+    if bf16:
+        bound.update(out=2.5e-2, dx=tol, dwq=4e-2)
+    bad = {k: v for k, v in worst.items() if v > bound[k]}
     assert not bad, (bad, worst)
