@@ -398,9 +398,12 @@ def main():
         layer.to_device(capi.DEVICE_CUDA)
         layer.set_precision(mma)
     if world > 1:
-        # the backward itself starts the gradient sums (dWo | dbo under the attention-core backward,
-        # the rest under the input-gradient GEMMs); allreduce_grads() then only joins them
-        layer.set_grad_overlap(True)
+        # the backward itself starts the sum of dWo | dbo (it runs under the attention-core backward);
+        # allreduce_grads() starts the rest and joins.  BOAT_GRAD_OVERLAP=1 also starts the rest from the
+        # backward, under the persistent input-gradient GEMMs (measured no better: those lose to a
+        # co-running collective about what the overlap saves); 0 sums everything at the end.
+        overlap_mode = int(os.environ.get("BOAT_GRAD_OVERLAP", "2"))
+        layer.set_grad_overlap(overlap_mode)
     adam = None
     if args.optimizer == "adam":
         from boat_b200.host import Adam
@@ -531,10 +534,10 @@ def main():
         strong_step()
         sync_all()
         reduced = bucket_to_host()
-        layer.set_grad_overlap(False)
+        layer.set_grad_overlap(0)
         n1_ms = timed(single_gpu_step, max(3, min(args.steps, 10)))
         whole = bucket_to_host()
-        layer.set_grad_overlap(True)
+        layer.set_grad_overlap(overlap_mode)
         grad_err = float(np.abs(reduced.astype(np.float64) - whole).max() / np.abs(whole).max()) if rank == 0 else None
         strong = dict(workload="the %s problem at GLOBAL batch %d split by (batch, head) units: %d units = %d token rows per GPU" %
                       (args.workload, B, u[1] - u[0], r1 - r0), global_batch=B, units_per_gpu=u[1] - u[0],

@@ -293,14 +293,29 @@ int launch(int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const vo
     return 0;
 }
 
+template <typename T, int BN>
+int dispatch_layout_bn(int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
+                       int64_t ldb, void* C, int64_t ldc, int out_type, const float* bias) {
+    // trans_a: A stored [K,M] (M-major).  trans_b == 0: B stored [K,N] (N-major).
+    if (!ta && !tb) return launch<T, false, true, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    if (!ta && tb) return launch<T, false, false, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    if (ta && !tb) return launch<T, true, true, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    return launch<T, true, false, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+}
+
 template <typename T>
 int dispatch_layout(int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
                     int64_t ldb, void* C, int64_t ldc, int out_type, const float* bias) {
-    // trans_a: A stored [K,M] (M-major).  trans_b == 0: B stored [K,N] (N-major).
-    if (!ta && !tb) return launch<T, false, true, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    if (!ta && tb) return launch<T, false, false, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    if (ta && !tb) return launch<T, true, true, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    return launch<T, true, false, 256>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    // 128 x 256 tiles by default.  A problem with fewer such tiles than SMs (and no long K to split
+    // instead) gets 128 x 128 tiles when those still fit in one wave: twice the CTAs at work, half
+    // the main loop per CTA.  (More narrow tiles than SMs would only add a second, partly empty wave.)
+    const int64_t tiles = ceil_div(M, BM) * ceil_div(N, 256);
+    const int64_t k_blocks = ceil_div(K, (int64_t)(128 / sizeof(T)));
+    const bool splits_k = out_type == BOAT_CUDA_F32 && tiles * 2 <= sm_count() && k_blocks >= 16;
+    const int64_t narrow_tiles = ceil_div(M, BM) * ceil_div(N, 128);
+    if (tiles < sm_count() && narrow_tiles <= sm_count() && !splits_k && N > 128)
+        return dispatch_layout_bn<T, 128>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    return dispatch_layout_bn<T, 256>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
 }
 
 }  // namespace

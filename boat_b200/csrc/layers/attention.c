@@ -35,7 +35,9 @@ struct boat_attention_t {
     boat_tensor_t* grad_bucket;         /* FP32, on `device`                       */
     boat_device_t  device;              /* where the parameters live               */
     int            precision;           /* -1 automatic, else BOAT_MMA_*           */
-    bool           grad_overlap;        /* backward starts the gradient sums itself */
+    int            grad_overlap;        /* 0: sums only in allreduce_grads; 1: backward starts both groups
+                                           itself; 2: backward starts dWo|dbo, the rest waits for allreduce_grads */
+    bool           rest_pending;        /* mode 2: dWq dWk dWv | dbq dbk dbv still to be summed */
 
     /* state of the last forward, consumed by backward */
     boat_tensor_t* cache_in[3];         /* query, key, value - referenced          */
@@ -753,7 +755,8 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     if (bias && boat_report("dbo", boat_cuda_colsum(d_go, type, T, H, d_db[WO])) != 0) goto done;
     /* Data parallel with overlap: dWo and dbo are final here, long before the step ends - their
      * sum over the ranks runs under the attention-core backward. */
-    const bool overlap = a->grad_overlap && a->device == BOAT_DEVICE_CUDA && boat_cuda_comm_world() > 1;
+    const bool overlap = a->grad_overlap != 0 && a->device == BOAT_DEVICE_CUDA && boat_cuda_comm_world() > 1;
+    a->rest_pending = false;
     if (overlap) {
         float* piece[2] = {d_dw[WO], d_db[WO]};
         const int64_t count[2] = {H * H, bias ? H : 0};
@@ -780,10 +783,12 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         if (boat_report("dW", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_in[i], H, d_dproj[i], H, type, d_dw[i], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
         if (bias && boat_report("db", boat_cuda_colsum(d_dproj[i], type, T, H, d_db[i])) != 0) goto done;
     }
-    if (overlap) {
+    if (overlap && a->grad_overlap == 1) {
         float* piece[2] = {d_dw[WQ], d_db[WQ]};            /* dWq|dWk|dWv and dbq|dbk|dbv are contiguous */
         const int64_t count[2] = {3 * H * H, bias ? 3 * H : 0};
         if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 2)) != 0) goto done;
+    } else if (overlap) {
+        a->rest_pending = true;
     }
     for (int i = 0; i < 3; ++i) {
         const boat_tensor_t* x = a->cache_in[i];
@@ -1026,15 +1031,25 @@ int boat_attention_grad_bucket(const boat_attention_t* a, float** data, size_t* 
     return 0;
 }
 
-int boat_attention_set_grad_overlap(boat_attention_t* a, int on) {
-    if (!a) return 1;
-    a->grad_overlap = on != 0;
+int boat_attention_set_grad_overlap(boat_attention_t* a, int mode) {
+    if (!a || mode < 0 || mode > 2) return 1;
+    a->grad_overlap = mode;
     return 0;
 }
 
 int boat_attention_allreduce_grads(boat_attention_t* a) {
     if (!a || !a->grad_bucket) return 1;
-    /* sums started by the backward itself: the library stream only has to wait for them */
+    /* sums started by the backward itself: the library stream only has to wait for them - after
+     * starting the group the backward left for now (mode 2) */
+    if (a->rest_pending) {
+        const int64_t H = (int64_t)a->config.hidden_size;
+        const bool bias = a->param[BQ] != NULL;
+        float* bucket = (float*)a->grad_bucket->data;
+        float* piece[2] = {bucket, bucket + 4 * H * H};
+        const int64_t count[2] = {3 * H * H, bias ? 3 * H : 0};
+        a->rest_pending = false;
+        if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 2)) != 0) return 3;
+    }
     if (boat_cuda_allreduce_pending()) return boat_report("gradient all-reduce", boat_cuda_allreduce_join());
     if (boat_cuda_comm_world() <= 1) return 0;
     if (a->device != BOAT_DEVICE_CUDA) {

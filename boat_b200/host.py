@@ -182,8 +182,8 @@ class Attention:
             return lib.boat_attention_load_safetensors(self.h, C.cast(buf, C.c_void_p), len(image), pre)
         return lib.boat_attention_load_safetensors_file(self.h, str(image).encode(), pre)
 
-    def set_grad_overlap(self, on=True):
-        if capi.load().boat_attention_set_grad_overlap(self.h, int(bool(on))):
+    def set_grad_overlap(self, mode=1):
+        if capi.load().boat_attention_set_grad_overlap(self.h, int(mode)):
             raise BoatError("boat_attention_set_grad_overlap failed")
 
     def allreduce_grads(self):

@@ -59,13 +59,16 @@ BOAT_API int boat_attention_grad_bucket(const boat_attention_t* attention, float
  * different slice of the batch).  No-op with a single rank.  Returns 0 on success. */
 BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
 
-/* Overlap that sum with the backward: with on != 0 (and a CUDA layer, more than one rank),
- * boat_attention_backward itself starts the sum of dWo | dbo as soon as the output projection's
- * gradients are final - it then runs under the attention-core backward - and the sum of
- * dWq dWk dWv | dbq dbk dbv before the three input-gradient GEMMs, on a communication stream.
- * boat_attention_allreduce_grads then only joins: call it, as before, after the backward and
- * before anything reads or updates the gradients.  Off by default. */
-BOAT_API int boat_attention_set_grad_overlap(boat_attention_t* attention, int on);
+/* Overlap that sum with the backward (a CUDA layer, more than one rank).  mode 0 (default): nothing
+ * is summed before boat_attention_allreduce_grads.  mode 1: boat_attention_backward itself starts,
+ * on a communication stream, the sum of dWo | dbo as soon as the output projection's gradients are
+ * final - it then runs under the attention-core backward - and the sum of dWq dWk dWv | dbq dbk dbv
+ * before the three input-gradient GEMMs.  mode 2: only the first of these is started by the
+ * backward; the second is started by boat_attention_allreduce_grads (persistent GEMM kernels that
+ * share the SMs with a running collective lose more than the collective costs alone).  In modes 1
+ * and 2 boat_attention_allreduce_grads joins the sums: call it, as before, after the backward and
+ * before anything reads or updates the gradients. */
+BOAT_API int boat_attention_set_grad_overlap(boat_attention_t* attention, int mode);
 
 /* Register the layer's parameters with an optimizer (boat/optimizers.h), each with its
  * gradient tensor.  The reference's layer makes new gradient tensors on every backward
