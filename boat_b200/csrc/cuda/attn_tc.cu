@@ -66,20 +66,9 @@ int attn_fwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float
 
 namespace {
 
-// out_lse2[i] = -lse[i] * log2(e), out_delta2[i] = -delta[i] * scale: the two per-row statistics in the
-// form the backward kernel's inner loops consume them (one FMA each), computed once per row here.
-__global__ void prescale_stats_kernel(const float* __restrict__ lse, const float* __restrict__ delta, float scale,
-                                      float* __restrict__ out_lse2, float* __restrict__ out_delta2, int64_t n) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) {
-        out_lse2[i] = lse[i] * -1.4426950408889634f;
-        out_delta2[i] = delta[i] * -scale;
-    }
-}
-
 template <int HS>
 int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q, const void* K, const void* V,
-               const void* dO, const float* lse, const float* delta, void* dQ, void* dK, void* dV, float* dq_accum,
+               const void* O, const void* dO, const float* lse, void* dQ, void* dK, void* dV, float* dq_accum,
                float* stats2) {
     using C = BwdCfg<HS>;
     CUtensorMap mq, mk, mv, mdo, mdq;
@@ -124,10 +113,13 @@ int launch_bwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
         configured = true;
     }
     {
+        // the per-row statistics in the form the kernel's inner loops consume them:
+        // -lse * log2(e) and -scale * rowsum(dO o O)
+        ProfileScope prof("attn_delta");
+        if (int rc = rowdot_stats(dO, O, BOAT_CUDA_BF16, (int64_t)rows, HS, lse, scale, stats2 + rows, stats2)) return rc;
+    }
+    {
         ProfileScope prof("attn_bwd_tc");
-        prescale_stats_kernel<<<(unsigned)ceil_div((int64_t)rows, 256), 256, 0, stream()>>>(lse, delta, scale, stats2, stats2 + rows,
-                                                                                            (int64_t)rows);
-        BOATCU_LAUNCH_OK("prescale_stats");
         BOATCU_CHECK(cudaMemsetAsync(dq_accum, 0, n * sizeof(float), stream()));
         const int64_t grid = units * (p.pair ? (S / kTile + 1) / 2 : S / kTile);
         kern<<<(unsigned)grid, kBwdThreads, C::SMEM, stream()>>>(mq, mk, mv, mdo, mdq, p);
@@ -191,16 +183,16 @@ size_t attn_bwd_tc_scratch_bytes(int mma, int64_t units, int64_t S, int64_t hs) 
 }
 
 int attn_bwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q, const void* K,
-                const void* V, const void* dO, const float* lse, const float* delta, int io_type, void* dQ, void* dK,
-                void* dV, void* scratch, size_t scratch_bytes) {
+                const void* V, const void* O, const void* dO, const float* lse, const float* delta, int io_type, void* dQ,
+                void* dK, void* dV, void* scratch, size_t scratch_bytes) {
     if (int rc = ensure_init()) return rc;
     if (mma == BOAT_MMA_BF16) {
         if (scratch_bytes < attn_bwd_tc_scratch_bytes(mma, units, S, hs))
             return set_error(12, "attention backward: scratch too small for the dQ accumulation buffer");
         float* stats2 = (float*)scratch + (size_t)units * (size_t)S * (size_t)hs;
         if (hs == 64)
-            return launch_bwd<64>(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV, (float*)scratch, stats2);
-        return launch_bwd<128>(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV, (float*)scratch, stats2);
+            return launch_bwd<64>(units, S, causal, scale, Q, K, V, O, dO, lse, dQ, dK, dV, (float*)scratch, stats2);
+        return launch_bwd<128>(units, S, causal, scale, Q, K, V, O, dO, lse, dQ, dK, dV, (float*)scratch, stats2);
     }
     (void)io_type;
     return launch_bwd_tf32(units, S, causal, scale, Q, K, V, dO, lse, delta, dQ, dK, dV);

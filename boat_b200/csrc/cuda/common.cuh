@@ -67,6 +67,10 @@ static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // out[r] = sum_d A[r,d]*B[r,d] over [rows, cols] row-major buffers of storage type `type`.
 int rowdot(const void* A, const void* B, int type, int64_t rows, int64_t cols, float* out);
+// The same pass emitting what the BF16 tensor-core backward reads per row:
+// delta2_out[r] = -scale * sum_d dO[r,d]*O[r,d] and lse2_out[r] = -lse[r] * log2(e).
+int rowdot_stats(const void* dO, const void* O, int type, int64_t rows, int64_t cols, const float* lse, float scale,
+                 float* delta2_out, float* lse2_out);
 
 // CUDA-core (exact FP32 accumulate) implementations, any shape.
 int gemm_simt(int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
@@ -84,5 +88,9 @@ bool gemm_tc_supported(int mma, int trans_a, int trans_b, int64_t M, int64_t N, 
                        int out_type);
 int gemm_tc(int mma, int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
             const void* B, int64_t ldb, int in_type, void* C, int64_t ldc, int out_type, const float* bias);
+// `groups` (1..4) problems of one shape, layout and type in one launch; bias may be NULL or hold NULLs.
+int gemm_tc_grouped(int mma, int trans_a, int trans_b, int groups, int64_t M, int64_t N, int64_t K,
+                    const void* const* A, int64_t lda, const void* const* B, int64_t ldb, void* const* C,
+                    int64_t ldc, int out_type, const float* const* bias);
 
 }  // namespace boatcu

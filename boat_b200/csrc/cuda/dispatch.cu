@@ -14,7 +14,7 @@ int attn_fwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float
                 const void* K, const void* V, int io_type, void* O, float* lse);
 size_t attn_bwd_tc_scratch_bytes(int mma, int64_t units, int64_t S, int64_t hs);
 int attn_bwd_tc(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q,
-                const void* K, const void* V, const void* dO, const float* lse, const float* delta,
+                const void* K, const void* V, const void* O, const void* dO, const float* lse, const float* delta,
                 int io_type, void* dQ, void* dK, void* dV, void* scratch, size_t scratch_bytes);
 }
 
@@ -45,6 +45,24 @@ int boat_cuda_gemm(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, con
     }
     ProfileScope prof("gemm_simt");
     return gemm_simt(ta, tb, M, N, K, A, lda, B, ldb, in_type, C, ldc, out_type, bias);
+}
+
+int boat_cuda_gemm_grouped(int mma, int ta, int tb, int groups, int64_t M, int64_t N, int64_t K, const void* const* A,
+                           int64_t lda, const void* const* B, int64_t ldb, int in_type, void* const* C, int64_t ldc,
+                           int out_type, const float* const* bias) {
+    if (groups < 1 || groups > 4) return set_error(11, "boat_cuda_gemm_grouped: %d groups (1 to 4)", groups);
+    if (!A || !B || !C) return set_error(11, "boat_cuda_gemm_grouped: NULL operand table");
+    if (int rc = check_types("boat_cuda_gemm_grouped", mma, in_type)) return rc;
+    const int store = in_type == BOAT_CUDA_F32_TF32 ? BOAT_CUDA_F32 : in_type;
+    bool one_launch = mma != BOAT_MMA_FP32 && out_type >= BOAT_CUDA_F32 && out_type <= BOAT_CUDA_F32_TF32 && M > 0 && N > 0 && K >= 0;
+    for (int g = 0; g < groups && one_launch; ++g)
+        one_launch = A[g] && B[g] && C[g] && gemm_tc_supported(mma, ta, tb, M, N, K, A[g], lda, B[g], ldb, store, C[g], ldc, out_type);
+    if (one_launch) return gemm_tc_grouped(mma, ta, tb, groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    // shapes the tensor-core kernel does not cover (or bad arguments, reported by the single call)
+    for (int g = 0; g < groups; ++g)
+        if (int rc = boat_cuda_gemm(mma, ta, tb, M, N, K, A[g], lda, B[g], ldb, in_type, C[g], ldc, out_type, bias ? bias[g] : nullptr))
+            return rc;
+    return 0;
 }
 
 int boat_cuda_attn_fwd(int mma, int64_t units, int64_t S, int64_t hs, int causal, float scale, const void* Q,
@@ -88,12 +106,13 @@ int boat_cuda_attn_bwd(int mma, int64_t units, int64_t S, int64_t hs, int causal
     if (((uintptr_t)scratch & 255) != 0) return set_error(12, "boat_cuda_attn_bwd: scratch must be 256-byte aligned");
     float* delta = (float*)scratch;
     size_t delta_bytes = ((size_t)units * (size_t)S * sizeof(float) + 255) & ~(size_t)255;
-    {
+    const bool tensor_cores = mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type);
+    if (!(tensor_cores && mma == BOAT_MMA_BF16)) {      // the BF16 kernel's launcher makes its own, pre-scaled
         ProfileScope prof("attn_delta");
         if (int rc = rowdot(dO, O, io_type, units * S, hs, delta)) return rc;
     }
-    if (mma != BOAT_MMA_FP32 && attn_tc_supported(mma, units, S, hs, io_type))
-        return attn_bwd_tc(mma, units, S, hs, causal, scale, Q, K, V, dO, lse, delta, io_type, dQ, dK, dV,
+    if (tensor_cores)
+        return attn_bwd_tc(mma, units, S, hs, causal, scale, Q, K, V, O, dO, lse, delta, io_type, dQ, dK, dV,
                            (char*)scratch + delta_bytes, scratch_bytes - delta_bytes);
     {
         ProfileScope prof("attn_bwd_simt");

@@ -189,11 +189,61 @@ __global__ void round_tf32_kernel(float* __restrict__ y, const float* __restrict
     }
 }
 
+// ---- several FP32 tensors to BF16 or to TF32-valued FP32, one launch ----------------------------
+constexpr int kMaxConvert = 8;
+struct ConvertTable {
+    const float* src[kMaxConvert];
+    void* dst[kMaxConvert];
+    int64_t n[kMaxConvert];
+};
+
+// blockIdx.y = tensor; vec: every tensor is 16-byte aligned with a multiple of 8 elements
+template <bool TO_BF16>
+__global__ void convert_multi_kernel(const ConvertTable t, int vec) {
+    const float* __restrict__ src = t.src[blockIdx.y];
+    const int64_t n = t.n[blockIdx.y];
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    if (vec) {
+        const int64_t n8 = n / 8;
+        for (; i < n8; i += step) {
+            const float4 a = reinterpret_cast<const float4*>(src)[2 * i];
+            const float4 b = reinterpret_cast<const float4*>(src)[2 * i + 1];
+            if (TO_BF16) {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+                uint4 o;
+                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                reinterpret_cast<uint4*>(t.dst[blockIdx.y])[i] = o;
+            } else {
+                float4* d = reinterpret_cast<float4*>(t.dst[blockIdx.y]);
+                d[2 * i] = make_float4(round_tf32(a.x), round_tf32(a.y), round_tf32(a.z), round_tf32(a.w));
+                d[2 * i + 1] = make_float4(round_tf32(b.x), round_tf32(b.y), round_tf32(b.z), round_tf32(b.w));
+            }
+        }
+    } else {
+        for (; i < n; i += step) {
+            if (TO_BF16) ((__nv_bfloat16*)t.dst[blockIdx.y])[i] = __float2bfloat16_rn(src[i]);
+            else         ((float*)t.dst[blockIdx.y])[i] = round_tf32(src[i]);
+        }
+    }
+}
+
 // ---- column sums: out[j] += sum_i X[i,j] -----------------------------------------------------
 // Block = 32 column lanes x 8 row lanes; a column lane owns VEC adjacent columns.  Row lanes
 // are combined through shared memory, blocks through atomicAdd into a zeroed output.
+// blockIdx.z selects one of several matrices of the same shape.
+constexpr int kMaxColsum = 4;
+struct ColsumTable {
+    const void* x[kMaxColsum];
+    float* out[kMaxColsum];
+};
+
 template <typename T, int VEC>
-__global__ void colsum_kernel(const T* __restrict__ X, int64_t rows, int64_t cols, float* __restrict__ out) {
+__global__ void colsum_kernel(const ColsumTable t, int64_t rows, int64_t cols) {
+    const T* __restrict__ X = (const T*)t.x[blockIdx.z];
+    float* __restrict__ out = t.out[blockIdx.z];
     __shared__ float part[8][32 * VEC + 1];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int64_t col0 = ((int64_t)blockIdx.x * 32 + tx) * VEC;
@@ -233,9 +283,25 @@ __global__ void colsum_kernel(const T* __restrict__ X, int64_t rows, int64_t col
 }
 
 // ---- delta[r] = sum_d dO[r,d] * O[r,d]: one warp per row, shuffle reduction --------------------
+// With `lse2_out` the kernel emits the two per-row statistics in the form the BF16 backward's inner
+// loops consume them (one FMA each): out[r] = -delta[r] * scale and lse2_out[r] = -lse[r] * log2(e).
+struct RowStats {
+    const float* lse;
+    float* lse2_out;
+    float scale;
+};
+__device__ __forceinline__ void emit_row(float* __restrict__ out, const RowStats& st, int64_t row, float s) {
+    if (st.lse2_out) {
+        out[row] = s * -st.scale;
+        st.lse2_out[row] = st.lse[row] * -1.4426950408889634f;
+    } else {
+        out[row] = s;
+    }
+}
+
 template <typename T>
 __global__ void rowdot_kernel(const T* __restrict__ A, const T* __restrict__ B, int64_t rows, int cols,
-                              float* __restrict__ out) {
+                              float* __restrict__ out, const RowStats st) {
     const int lane = threadIdx.x & 31;
     int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t step = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -246,14 +312,14 @@ __global__ void rowdot_kernel(const T* __restrict__ A, const T* __restrict__ B, 
         for (int d = lane; d < cols; d += 32) s += to_f32(a[d]) * to_f32(b[d]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) out[row] = s;
+        if (lane == 0) emit_row(out, st, row, s);
     }
 }
 
 // 128-bit variant: 8 bf16 (or 4 floats) per lane per access; cols must divide accordingly.
 template <typename T, int VEC>
 __global__ void rowdot_vec_kernel(const T* __restrict__ A, const T* __restrict__ B, int64_t rows, int cols,
-                                  float* __restrict__ out) {
+                                  float* __restrict__ out, const RowStats st) {
     const int lanes_per_row = cols / VEC;            // power of two <= 32 checked by the launcher
     const int rows_per_warp = 32 / lanes_per_row;
     const int lane = threadIdx.x & 31;
@@ -282,11 +348,11 @@ __global__ void rowdot_vec_kernel(const T* __restrict__ A, const T* __restrict__
             }
         }
         for (int o = lanes_per_row >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (l == 0 && row < rows) out[row] = s;
+        if (l == 0 && row < rows) emit_row(out, st, row, s);
     }
 }
 
-int rowdot(const void* A, const void* B, int type, int64_t rows, int64_t cols, float* out) {
+static int rowdot_launch(const void* A, const void* B, int type, int64_t rows, int64_t cols, float* out, const RowStats st) {
     if (rows <= 0) return 0;
     if (int rc = ensure_init()) return rc;
     const int vec = type == BOAT_CUDA_BF16 ? 8 : 4;
@@ -297,19 +363,28 @@ int rowdot(const void* A, const void* B, int type, int64_t rows, int64_t cols, f
         int grid = grid_for(rows, rows_per_block);
         if (type == BOAT_CUDA_BF16)
             rowdot_vec_kernel<__nv_bfloat16, 8><<<grid, kThreads, 0, stream()>>>(
-                (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, rows, (int)cols, out);
+                (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, rows, (int)cols, out, st);
         else
-            rowdot_vec_kernel<float, 4><<<grid, kThreads, 0, stream()>>>((const float*)A, (const float*)B, rows, (int)cols, out);
+            rowdot_vec_kernel<float, 4><<<grid, kThreads, 0, stream()>>>((const float*)A, (const float*)B, rows, (int)cols, out, st);
     } else {
         int grid = grid_for(rows, kThreads / 32);
         if (type == BOAT_CUDA_BF16)
             rowdot_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream()>>>(
-                (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, rows, (int)cols, out);
+                (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, rows, (int)cols, out, st);
         else
-            rowdot_kernel<float><<<grid, kThreads, 0, stream()>>>((const float*)A, (const float*)B, rows, (int)cols, out);
+            rowdot_kernel<float><<<grid, kThreads, 0, stream()>>>((const float*)A, (const float*)B, rows, (int)cols, out, st);
     }
     BOATCU_LAUNCH_OK("rowdot");
     return 0;
+}
+
+int rowdot(const void* A, const void* B, int type, int64_t rows, int64_t cols, float* out) {
+    return rowdot_launch(A, B, type, rows, cols, out, RowStats{nullptr, nullptr, 0.f});
+}
+
+int rowdot_stats(const void* dO, const void* O, int type, int64_t rows, int64_t cols, const float* lse, float scale,
+                 float* delta2_out, float* lse2_out) {
+    return rowdot_launch(dO, O, type, rows, cols, delta2_out, RowStats{lse, lse2_out, scale});
 }
 
 // ---- out[b, j, i] = in[b, i, j], 32x32 shared-memory tiles --------------------------------------
@@ -399,28 +474,81 @@ int boat_cuda_round_tf32(float* y, const float* x, int64_t n) {
     return 0;
 }
 
-int boat_cuda_colsum(const void* X, int x_type, int64_t rows, int64_t cols, float* out) {
-    if (cols <= 0) return 0;
+int boat_cuda_colsum_multi(const void* const* X, int x_type, int64_t rows, int64_t cols, float* const* out, int count) {
+    if (cols <= 0 || count <= 0) return 0;
+    if (count > kMaxColsum) return set_error(11, "boat_cuda_colsum_multi: %d matrices (1 to %d)", count, kMaxColsum);
+    if (!X || !out) return set_error(11, "boat_cuda_colsum_multi: NULL table");
     if (int rc = ensure_init()) return rc;
     ProfileScope prof("colsum");
-    BOATCU_CHECK(cudaMemsetAsync(out, 0, (size_t)cols * sizeof(float), stream()));
-    if (rows <= 0) return 0;
+    ColsumTable t;
     const int vec = x_type == BOAT_CUDA_BF16 ? 8 : 4;
-    const bool can_vec = (cols % vec) == 0 && aligned16(X);
+    bool can_vec = (cols % vec) == 0;
+    for (int i = 0; i < kMaxColsum; ++i) {
+        const int s = i < count ? i : 0;
+        if (!X[s] || !out[s]) return set_error(11, "boat_cuda_colsum_multi: NULL operand");
+        t.x[i] = X[s];
+        t.out[i] = out[s];
+        can_vec = can_vec && aligned16(X[s]);
+    }
+    for (int i = 0; i < count; ++i) {
+        // outputs that follow one another in memory (the layer's gradient bucket) are cleared together
+        int j = i;
+        while (j + 1 < count && out[j + 1] == out[j] + cols) ++j;
+        BOATCU_CHECK(cudaMemsetAsync(out[i], 0, (size_t)(j - i + 1) * (size_t)cols * sizeof(float), stream()));
+        i = j;
+    }
+    if (rows <= 0) return 0;
     const int cols_per_block = 32 * (can_vec ? vec : 1);
-    dim3 grid((unsigned)ceil_div(cols, cols_per_block), 1, 1);
-    int64_t want = (int64_t)sm_count() * 8 / grid.x;
+    dim3 grid((unsigned)ceil_div(cols, cols_per_block), 1, (unsigned)count);
+    int64_t want = (int64_t)sm_count() * 8 / ((int64_t)grid.x * count);
     int64_t max_y = ceil_div(rows, 8);
     grid.y = (unsigned)(want < 1 ? 1 : (want > max_y ? max_y : want));
     if (grid.y > 65535) grid.y = 65535;
     if (x_type == BOAT_CUDA_BF16) {
-        if (can_vec) colsum_kernel<__nv_bfloat16, 8><<<grid, kThreads, 0, stream()>>>((const __nv_bfloat16*)X, rows, cols, out);
-        else         colsum_kernel<__nv_bfloat16, 1><<<grid, kThreads, 0, stream()>>>((const __nv_bfloat16*)X, rows, cols, out);
+        if (can_vec) colsum_kernel<__nv_bfloat16, 8><<<grid, kThreads, 0, stream()>>>(t, rows, cols);
+        else         colsum_kernel<__nv_bfloat16, 1><<<grid, kThreads, 0, stream()>>>(t, rows, cols);
     } else {
-        if (can_vec) colsum_kernel<float, 4><<<grid, kThreads, 0, stream()>>>((const float*)X, rows, cols, out);
-        else         colsum_kernel<float, 1><<<grid, kThreads, 0, stream()>>>((const float*)X, rows, cols, out);
+        if (can_vec) colsum_kernel<float, 4><<<grid, kThreads, 0, stream()>>>(t, rows, cols);
+        else         colsum_kernel<float, 1><<<grid, kThreads, 0, stream()>>>(t, rows, cols);
     }
     BOATCU_LAUNCH_OK("colsum");
+    return 0;
+}
+
+int boat_cuda_colsum(const void* X, int x_type, int64_t rows, int64_t cols, float* out) {
+    if (cols <= 0) return 0;
+    return boat_cuda_colsum_multi(&X, x_type, rows, cols, &out, 1);
+}
+
+int boat_cuda_convert_multi(void* const* dst, int dst_type, const float* const* src, const int64_t* n, int count) {
+    if (count <= 0) return 0;
+    if (count > kMaxConvert) return set_error(11, "boat_cuda_convert_multi: %d tensors (1 to %d)", count, kMaxConvert);
+    if (dst_type != BOAT_CUDA_BF16 && dst_type != BOAT_CUDA_F32_TF32)
+        return set_error(10, "boat_cuda_convert_multi: target type %d (BF16 or TF32-valued FP32)", dst_type);
+    if (!dst || !src || !n) return set_error(11, "boat_cuda_convert_multi: NULL table");
+    if (int rc = ensure_init()) return rc;
+    ConvertTable t;
+    int vec = 1;
+    int64_t longest = 0;
+    for (int i = 0; i < kMaxConvert; ++i) {
+        const int s = i < count ? i : 0;
+        if (n[s] < 0 || (n[s] > 0 && (!dst[s] || !src[s]))) return set_error(11, "boat_cuda_convert_multi: bad entry %d", s);
+        t.src[i] = src[s];
+        t.dst[i] = dst[s];
+        t.n[i] = n[s];
+        vec = vec && aligned16(dst[s]) && aligned16(src[s]) && (n[s] % 8) == 0;
+        if (n[s] > longest) longest = n[s];
+    }
+    if (longest == 0) return 0;
+    // the blocks of all tensors together fill the GPU a few times over
+    int64_t per_tensor = ceil_div(vec ? longest / 8 : longest, kThreads);
+    const int64_t cap = ceil_div((int64_t)sm_count() * 16, count);
+    if (per_tensor > cap) per_tensor = cap;
+    dim3 grid((unsigned)per_tensor, (unsigned)count, 1);
+    ProfileScope prof("cast");
+    if (dst_type == BOAT_CUDA_BF16) convert_multi_kernel<true><<<grid, kThreads, 0, stream()>>>(t, vec);
+    else                            convert_multi_kernel<false><<<grid, kThreads, 0, stream()>>>(t, vec);
+    BOATCU_LAUNCH_OK("convert_multi");
     return 0;
 }
 

@@ -20,6 +20,11 @@
 // accumulator is double-buffered in tensor memory (2 x BN columns) so that the epilogue of one
 // tile overlaps the main loop of the next.  Weight gradients have few output tiles and a
 // very long K: they are split along K over several CTAs that add into a zeroed output.
+//
+// Up to kMaxGroups problems of one shape and layout (the Q, K and V projections of a layer, their
+// weight gradients, their input gradients) run as one launch: the persistent CTAs walk the tiles of
+// all groups, group index fastest, so CTAs at work at the same time read the operand the groups
+// share (X for self-attention) from L2.
 #include "tc_common.cuh"
 
 namespace boatcu {
@@ -44,9 +49,16 @@ struct Cfg {
     static constexpr uint32_t TMEM_COLS = 2 * BN;   // two accumulators
 };
 
+constexpr int kMaxGroups = 4;
+
+struct GroupMaps {
+    CUtensorMap a[kMaxGroups], b[kMaxGroups];
+};
+
 struct Params {
-    void* C;
-    const float* bias;
+    void* C[kMaxGroups];
+    const float* bias[kMaxGroups];
+    int groups;
     int64_t ldc;
     int M, N, K;
     int out_type;
@@ -56,7 +68,7 @@ struct Params {
 
 template <typename T, bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+gemm_tc_kernel(const __grid_constant__ GroupMaps maps, const Params p) {
     using C = Cfg<T, BN>;
     constexpr bool TF32 = sizeof(T) == 4;
     extern __shared__ uint8_t smem_raw[];
@@ -73,7 +85,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (p.M + BM - 1) / BM, n_tiles = (p.N + BN - 1) / BN;
     const int k_blocks = (p.K + C::BK - 1) / C::BK;
-    const int work_items = m_tiles * n_tiles * p.split_k;
+    const int work_items = m_tiles * n_tiles * p.groups * p.split_k;      // w = ((tile * groups) + g) * split_k + split
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -85,8 +97,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(&acc_empty[b], 128);
         }
         fence_barrier_init();
-        tma_prefetch_desc(&map_a);
-        tma_prefetch_desc(&map_b);
+        for (int g = 0; g < p.groups; ++g) {
+            tma_prefetch_desc(&maps.a[g]);
+            tma_prefetch_desc(&maps.b[g]);
+        }
     }
     if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
     tc_fence_before_sync();
@@ -100,7 +114,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t it = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
-                const int tile = w / p.split_k, split = w % p.split_k;
+                const int split = w % p.split_k, gt = w / p.split_k;
+                const int g = gt % p.groups, tile = gt / p.groups;
+                const CUtensorMap* map_a = &maps.a[g];
+                const CUtensorMap* map_b = &maps.b[g];
                 const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
                 const int kb0 = (int)((int64_t)split * k_blocks / p.split_k);
                 const int kb1 = (int)((int64_t)(split + 1) * k_blocks / p.split_k);
@@ -113,15 +130,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     uint8_t* b_dst = b_smem + s * C::B_BYTES;
                     if (A_MN) {
                         for (int c = 0; c < BM / C::BK; ++c)
-                            tma_load_2d(a_dst + c * C::CHUNK_BYTES, &map_a, &full[s], m0 + c * C::BK, k0);
+                            tma_load_2d(a_dst + c * C::CHUNK_BYTES, map_a, &full[s], m0 + c * C::BK, k0);
                     } else {
-                        tma_load_2d(a_dst, &map_a, &full[s], k0, m0);
+                        tma_load_2d(a_dst, map_a, &full[s], k0, m0);
                     }
                     if (B_MN) {
                         for (int c = 0; c < BN / C::BK; ++c)
-                            tma_load_2d(b_dst + c * C::CHUNK_BYTES, &map_b, &full[s], n0 + c * C::BK, k0);
+                            tma_load_2d(b_dst + c * C::CHUNK_BYTES, map_b, &full[s], n0 + c * C::BK, k0);
                     } else {
-                        tma_load_2d(b_dst, &map_b, &full[s], k0, n0);
+                        tma_load_2d(b_dst, map_b, &full[s], k0, n0);
                     }
                 }
             }
@@ -169,14 +186,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t acc_it = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x, ++acc_it) {
-            const int tile = w / p.split_k, split = w % p.split_k;
+            const int split = w % p.split_k, gt = w / p.split_k;
+            const int g = gt % p.groups, tile = gt / p.groups;
             const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+            void* const out = p.C[g];
+            const float* const bias = p.bias[g];
             const int buf = acc_it & 1;
             if (!mbar_wait(&acc_full[buf], (acc_it >> 1) & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
             tc_fence_after_sync();
             const int row = m0 + lane_group * 32 + lane;
             const uint32_t t_addr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + buf * BN;
-            const bool add_bias = p.bias != nullptr && split == 0;
+            const bool add_bias = bias != nullptr && split == 0;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
@@ -190,10 +210,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (add_bias) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.N) v[j] += __ldg(p.bias + col0 + j);
+                            if (col0 + j < p.N) v[j] += __ldg(bias + col0 + j);
                     }
                     if (p.split_k > 1) {
-                        float* dst = (float*)p.C + (int64_t)row * p.ldc + col0;
+                        float* dst = (float*)out + (int64_t)row * p.ldc + col0;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (col0 + j < p.N) atomicAdd(dst + j, v[j]);
@@ -202,13 +222,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = round_to_tf32(v[j]);
                         }
-                        float* dst = (float*)p.C + (int64_t)row * p.ldc + col0;
+                        float* dst = (float*)out + (int64_t)row * p.ldc + col0;
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
                             if (col0 + j < p.N)       // N is a multiple of 4 on this path
                                 *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                     } else {
-                        __nv_bfloat16* dst = (__nv_bfloat16*)p.C + (int64_t)row * p.ldc + col0;
+                        __nv_bfloat16* dst = (__nv_bfloat16*)out + (int64_t)row * p.ldc + col0;
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             if (col0 + j < p.N) {     // N is a multiple of 8 on this path
@@ -240,38 +260,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 template <typename T, bool A_MN, bool B_MN, int BN>
-int launch(int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B, int64_t ldb, void* Cp,
-           int64_t ldc, int out_type, const float* bias) {
+int launch(int groups, int64_t M, int64_t N, int64_t K, const void* const* A, int64_t lda, const void* const* B,
+           int64_t ldb, void* const* Cp, int64_t ldc, int out_type, const float* const* bias, int split_k) {
     using C = Cfg<T, BN>;
-    CUtensorMap map_a, map_b;
-    // A: K-major -> matrix [M rows, K cols], box [BM, BK].  M-major -> stored [K rows, M cols], box [BK, BK].
-    if (int rc = A_MN ? make_tensor_map_2d(&map_a, A, C::ES, (uint64_t)K, (uint64_t)M, (uint64_t)lda, C::BK, C::BK, C::ES == 4)
-                      : make_tensor_map_2d(&map_a, A, C::ES, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, C::BK))
-        return rc;
-    if (int rc = B_MN ? make_tensor_map_2d(&map_b, B, C::ES, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, C::BK, C::BK, C::ES == 4)
-                      : make_tensor_map_2d(&map_b, B, C::ES, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, C::BK))
-        return rc;
-    const int m_tiles = (int)ceil_div(M, BM), n_tiles = (int)ceil_div(N, BN);
-    const int k_blocks = (int)ceil_div(K, C::BK);
-    const int tiles = m_tiles * n_tiles;
-    const int kSMs = sm_count();
-    int split_k = 1;
-    if (out_type == BOAT_CUDA_F32 && tiles * 2 <= kSMs) {
-        // few output tiles (weight gradients): spread K over the idle SMs, at least 8 K-blocks each
-        split_k = kSMs / tiles;
-        if (split_k > k_blocks / 8) split_k = k_blocks / 8;
-        if (split_k < 1) split_k = 1;
+    GroupMaps maps;
+    Params p;
+    for (int g = 0; g < kMaxGroups; ++g) {
+        const int s = g < groups ? g : 0;       // unused slots repeat group 0: valid descriptors, never walked
+        // A: K-major -> matrix [M rows, K cols], box [BM, BK].  M-major -> stored [K rows, M cols], box [BK, BK].
+        if (int rc = A_MN ? make_tensor_map_2d(&maps.a[g], A[s], C::ES, (uint64_t)K, (uint64_t)M, (uint64_t)lda, C::BK, C::BK, C::ES == 4)
+                          : make_tensor_map_2d(&maps.a[g], A[s], C::ES, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, C::BK))
+            return rc;
+        if (int rc = B_MN ? make_tensor_map_2d(&maps.b[g], B[s], C::ES, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, C::BK, C::BK, C::ES == 4)
+                          : make_tensor_map_2d(&maps.b[g], B[s], C::ES, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, C::BK))
+            return rc;
+        p.C[g] = Cp[s];
+        p.bias[g] = bias ? bias[s] : nullptr;
     }
+    const int tiles = (int)(ceil_div(M, BM) * ceil_div(N, BN)) * groups;
     if (split_k > 1) {
-        if (ldc == N) {
-            BOATCU_CHECK(cudaMemsetAsync(Cp, 0, (size_t)M * N * sizeof(float), stream()));
-        } else {
-            BOATCU_CHECK(cudaMemset2DAsync(Cp, (size_t)ldc * sizeof(float), 0, (size_t)N * sizeof(float), (size_t)M, stream()));
+        for (int g = 0; g < groups; ++g) {
+            if (ldc == N) {
+                BOATCU_CHECK(cudaMemsetAsync(Cp[g], 0, (size_t)M * N * sizeof(float), stream()));
+            } else {
+                BOATCU_CHECK(cudaMemset2DAsync(Cp[g], (size_t)ldc * sizeof(float), 0, (size_t)N * sizeof(float), (size_t)M, stream()));
+            }
         }
     }
-    Params p;
-    p.C = Cp;
-    p.bias = bias;
+    p.groups = groups;
     p.ldc = ldc;
     p.M = (int)M;
     p.N = (int)N;
@@ -285,37 +301,47 @@ int launch(int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const vo
         BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
-    int work = tiles * split_k;
-    int grid = work < kSMs ? work : kSMs;
+    const int work = tiles * split_k;
+    const int grid = work < sm_count() ? work : sm_count();
     ProfileScope prof(A_MN ? "gemm_tc_tn" : (B_MN ? "gemm_tc_nn" : "gemm_tc_nt"));
-    kern<<<grid, kThreads, C::SMEM, stream()>>>(map_a, map_b, p);
+    kern<<<grid, kThreads, C::SMEM, stream()>>>(maps, p);
     BOATCU_LAUNCH_OK("gemm_tc");
     return 0;
 }
 
 template <typename T, int BN>
-int dispatch_layout_bn(int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
-                       int64_t ldb, void* C, int64_t ldc, int out_type, const float* bias) {
+int dispatch_layout_bn(int ta, int tb, int groups, int64_t M, int64_t N, int64_t K, const void* const* A, int64_t lda,
+                       const void* const* B, int64_t ldb, void* const* C, int64_t ldc, int out_type,
+                       const float* const* bias, int split_k) {
     // trans_a: A stored [K,M] (M-major).  trans_b == 0: B stored [K,N] (N-major).
-    if (!ta && !tb) return launch<T, false, true, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    if (!ta && tb) return launch<T, false, false, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    if (ta && !tb) return launch<T, true, true, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    return launch<T, true, false, BN>(M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    if (!ta && !tb) return launch<T, false, true, BN>(groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias, split_k);
+    if (!ta && tb) return launch<T, false, false, BN>(groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias, split_k);
+    if (ta && !tb) return launch<T, true, true, BN>(groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias, split_k);
+    return launch<T, true, false, BN>(groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias, split_k);
 }
 
 template <typename T>
-int dispatch_layout(int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
-                    int64_t ldb, void* C, int64_t ldc, int out_type, const float* bias) {
+int dispatch_layout(int ta, int tb, int groups, int64_t M, int64_t N, int64_t K, const void* const* A, int64_t lda,
+                    const void* const* B, int64_t ldb, void* const* C, int64_t ldc, int out_type,
+                    const float* const* bias) {
+    const int64_t sms = sm_count();
+    const int64_t tiles = ceil_div(M, BM) * ceil_div(N, 256) * groups;
+    const int64_t k_blocks = ceil_div(K, (int64_t)(128 / sizeof(T)));
+    // Few output tiles and a long K (weight gradients): spread K over the idle SMs, at least 8
+    // K-blocks per piece; the pieces add into a zeroed FP32 output.
+    int64_t split_k = 1;
+    if (out_type == BOAT_CUDA_F32 && tiles * 2 <= sms) {
+        split_k = sms / tiles;
+        if (split_k > k_blocks / 8) split_k = k_blocks / 8;
+        if (split_k < 1) split_k = 1;
+    }
     // 128 x 256 tiles by default.  A problem with fewer such tiles than SMs (and no long K to split
     // instead) gets 128 x 128 tiles when those still fit in one wave: twice the CTAs at work, half
     // the main loop per CTA.  (More narrow tiles than SMs would only add a second, partly empty wave.)
-    const int64_t tiles = ceil_div(M, BM) * ceil_div(N, 256);
-    const int64_t k_blocks = ceil_div(K, (int64_t)(128 / sizeof(T)));
-    const bool splits_k = out_type == BOAT_CUDA_F32 && tiles * 2 <= sm_count() && k_blocks >= 16;
-    const int64_t narrow_tiles = ceil_div(M, BM) * ceil_div(N, 128);
-    if (tiles < sm_count() && narrow_tiles <= sm_count() && !splits_k && N > 128)
-        return dispatch_layout_bn<T, 128>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    return dispatch_layout_bn<T, 256>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    const int64_t narrow_tiles = ceil_div(M, BM) * ceil_div(N, 128) * groups;
+    if (tiles < sms && narrow_tiles <= sms && split_k == 1 && N > 128)
+        return dispatch_layout_bn<T, 128>(ta, tb, groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias, 1);
+    return dispatch_layout_bn<T, 256>(ta, tb, groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias, (int)split_k);
 }
 
 }  // namespace
@@ -336,13 +362,20 @@ bool gemm_tc_supported(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K,
     return true;
 }
 
+int gemm_tc_grouped(int mma, int ta, int tb, int groups, int64_t M, int64_t N, int64_t K, const void* const* A,
+                    int64_t lda, const void* const* B, int64_t ldb, void* const* C, int64_t ldc, int out_type,
+                    const float* const* bias) {
+    if (groups < 1 || groups > kMaxGroups) return set_error(11, "gemm_tc_grouped: %d groups (1..%d)", groups, kMaxGroups);
+    if (int rc = ensure_init()) return rc;
+    if (mma == BOAT_MMA_BF16)
+        return dispatch_layout<__nv_bfloat16>(ta, tb, groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    return dispatch_layout<float>(ta, tb, groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+}
+
 int gemm_tc(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
             int64_t ldb, int in_type, void* C, int64_t ldc, int out_type, const float* bias) {
     (void)in_type;
-    if (int rc = ensure_init()) return rc;
-    if (mma == BOAT_MMA_BF16)
-        return dispatch_layout<__nv_bfloat16>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
-    return dispatch_layout<float>(ta, tb, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
+    return gemm_tc_grouped(mma, ta, tb, 1, M, N, K, &A, lda, &B, ldb, &C, ldc, out_type, &bias);
 }
 
 }  // namespace boatcu

@@ -53,6 +53,15 @@ struct boat_attention_t {
     void*          d_proj[3];           /* Qp, Kp, Vp [B*S, H]                     */
     void*          d_ctx;               /* attention output before Wo              */
     float*         d_lse;               /* [B*nh*S]                                */
+
+    /* The four FP32 weights of a CUDA layer in the form the tensor cores read (BF16, or TF32-valued
+     * FP32), made by one launch in forward and used again by the backward of the same step.
+     * `shadow_fresh` holds only from a forward to the end of the next backward, and every call
+     * that hands out or changes a weight clears it; a caller that overwrites a weight through a
+     * raw device pointer between forward and backward is not seen. */
+    void*          shadow_w;            /* 4 * H * H elements                      */
+    int            shadow_form;         /* BOAT_CUDA_BF16 or BOAT_CUDA_F32_TF32    */
+    bool           shadow_fresh;
 };
 
 /* ---- small helpers ---------------------------------------------------------------------- */
@@ -220,10 +229,48 @@ static void release_params(staged_params_t* p) {
     memset(p, 0, sizeof *p);
 }
 
-static bool stage_params(const boat_attention_t* a, int mma, int type, staged_params_t* p) {
-    memset(p, 0, sizeof *p);
+/* The weights of a CUDA layer as tensor-core operands, from the layer's shadow block: converted
+ * by one launch, or - in the backward that follows a forward - not at all. */
+static bool shadow_weights(boat_attention_t* a, int form, bool backward, staged_params_t* p) {
+    const size_t H = a->config.hidden_size, n = H * H, es = form == BOAT_CUDA_BF16 ? 2 : 4;
+    if (a->shadow_w && a->shadow_form != form) {
+        dev_free(a->shadow_w);
+        a->shadow_w = NULL;
+    }
+    if (!a->shadow_w) {
+        a->shadow_w = dev_alloc(4 * n * es);
+        if (!a->shadow_w) return false;
+        a->shadow_form = form;
+        a->shadow_fresh = false;
+    }
+    void* dst[4];
+    const float* src[4];
+    int64_t count[4];
     for (int i = 0; i < 4; ++i) {
-        p->w[i] = stage_operand(a->param[WQ + i], mma, type, &p->w_owned[i]);
+        dst[i] = (char*)a->shadow_w + (size_t)i * n * es;
+        src[i] = (const float*)a->param[WQ + i]->data;
+        count[i] = (int64_t)n;
+        p->w[i] = dst[i];
+        p->w_owned[i] = false;
+    }
+    if (backward && a->shadow_fresh) return true;
+    a->shadow_fresh = false;
+    if (boat_report("weight conversion", boat_cuda_convert_multi(dst, form, src, count, 4)) != 0) return false;
+    a->shadow_fresh = !backward;
+    return true;
+}
+
+static bool stage_params(boat_attention_t* a, int mma, int type, bool backward, staged_params_t* p) {
+    memset(p, 0, sizeof *p);
+    bool shadow = a->device == BOAT_DEVICE_CUDA && (type == BOAT_CUDA_BF16 || mma == BOAT_MMA_TF32);
+    for (int i = 0; i < 4 && shadow; ++i) {
+        const boat_tensor_t* w = a->param[WQ + i];
+        shadow = w->device == BOAT_DEVICE_CUDA && w->dtype == BOAT_DTYPE_FLOAT32 &&
+                 w->nelements == a->config.hidden_size * a->config.hidden_size;
+    }
+    if (shadow && !shadow_weights(a, mma == BOAT_MMA_TF32 ? BOAT_CUDA_F32_TF32 : BOAT_CUDA_BF16, backward, p)) return false;
+    for (int i = 0; i < 4; ++i) {
+        if (!shadow) p->w[i] = stage_operand(a->param[WQ + i], mma, type, &p->w_owned[i]);
         if (!p->w[i]) goto fail;
         if (a->param[BQ + i]) {
             p->b[i] = (float*)stage_in(a->param[BQ + i], BOAT_CUDA_F32, &p->b_owned[i]);
@@ -501,9 +548,16 @@ fail:
     return NULL;
 }
 
+static void drop_shadow(boat_attention_t* a) {
+    dev_free(a->shadow_w);
+    a->shadow_w = NULL;
+    a->shadow_fresh = false;
+}
+
 void boat_attention_free(boat_attention_t* a) {
     if (!a) return;
     drop_forward_state(a);
+    drop_shadow(a);
     for (int i = 0; i < NPARAM; ++i) {
         if (a->param[i]) boat_tensor_free(a->param[i]);
         if (a->grad[i]) boat_tensor_free(a->grad[i]);
@@ -545,7 +599,7 @@ static boat_tensor_t* forward_rows(boat_attention_t* a, const boat_tensor_t* que
     /* host parameters of a chunked call go up on the upload stream, ahead of the first chunk,
      * without blocking the host between them */
     g_async_uploads = pipelined;
-    const bool staged = stage_params(a, mma, type, &p);
+    const bool staged = stage_params(a, mma, type, false, &p);
     g_async_uploads = false;
     if (!staged) {
         if (pipelined) boat_cuda_sync();        /* uploads already under way still read host memory */
@@ -572,10 +626,12 @@ static boat_tensor_t* forward_rows(boat_attention_t* a, const boat_tensor_t* que
     for (int i = 0; i < 3; ++i) {
         a->d_proj[i] = dev_alloc(act_bytes);
         if (!a->d_proj[i]) goto done;
-        if (boat_report("projection", boat_cuda_gemm(mma, 0, 0, T, H, H, a->d_in[i], H, p.w[i], H, type,
-                                                     a->d_proj[i], H, feed_type(mma, type), p.b[i])) != 0)
-            goto done;
     }
+    /* the three projections (attention.c:363-365) as one launch */
+    if (boat_report("projections", boat_cuda_gemm_grouped(mma, 0, 0, 3, T, H, H, (const void* const*)a->d_in, H,
+                                                          (const void* const*)p.w, H, type, a->d_proj, H,
+                                                          feed_type(mma, type), (const float* const*)p.b)) != 0)
+        goto done;
     a->d_ctx = dev_alloc(act_bytes);
     a->d_lse = (float*)dev_alloc((size_t)units * S * sizeof(float));
     if (!a->d_ctx || !a->d_lse) goto done;
@@ -724,7 +780,8 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     const bool pipelined = units / a->gran >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) &&
                            on_host(a->cache_in[1]) && on_host(a->cache_in[2]);
     g_async_uploads = pipelined;
-    const bool staged = stage_params(a, mma, type, &p);
+    const bool staged = stage_params(a, mma, type, true, &p);
+    a->shadow_fresh = false;                    /* one backward per forward may trust the forward's copies */
     g_async_uploads = false;
     if (!staged) {
         if (pipelined) boat_cuda_sync();        /* uploads already under way still read host memory */
@@ -779,10 +836,11 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
 
     /* input projections: dW = X^T . dP and db = colsum(dP) first - with overlap their sum over
      * the ranks then runs under the three dX = dP . W^T GEMMs that follow */
-    for (int i = 0; i < 3; ++i) {
-        if (boat_report("dW", boat_cuda_gemm(mma, 1, 0, H, H, T, a->d_in[i], H, d_dproj[i], H, type, d_dw[i], H, BOAT_CUDA_F32, NULL)) != 0) goto done;
-        if (bias && boat_report("db", boat_cuda_colsum(d_dproj[i], type, T, H, d_db[i])) != 0) goto done;
-    }
+    if (boat_report("dW", boat_cuda_gemm_grouped(mma, 1, 0, 3, H, H, T, (const void* const*)a->d_in, H,
+                                                 (const void* const*)d_dproj, H, type, (void* const*)d_dw, H,
+                                                 BOAT_CUDA_F32, NULL)) != 0)
+        goto done;
+    if (bias && boat_report("db", boat_cuda_colsum_multi((const void* const*)d_dproj, type, T, H, d_db, 3)) != 0) goto done;
     if (overlap && a->grad_overlap == 1) {
         float* piece[2] = {d_dw[WQ], d_db[WQ]};            /* dWq|dWk|dWv and dbq|dbk|dbv are contiguous */
         const int64_t count[2] = {3 * H * H, bias ? 3 * H : 0};
@@ -790,26 +848,47 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     } else if (overlap) {
         a->rest_pending = true;
     }
-    for (int i = 0; i < 3; ++i) {
-        const boat_tensor_t* x = a->cache_in[i];
-        int out_type = storage_of(x->dtype);
-        void* dx_target;
-        if (x->device == BOAT_DEVICE_CUDA) {
-            /* a CUDA gradient is the GEMM's own output buffer: no copy */
-            gin[i] = boat_tensor_create_uninit(x->shape, x->ndim, x->dtype, BOAT_DEVICE_CUDA);
-            if (!gin[i]) goto done;
-            dx_target = gin[i]->data;
+    {
+        /* dX = dP . W^T for the three inputs: one launch when they share device and dtype */
+        const boat_tensor_t* x0 = a->cache_in[0];
+        bool together = x0->device == BOAT_DEVICE_CUDA;
+        for (int i = 1; i < 3; ++i)
+            together = together && a->cache_in[i]->device == BOAT_DEVICE_CUDA && a->cache_in[i]->dtype == x0->dtype;
+        if (together) {
+            void* target[3];
+            for (int i = 0; i < 3; ++i) {
+                const boat_tensor_t* x = a->cache_in[i];
+                /* a CUDA gradient is the GEMM's own output buffer: no copy */
+                gin[i] = boat_tensor_create_uninit(x->shape, x->ndim, x->dtype, BOAT_DEVICE_CUDA);
+                if (!gin[i]) goto done;
+                target[i] = gin[i]->data;
+            }
+            if (boat_report("dX", boat_cuda_gemm_grouped(mma, 0, 1, 3, T, H, H, (const void* const*)d_dproj, H,
+                                                         (const void* const*)p.w, H, type, target, H,
+                                                         storage_of(x0->dtype), NULL)) != 0)
+                goto done;
         } else {
-            d_dx = dev_alloc((size_t)T * H * storage_size(out_type));
-            if (!d_dx) goto done;
-            dx_target = d_dx;
-        }
-        if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, T, H, H, d_dproj[i], H, p.w[i], H, type, dx_target, H, out_type, NULL)) != 0) goto done;
-        if (x->device != BOAT_DEVICE_CUDA) {
-            gin[i] = emit_out(x->shape, x->ndim, x, d_dx, out_type);
-            dev_free(d_dx);
-            d_dx = NULL;
-            if (!gin[i]) goto done;
+            for (int i = 0; i < 3; ++i) {
+                const boat_tensor_t* x = a->cache_in[i];
+                int out_type = storage_of(x->dtype);
+                void* dx_target;
+                if (x->device == BOAT_DEVICE_CUDA) {
+                    gin[i] = boat_tensor_create_uninit(x->shape, x->ndim, x->dtype, BOAT_DEVICE_CUDA);
+                    if (!gin[i]) goto done;
+                    dx_target = gin[i]->data;
+                } else {
+                    d_dx = dev_alloc((size_t)T * H * storage_size(out_type));
+                    if (!d_dx) goto done;
+                    dx_target = d_dx;
+                }
+                if (boat_report("dX", boat_cuda_gemm(mma, 0, 1, T, H, H, d_dproj[i], H, p.w[i], H, type, dx_target, H, out_type, NULL)) != 0) goto done;
+                if (x->device != BOAT_DEVICE_CUDA) {
+                    gin[i] = emit_out(x->shape, x->ndim, x, d_dx, out_type);
+                    dev_free(d_dx);
+                    d_dx = NULL;
+                    if (!gin[i]) goto done;
+                }
+            }
         }
     }
     if (a->device != BOAT_DEVICE_CUDA &&
@@ -841,6 +920,7 @@ done:
 
 void boat_attention_update(boat_attention_t* a, float learning_rate) {
     if (!a || !a->grad_bucket) return;
+    a->shadow_fresh = false;
     for (int i = 0; i < NPARAM; ++i) {
         boat_tensor_t *w = a->param[i], *g = a->grad[i];
         if (!w || !g) continue;
@@ -971,7 +1051,14 @@ BOAT_NOINLINE void boat_attention_layer_update(boat_attention_layer_t* layer, fl
 
 #define ACCESSOR(name, field, idx) \
     BOAT_NOINLINE boat_tensor_t* boat_attention_get_##name(const boat_attention_t* a) { return a ? a->field[idx] : NULL; }
-ACCESSOR(weight_q, param, WQ) ACCESSOR(weight_k, param, WK) ACCESSOR(weight_v, param, WV) ACCESSOR(weight_o, param, WO)
+/* a caller holding a weight tensor may write it: the converted copies are no longer trusted */
+#define WEIGHT_ACCESSOR(name, idx)                                                         \
+    BOAT_NOINLINE boat_tensor_t* boat_attention_get_##name(const boat_attention_t* a) {    \
+        if (!a) return NULL;                                                               \
+        ((boat_attention_t*)a)->shadow_fresh = false;                                      \
+        return a->param[idx];                                                              \
+    }
+WEIGHT_ACCESSOR(weight_q, WQ) WEIGHT_ACCESSOR(weight_k, WK) WEIGHT_ACCESSOR(weight_v, WV) WEIGHT_ACCESSOR(weight_o, WO)
 ACCESSOR(bias_q, param, BQ) ACCESSOR(bias_k, param, BK) ACCESSOR(bias_v, param, BV) ACCESSOR(bias_o, param, BO)
 ACCESSOR(grad_weight_q, grad, WQ) ACCESSOR(grad_weight_k, grad, WK) ACCESSOR(grad_weight_v, grad, WV)
 ACCESSOR(grad_weight_o, grad, WO) ACCESSOR(grad_bias_q, grad, BQ) ACCESSOR(grad_bias_k, grad, BK)
@@ -982,6 +1069,7 @@ ACCESSOR(grad_bias_v, grad, BV) ACCESSOR(grad_bias_o, grad, BO)
 int boat_attention_to_device(boat_attention_t* a, boat_device_t device) {
     if (!a || (device != BOAT_DEVICE_CPU && device != BOAT_DEVICE_CUDA)) return 1;
     if (a->device == device) return 0;
+    drop_shadow(a);
     boat_tensor_t* moved[NPARAM] = {0};
     for (int i = 0; i < NPARAM; ++i) {
         if (!a->param[i]) continue;

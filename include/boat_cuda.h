@@ -92,6 +92,16 @@ int boat_cuda_gemm(int mma, int trans_a, int trans_b, int64_t M, int64_t N, int6
                    const void* A, int64_t lda, const void* B, int64_t ldb, int in_type,
                    void* C, int64_t ldc, int out_type, const float* bias);
 
+/* `groups` (1 to 4) contractions of one shape, layout and type as one launch: the Q, K and V
+ * projections of a layer (attention.c:363-365 makes three linear_projection calls), their three
+ * weight gradients, their three input gradients.  A, B, C are tables of `groups` pointers (entries
+ * may repeat: self-attention passes the same X three times); bias is NULL or a table whose
+ * entries may be NULL.  Results equal `groups` calls of boat_cuda_gemm, to which shapes outside
+ * the tensor-core kernel fall back one by one. */
+int boat_cuda_gemm_grouped(int mma, int trans_a, int trans_b, int groups, int64_t M, int64_t N, int64_t K,
+                           const void* const* A, int64_t lda, const void* const* B, int64_t ldb, int in_type,
+                           void* const* C, int64_t ldc, int out_type, const float* const* bias);
+
 /* ---- attention core: replaces scaled_dot_product_attention_impl
  *      (src/layers/attention.c:882-1079) ------------------------------------------------
  * Q,K,V,O are [units, S, hs] contiguous: unit u = (b*nh + h) is the block at element
@@ -155,6 +165,9 @@ int boat_cuda_attn_bwd_static(int mma, int64_t units, int64_t S, int64_t hs, int
  *          operands prepared this way make the tensor core's own truncation exact
  * transpose: out[b, j, i] = in[b, i, j]   boat_transpose of the last two dims (linear.c:238-406) */
 int boat_cuda_colsum(const void* X, int x_type, int64_t rows, int64_t cols, float* out);
+/* colsum of `count` (1 to 4) matrices of one shape and type in one launch: the bias gradients of
+ * the Q, K and V projections. */
+int boat_cuda_colsum_multi(const void* const* X, int x_type, int64_t rows, int64_t cols, float* const* out, int count);
 int boat_cuda_axpy(float* y, const float* x, float alpha, int64_t n);
 int boat_cuda_scale(float* y, const float* x, float alpha, int64_t n);
 int boat_cuda_add_bias(float* y, const float* x, const float* bias, int64_t rows, int64_t cols);
@@ -162,6 +175,10 @@ int boat_cuda_mul(float* y, const float* a, const float* b, int64_t n);
 int boat_cuda_lincomb(void* y, const void* a, float alpha, const void* b, float beta, int type, int64_t n);
 int boat_cuda_cast(void* dst, int dst_type, const void* src, int src_type, int64_t n);
 int boat_cuda_round_tf32(float* y, const float* x, int64_t n);
+/* `count` (1 to 8) FP32 tensors converted in one launch: to BF16 (dst_type BOAT_CUDA_BF16) or to
+ * TF32-valued FP32 (BOAT_CUDA_F32_TF32) - the per-step copies of a layer's FP32 weights in the
+ * form the tensor cores read. */
+int boat_cuda_convert_multi(void* const* dst, int dst_type, const float* const* src, const int64_t* n, int count);
 int boat_cuda_transpose(float* out, const float* in, int64_t batch, int64_t rows, int64_t cols);
 
 /* ---- LayerNorm and GELU (the pre-LN encoder block around the attention layer) --------------

@@ -261,3 +261,125 @@ def test_backward_schedules_one_and_two_walks_per_cta():
                                "-k", "attention_core or bf16_tensor_core or chunked"],
                               cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=900)
         assert proc.returncode == 0, "BOAT_BWD_PAIR=%s:\n%s" % (forced, proc.stdout[-3000:])
+
+
+# ---- several problems in one launch -------------------------------------------------------------
+
+def _ptr_table(bufs):
+    """ctypes array of device pointers (None entries become NULL)."""
+    arr = (C.c_void_p * len(bufs))()
+    for i, b in enumerate(bufs):
+        arr[i] = None if b is None else b.p
+    return arr
+
+
+@pytest.mark.parametrize("mma", [capi.MMA_BF16, capi.MMA_TF32, capi.MMA_FP32], ids=["bf16", "tf32", "fp32"])
+@pytest.mark.parametrize("layout", LAYOUTS, ids=["nn", "nt", "tn"])
+@pytest.mark.parametrize("shape,groups,shared_a", [((512, 512, 256), 3, True), ((1024, 256, 512), 3, False),
+                                                   ((256, 768, 8192), 3, True), ((384, 256, 192), 2, False),
+                                                   ((128, 1024, 128), 4, False), ((64, 40, 24), 3, False)],
+                         ids=["shared_x", "distinct", "long_k_split", "two", "four", "cuda_core_shape"])
+def test_grouped_gemm_equals_single_calls(gpu_lib, mma, layout, shape, groups, shared_a):
+    """boat_cuda_gemm_grouped against `groups` boat_cuda_gemm calls on the same operands: the same
+    bits when no K split is involved (one accumulation order), within the arithmetic's tolerance
+    when pieces of K are added by atomics."""
+    lib = gpu_lib
+    M, N, K = shape
+    ta, tb = layout
+    bf = mma == capi.MMA_BF16
+    typ = capi.CUDA_BF16 if bf else capi.CUDA_F32
+    a_shape = (K, M) if ta else (M, K)
+    b_shape = (N, K) if tb else (K, N)
+    hA = [rng.normal(11, 0 if shared_a else g, a_shape) for g in range(groups)]
+    hB = [rng.normal(12, g, b_shape, std=1.0 / np.sqrt(K)) for g in range(groups)]
+    hbias = [rng.normal(13, g, (N,)) if g != 1 else None for g in range(groups)]        # one group without a bias
+    if bf:
+        hA, hB = [rng.bf16_round(x) for x in hA], [rng.bf16_round(x) for x in hB]
+    dA0 = DeviceBuffer.from_numpy(hA[0], bf16=bf)
+    dA = [dA0 if shared_a else DeviceBuffer.from_numpy(hA[g], bf16=bf) for g in range(groups)]
+    dB = [DeviceBuffer.from_numpy(hB[g], bf16=bf) for g in range(groups)]
+    dbias = [None if b is None else DeviceBuffer.from_numpy(b) for b in hbias]
+    for out_type in sorted({typ, capi.CUDA_F32}):
+        split_possible = out_type == capi.CUDA_F32      # FP32 outputs of few tiles with a long K are summed by atomics
+        osz = 2 if out_type == capi.CUDA_BF16 else 4
+        single = [DeviceBuffer(M * N * osz) for _ in range(groups)]
+        grouped = [DeviceBuffer(M * N * osz) for _ in range(groups)]
+        for g in range(groups):
+            check(lib.boat_cuda_gemm(mma, ta, tb, M, N, K, dA[g].p, a_shape[1], dB[g].p, b_shape[1], typ, single[g].p, N,
+                                     out_type, None if dbias[g] is None else dbias[g].p), "gemm")
+        check(lib.boat_cuda_gemm_grouped(mma, ta, tb, groups, M, N, K, _ptr_table(dA), a_shape[1], _ptr_table(dB),
+                                         b_shape[1], typ, _ptr_table(grouped), N, out_type, _ptr_table(dbias)), "grouped")
+        check(lib.boat_cuda_sync(), "sync")
+        for g in range(groups):
+            one = single[g].numpy((M, N), bf16=out_type == capi.CUDA_BF16)
+            many = grouped[g].numpy((M, N), bf16=out_type == capi.CUDA_BF16)
+            opA = hA[g].T if ta else hA[g]
+            opB = hB[g].T if tb else hB[g]
+            ref = opA.astype(np.float64) @ opB.astype(np.float64) + (0 if hbias[g] is None else hbias[g].astype(np.float64))
+            assert rel(many, ref) <= TOL[mma], (g, out_type)
+            if not (split_possible and K >= 2048):
+                assert np.array_equal(one, many), (g, out_type)
+
+
+def test_grouped_gemm_argument_errors(gpu_lib):
+    lib = gpu_lib
+    buf = DeviceBuffer(128 * 128 * 4)
+    tab = _ptr_table([buf, buf])
+    assert lib.boat_cuda_gemm_grouped(capi.MMA_TF32, 0, 0, 0, 128, 128, 128, tab, 128, tab, 128, capi.CUDA_F32, tab, 128,
+                                      capi.CUDA_F32, None) != 0
+    assert lib.boat_cuda_gemm_grouped(capi.MMA_TF32, 0, 0, 5, 128, 128, 128, tab, 128, tab, 128, capi.CUDA_F32, tab, 128,
+                                      capi.CUDA_F32, None) != 0
+    assert lib.boat_cuda_gemm_grouped(capi.MMA_TF32, 0, 0, 2, 128, 128, 128, None, 128, tab, 128, capi.CUDA_F32, tab, 128,
+                                      capi.CUDA_F32, None) != 0
+    hole = _ptr_table([buf, None])
+    assert lib.boat_cuda_gemm_grouped(capi.MMA_TF32, 0, 0, 2, 128, 128, 128, hole, 128, tab, 128, capi.CUDA_F32, tab, 128,
+                                      capi.CUDA_F32, None) != 0
+
+
+@pytest.mark.parametrize("bf", [True, False], ids=["bf16", "f32"])
+@pytest.mark.parametrize("rows,cols,count", [(4096, 1024, 3), (333, 72, 2), (8, 2048, 4), (1000, 13, 3)])
+def test_colsum_multi(gpu_lib, bf, rows, cols, count):
+    """Column sums of several matrices in one launch, with the outputs next to one another (as in
+    the layer's gradient bucket) and apart."""
+    lib = gpu_lib
+    hx = [rng.normal(21, i, (rows, cols)) for i in range(count)]
+    if bf:
+        hx = [rng.bf16_round(x) for x in hx]
+    dx = [DeviceBuffer.from_numpy(x, bf16=bf) for x in hx]
+    packed = DeviceBuffer(count * cols * 4)
+    apart = [DeviceBuffer(cols * 4) for _ in range(count)]
+    out_packed = (C.c_void_p * count)(*[packed.p.value + i * cols * 4 for i in range(count)])
+    typ = capi.CUDA_BF16 if bf else capi.CUDA_F32
+    check(lib.boat_cuda_colsum_multi(_ptr_table(dx), typ, rows, cols, out_packed, count), "colsum_multi")
+    check(lib.boat_cuda_colsum_multi(_ptr_table(dx), typ, rows, cols, _ptr_table(apart), count), "colsum_multi")
+    check(lib.boat_cuda_sync(), "sync")
+    got = packed.numpy((count, cols))
+    for i in range(count):
+        ref = hx[i].astype(np.float64).sum(axis=0)
+        scale = np.abs(hx[i]).astype(np.float64).sum(axis=0).max()
+        assert np.abs(got[i] - ref).max() <= 1e-6 * scale
+        assert np.abs(apart[i].numpy((cols,)) - ref).max() <= 1e-6 * scale
+
+
+@pytest.mark.parametrize("sizes", [(1 << 20, 1 << 20, 1 << 20, 1 << 20), (4096, 8, 100000, 24), (7, 1001, 64)])
+def test_convert_multi_equals_single_conversions(gpu_lib, sizes):
+    """Several FP32 tensors to BF16 / to TF32-valued FP32 in one launch: the bits of boat_cuda_cast /
+    boat_cuda_round_tf32 on each."""
+    lib = gpu_lib
+    hx = [rng.normal(31, i, (n,)) for i, n in enumerate(sizes)]
+    dx = [DeviceBuffer.from_numpy(x) for x in hx]
+    counts = (C.c_int64 * len(sizes))(*sizes)
+    for dst_type, esz in ((capi.CUDA_BF16, 2), (capi.CUDA_F32_TF32, 4)):
+        many = [DeviceBuffer(n * esz) for n in sizes]
+        one = [DeviceBuffer(n * esz) for n in sizes]
+        check(lib.boat_cuda_convert_multi(_ptr_table(many), dst_type, _ptr_table(dx), counts, len(sizes)), "convert_multi")
+        for i, n in enumerate(sizes):
+            if dst_type == capi.CUDA_BF16:
+                check(lib.boat_cuda_cast(one[i].p, capi.CUDA_BF16, dx[i].p, capi.CUDA_F32, n), "cast")
+            else:
+                check(lib.boat_cuda_round_tf32(one[i].p, dx[i].p, n), "round_tf32")
+        check(lib.boat_cuda_sync(), "sync")
+        for i, n in enumerate(sizes):
+            bf = dst_type == capi.CUDA_BF16
+            assert np.array_equal(many[i].numpy((n,), bf16=bf), one[i].numpy((n,), bf16=bf)), (dst_type, i)
+    assert lib.boat_cuda_convert_multi(_ptr_table(dx), capi.CUDA_F32, _ptr_table(dx), counts, len(sizes)) != 0

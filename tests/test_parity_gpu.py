@@ -243,3 +243,63 @@ def test_chunked_host_path_equals_the_device_path(gpu_lib, B, S, H, nh, precisio
         else:
             # per-row arithmetic is the same in both paths
             assert np.array_equal(fh[key], fd[key]), key
+
+
+@pytest.mark.parametrize("precision,bf16,tol", [(capi.MMA_BF16, True, TOL_BF16), (capi.MMA_TF32, False, TOL_TF32)],
+                         ids=["bf16", "tf32"])
+def test_cuda_layer_sees_every_weight_change(gpu_lib, precision, bf16, tol):
+    """A CUDA layer keeps tensor-core copies of its FP32 weights from a forward to the backward of
+    the same step.  Each way the weights can change - an SGD update, writing a weight tensor fetched
+    through an accessor (also between forward and backward), moving the layer - must show in the
+    next result as it does in the restatement run with the changed weights."""
+    from boat_b200.host import Attention, Tensor
+    B, S, H, nh = 1, 256, 128, 2
+    case = cases.Case("shadow", B, S, H, nh, causal=True, bias_std=0.1)
+    inp = case.inputs(bf16=bf16)
+    names = ["weight_q", "weight_k", "weight_v", "weight_o"]
+    layer = Attention(H, nh, causal=True, use_bias=True)
+    for i, n in enumerate(names):
+        layer.param(n).set(inp["w"][i])
+    for i, p in enumerate("qkvo"):
+        layer.param("bias_" + p).set(inp["b"][i])
+    layer.to_device(capi.DEVICE_CUDA)
+    layer.set_precision(precision)
+    x = Tensor.from_numpy(inp["q"], capi.DEVICE_CUDA, bf16=bf16)
+    g = Tensor.from_numpy(inp["dout"], capi.DEVICE_CUDA, bf16=bf16)
+
+    def ours():
+        out = layer.forward(x, x, x)
+        gq, gk, gv = layer.backward(g)
+        res = {"out": out.numpy(), "dq": gq.numpy(), "dk": gk.numpy(), "dv": gv.numpy(),
+               "dw": [layer.param("grad_" + n).numpy() for n in names],
+               "db": [layer.param("grad_bias_" + p).numpy() for p in "qkvo"]}
+        return res
+
+    def theirs(w, b):
+        return oracle.port_step(inp["q"], inp["q"], inp["q"], w, b, inp["dout"], nh, True)
+
+    w = [a.copy() for a in inp["w"]]
+    b = [a.copy() for a in inp["b"]]
+    first = ours()
+    assert_close(first, theirs(w, b), tol, "first step")
+    # SGD update with a step large enough to matter at this precision
+    layer.update(0.5)
+    w = [wi - np.float32(0.5) * gi for wi, gi in zip(w, first["dw"])]
+    b = [bi - np.float32(0.5) * gi for bi, gi in zip(b, first["db"])]
+    second = ours()
+    assert_close(second, theirs(w, b), tol, "after update")
+    assert cases.rel_err(second["out"], first["out"]) > 10 * tol      # the change is visible at all
+    # a weight written between forward and backward: the backward must use the new values
+    out = layer.forward(x, x, x)
+    w[3] = np.ascontiguousarray(w[3][::-1] * np.float32(0.5))
+    layer.param("weight_o").set(w[3])
+    gq, gk, gv = layer.backward(g)
+    ref = theirs(w, b)
+    assert cases.rel_err(gq.numpy(), ref["dq"]) <= tol
+    assert cases.rel_err(layer.param("grad_weight_q").numpy(), ref["dw"][0]) <= tol
+    # moving the layer to the host and back keeps working
+    layer.to_device(capi.DEVICE_CPU)
+    layer.to_device(capi.DEVICE_CUDA)
+    third = ours()
+    assert_close(third, theirs(w, b), tol, "after moving the layer")
+    layer.free()
