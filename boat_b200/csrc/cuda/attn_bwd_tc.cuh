@@ -41,6 +41,7 @@
 // Warp 0: TMA producer (K, V, Q, statistics), warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store
 // (two warps per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.
 #pragma once
+#include <type_traits>
 #include "attn_fwd_tc.cuh"
 
 namespace boatcu {
@@ -352,6 +353,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
         const uint32_t col0 = 64u * half;                           // first query column of this thread
         const float sl2 = p.scale * 1.4426950408889634f;
+        const uint64_t sl2_2 = pack_f32x2(sl2, sl2), scale_2 = pack_f32x2(p.scale, p.scale);
         uint8_t* ds_row = ds_smem + half * kBoxBytes + r * 128;     // box `half` holds query columns 64h..64h+63
         const int swz = r & 7;
         bool ok = true;
@@ -400,6 +402,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_ld32(tmem_base + C::COL_S + lane_addr + col0, s0);
                 tmem_ld32(tmem_base + C::COL_S + lane_addr + col0 + 32, s1);
                 tmem_wait_ld();
+                // The mask test is a compile-time flag of the loop body: a branch per group of
+                // columns would end the compiler's scheduling region there and leave the warp
+                // running each group's FMA -> exp2 -> convert chain at its latency.
+                auto phase_a = [&](auto diag_c) {
+                constexpr bool kDiag = decltype(diag_c)::value;
 #pragma unroll
                 for (int x = 0; x < 32; x += 4) {
                     // four consecutive query columns from each 32-column chunk; their -lse come
@@ -408,19 +415,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const float4 la = *reinterpret_cast<const float4*>(lse_s + q0);
                     const float4 lb = *reinterpret_cast<const float4*>(lse_s + q1);
                     float a[4], b[4];
-                    a[0] = fast_exp2(fmaf(__uint_as_float(s0[x]), sl2, la.x));
-                    a[1] = fast_exp2(fmaf(__uint_as_float(s0[x + 1]), sl2, la.y));
-                    a[2] = fast_exp2(fmaf(__uint_as_float(s0[x + 2]), sl2, la.z));
-                    a[3] = fast_exp2(fmaf(__uint_as_float(s0[x + 3]), sl2, la.w));
-                    b[0] = fast_exp2(fmaf(__uint_as_float(s1[x]), sl2, lb.x));
-                    b[1] = fast_exp2(fmaf(__uint_as_float(s1[x + 1]), sl2, lb.y));
-                    b[2] = fast_exp2(fmaf(__uint_as_float(s1[x + 2]), sl2, lb.z));
-                    b[3] = fast_exp2(fmaf(__uint_as_float(s1[x + 3]), sl2, lb.w));
-                    if (diag) {                      // query q sees key r only when q >= r
+                    // s*c - lse for two columns per FMA-pipe instruction
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s0[x]), __uint_as_float(s0[x + 1])), sl2_2, pack_f32x2(la.x, la.y)), a[0], a[1]);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s0[x + 2]), __uint_as_float(s0[x + 3])), sl2_2, pack_f32x2(la.z, la.w)), a[2], a[3]);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s1[x]), __uint_as_float(s1[x + 1])), sl2_2, pack_f32x2(lb.x, lb.y)), b[0], b[1]);
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s1[x + 2]), __uint_as_float(s1[x + 3])), sl2_2, pack_f32x2(lb.z, lb.w)), b[2], b[3]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        a[e] = fast_exp2(a[e]);
+                        b[e] = fast_exp2(b[e]);
+                    }
+                    if (kDiag) {                     // query q sees key r only when q >= r
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            if (q0 + e < r) a[e] = 0.f;
-                            if (q1 + e < r) b[e] = 0.f;
+                            a[e] = q0 + e < r ? 0.f : a[e];
+                            b[e] = q1 + e < r ? 0.f : b[e];
                         }
                     }
                     ph[x >> 1] = pack_bf16(a[0], a[1]);
@@ -428,6 +437,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     ph[16 + (x >> 1)] = pack_bf16(b[0], b[1]);
                     ph[16 + (x >> 1) + 1] = pack_bf16(b[2], b[3]);
                 }
+                };
+                if (diag) phase_a(std::true_type{});
+                else      phase_a(std::false_type{});
                 // P^T over this thread's own S^T columns: 64 BF16 = 32 columns starting at col0
                 tmem_st32(tmem_base + C::COL_S + lane_addr + col0, ph);
             }
@@ -454,12 +466,14 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         uint32_t o[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const uint32_t pk = ph[half32 * 16 + (x >> 1) + e];
-                            const float p0 = __uint_as_float(pk << 16), p1 = __uint_as_float(pk & 0xffff0000u);
+                            const uint32_t pk = ph[half32 * 16 + (x >> 1) + e];        // two probabilities, BF16
                             const float dp0 = __uint_as_float(half32 ? d1[x + 2 * e] : d0[x + 2 * e]);
                             const float dp1 = __uint_as_float(half32 ? d1[x + 2 * e + 1] : d0[x + 2 * e + 1]);
-                            // P * (dP - delta) / sqrt(hs), the last two folded into one FMA
-                            o[e] = pack_bf16(p0 * fmaf(dp0, p.scale, nd[2 * e]), p1 * fmaf(dp1, p.scale, nd[2 * e + 1]));
+                            // (dP - delta) / sqrt(hs) for both columns in one FP32 FMA, rounded to BF16 and
+                            // multiplied with the BF16 probabilities in one packed BF16 multiply
+                            float t0, t1;
+                            unpack_f32x2(fma_f32x2(pack_f32x2(dp0, dp1), scale_2, pack_f32x2(nd[2 * e], nd[2 * e + 1])), t0, t1);
+                            o[e] = mul_bf16x2(pk, pack_bf16(t0, t1));
                         }
                         const int unit16 = half32 * 4 + u;
                         *reinterpret_cast<uint4*>(ds_row + ((unit16 ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);

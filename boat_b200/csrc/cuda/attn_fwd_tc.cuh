@@ -5,19 +5,29 @@
 // Replaces scaled_dot_product_attention_impl (reference src/layers/attention.c:997-1073),
 // which materialises scores and probabilities as [B,nh,S,S] FP32 tensors.
 //
-// One CTA = one 128-row query tile of one (batch,head) unit; it walks the key/value tiles of
-// 128 rows.  Per key tile:
+// One CTA owns an SM and two adjacent 128-row query tiles A and B of one (batch, head) unit and
+// walks the key/value tiles of 128 rows.  Per key tile and query tile:
 //     S  = Q . K^T            tcgen05.mma, both operands from shared memory, S in tensor memory
-//     P  = exp2(S*c - m*c)    4 softmax warps, one thread per query row (TMEM lane = row):
-//                             tcgen05.ld, running max m and sum l in registers, P written
-//                             back over S in tensor memory (BF16 pairs, or FP32 for TF32)
+//     P  = exp2(S*c - m*c)    4 softmax warps per query tile, one thread per query row (TMEM lane =
+//                             row): the row of 128 scores comes into registers with one
+//                             tcgen05.ld wait, running max m and sum l stay in registers, P is
+//                             written back over S (BF16 pairs, or TF32-valued FP32)
 //     O += P . V              tcgen05.mma, A = P from tensor memory, B = V from shared memory
 //                             read along its contiguous head dimension (no transpose)
 // The accumulator O is rescaled in tensor memory only when the running max has grown by more
 // than 2^8 (the warp votes), the exact correction is folded into the final 1/l.
-// Two CTAs share an SM (<= 112 KB shared memory, <= 256 TMEM columns each), so one CTA's
-// softmax overlaps the other's MMAs.  Warp 0: TMA producer, warp 1: MMA issuer,
-// warps 2-5: softmax and epilogue.
+//
+// One thread issues the MMAs of both query tiles in a fixed order,
+//     S_A(0) S_B(0) | P.V_A(0) S_A(1) | P.V_B(0) S_B(1) | P.V_A(1) S_A(2) | ...
+// so that the exponentials of tile A's step run under the MMAs of tile B and the other way
+// round (with one query tile per CTA and two CTAs per SM nothing orders the two, and they
+// drift into doing their exponentials at the same time on the SM's one special-function unit).
+// K and V tiles are loaded once for both query tiles; CTAs of a few units at a time are scheduled
+// together so that those tiles stay in L2.
+//
+// Warp 0: TMA producer; warp 1: MMA issuer; warps 2-5: softmax and epilogue of tile A;
+// warps 6-9: of tile B.  Tensor memory: S/P of A and B in columns [0,128) and [128,256), the
+// two O accumulators behind them.
 #pragma once
 #include "tc_common.cuh"
 #include <float.h>
@@ -29,7 +39,7 @@ using namespace tc;
 
 constexpr int kTile = 128;            // query rows per CTA and key rows per step
 constexpr int kBoxBytes = kTile * 128;   // one TMA box: 128 rows x 128 bytes
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 320;     // producer, MMA issuer, 2 x 4 softmax warps
 
 template <typename T, int HS>
 struct FwdCfg {
@@ -40,11 +50,12 @@ struct FwdCfg {
     static constexpr int BOXC = 128 / ES;                // elements per box row
     static constexpr int UK = 32 / ES;                   // K extent of one MMA
     static constexpr int TILE_BYTES = NBOX * kBoxBytes;
-    static constexpr int KV_STAGES = TILE_BYTES <= 16384 ? 2 : 1;
-    static constexpr int SMEM = TILE_BYTES * (1 + 2 * KV_STAGES) + 1024 + 256;
-    static constexpr uint32_t S_COLS = kTile;            // FP32 scores, later P in place
-    static constexpr uint32_t TMEM_COLS = (S_COLS + HS) <= 128 ? 128 : 256;
-    static_assert(S_COLS + HS <= 256, "tensor memory budget");
+    static constexpr int KV_STAGES = TILE_BYTES <= 16384 ? 3 : 2;
+    static constexpr int SMEM = TILE_BYTES * (2 + 2 * KV_STAGES) + 1024 + 256;   // Q of both tiles, K and V rings
+    static constexpr uint32_t COL_O = 2 * kTile;         // S/P of tiles A and B, then O of A, then O of B
+    static constexpr uint32_t TMEM_COLS = 512;           // 2 x (128 + HS) rounded up to a power of two
+    static_assert(2 * (kTile + HS) <= 512, "tensor memory budget");
+    static_assert(SMEM <= 227 * 1024, "shared memory budget");
     static_assert(ROWB % 128 == 0, "row must be whole 128-byte boxes");
 };
 
@@ -55,6 +66,7 @@ struct FwdParams {
     int units;
     int causal;
     float scale;       // 1/sqrt(hs)
+    int group;         // units whose CTAs are scheduled together (their K and V share L2)
     unsigned int* status;
 };
 
@@ -64,17 +76,52 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// One row of 128 scores in registers -> probabilities exp2(s*sl2 + neg_m) in place (BF16: packed
+// pairs in sc[0..63]; TF32: TF32-valued floats in sc[0..127]); returns their sum.  Columns beyond
+// `last` are masked (DIAG only).  DIAG is a template parameter so that the loop body is one
+// straight-line block: a branch per element pair would keep the compiler from overlapping the
+// pairs' FMA -> exp2 -> convert chains, and a lone warp would then run at the chain's latency.
+template <bool TF32, bool DIAG>
+__device__ __forceinline__ float exp_row(uint32_t (&sc)[kTile], float sl2, float neg_m, int last) {
+    const uint64_t sl2_2 = pack_f32x2(sl2, sl2), neg_m2 = pack_f32x2(neg_m, neg_m);
+    uint64_t l2[4] = {0ull, 0ull, 0ull, 0ull};          // four chains of (even, odd) partial sums
+#pragma unroll
+    for (int i = 0; i < kTile; i += 2) {
+        float x0, x1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), sl2_2, neg_m2), x0, x1);
+        float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+        if (DIAG) {
+            e0 = i > last ? 0.f : e0;
+            e1 = i + 1 > last ? 0.f : e1;
+        }
+        if (TF32) {
+            // round to the nearest TF32 value: the MMA would otherwise truncate
+            e0 = round_to_tf32(e0);
+            e1 = round_to_tf32(e1);
+            sc[i] = __float_as_uint(e0);
+            sc[i + 1] = __float_as_uint(e1);
+        } else {
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+            sc[i >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+        l2[(i >> 1) & 3] = add_f32x2(l2[(i >> 1) & 3], pack_f32x2(e0, e1));
+    }
+    float a0, a1;
+    unpack_f32x2(add_f32x2(add_f32x2(l2[0], l2[1]), add_f32x2(l2[2], l2[3])), a0, a1);
+    return a0 + a1;
+}
+
 template <typename T, int HS>
-__global__ void __launch_bounds__(kFwdThreads, 2)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                 const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+                        const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
     using C = FwdCfg<T, HS>;
     constexpr bool TF32 = C::TF32;
     constexpr int ST = C::KV_STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_smem = smem;
-    uint8_t* k_smem = q_smem + C::TILE_BYTES;
+    uint8_t* q_smem = smem;                               // tile A, then tile B
+    uint8_t* k_smem = q_smem + 2 * C::TILE_BYTES;
     uint8_t* v_smem = k_smem + ST * C::TILE_BYTES;
     uint64_t* bars = (uint64_t*)(v_smem + ST * C::TILE_BYTES);
     uint64_t* q_full = bars;              // 1
@@ -82,16 +129,28 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint64_t* k_empty = k_full + ST;      // [ST]
     uint64_t* v_full = k_empty + ST;      // [ST]
     uint64_t* v_empty = v_full + ST;      // [ST]
-    uint64_t* s_full = v_empty + ST;      // 1: S tile complete in TMEM
-    uint64_t* p_full = s_full + 1;        // 1: P written (128 arrivals)
-    uint64_t* o_done = p_full + 1;        // 1: last PV complete
+    uint64_t* s_full = v_empty + ST;      // [2]: S of tile A / B complete in tensor memory
+    uint64_t* p_full = s_full + 2;        // [2]: P of tile A / B written (128 arrivals each)
+    uint64_t* o_done = p_full + 2;        // 1: every MMA complete
     uint32_t* tmem_slot = (uint32_t*)(o_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_tiles = p.S / kTile;
-    const int unit = blockIdx.x % p.units;
-    const int qt = q_tiles - 1 - blockIdx.x / p.units;     // long (late) rows first when causal
-    const int n_kv = p.causal ? qt + 1 : q_tiles;
+    const int n_pairs = (q_tiles + 1) / 2;
+    // CTA order: units in groups of p.group, so that the K and V tiles which the CTAs running at one
+    // time stream through shared memory (every CTA of a unit reads all of the unit's K and V) stay
+    // in L2; inside a group the tile pair is the slow index, long (late) rows first when causal.
+    const int per_group = p.group * n_pairs;
+    const int grp = blockIdx.x / per_group;
+    const int rem = blockIdx.x - grp * per_group;
+    const int in_group = min(p.group, p.units - grp * p.group);
+    const int unit = grp * p.group + rem % in_group;
+    const int pt = n_pairs - 1 - rem / in_group;
+    const int qt_a = 2 * pt, qt_b = 2 * pt + 1;
+    const bool has_b = qt_b < q_tiles;                     // an odd tile count leaves the last CTA one tile
+    const int n_a = p.causal ? qt_a + 1 : q_tiles;
+    const int n_b = has_b ? (p.causal ? qt_b + 1 : q_tiles) : 0;
+    const int n_kv = n_a > n_b ? n_a : n_b;
     const int row_base = unit * p.S;                       // first row of this unit in [units*S, hs]
 
     if (threadIdx.x == 0) {
@@ -102,8 +161,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
         }
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(&s_full[g], 1);
+            mbar_init(&p_full[g], 128);
+        }
         mbar_init(o_done, 1);
         fence_barrier_init();
         tma_prefetch_desc(&map_q);
@@ -115,16 +176,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;                 // S / P
-    const uint32_t tmem_o = tmem_base + C::S_COLS;     // O accumulator, HS columns
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             bool ok = true;
-            mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
-            for (int b = 0; b < C::NBOX; ++b)
-                tma_load_2d(q_smem + b * kBoxBytes, &map_q, q_full, b * C::BOXC, row_base + qt * kTile);
+            mbar_arrive_expect_tx(q_full, (has_b ? 2 : 1) * C::TILE_BYTES);
+            for (int g = 0; g < (has_b ? 2 : 1); ++g)
+                for (int b = 0; b < C::NBOX; ++b)
+                    tma_load_2d(q_smem + g * C::TILE_BYTES + b * kBoxBytes, &map_q, q_full, b * C::BOXC,
+                                row_base + (qt_a + g) * kTile);
             for (int j = 0; j < n_kv && ok; ++j) {
                 const int s = j % ST;
                 const uint32_t par = ((j / ST) & 1) ^ 1;
@@ -148,72 +209,105 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             constexpr uint32_t idesc_s = make_idesc(fmt, false, false, kTile, kTile);   // S = Q K^T
             constexpr uint32_t idesc_o = make_idesc(fmt, false, true, kTile, HS);       // O = P V
             bool ok = mbar_wait(q_full, 0, p.status, kTimeoutMma);
-            const uint32_t q_addr = smem_u32(q_smem);
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const int s = j % ST;
-                const uint32_t par = (j / ST) & 1;
-                if (!mbar_wait(&k_full[s], par, p.status, kTimeoutMma)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t k_addr = smem_u32(k_smem + s * C::TILE_BYTES);
+            tc_fence_after_sync();
+            // S of tile g against key tile j (already waited for) into the tile's S columns
+            auto issue_s = [&](int g, int j) {
+                const uint32_t q_addr = smem_u32(q_smem + g * C::TILE_BYTES);
+                const uint32_t k_addr = smem_u32(k_smem + (j % ST) * C::TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < C::ROWB / 32; ++kk) {
                     const uint32_t off = (kk / 4) * kBoxBytes + (kk % 4) * 32;
-                    mma_ss<TF32>(tmem_s, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024),
-                                 idesc_s, kk > 0);
+                    mma_ss<TF32>(tmem_base + g * kTile, smem_desc_sw128(q_addr + off, 16, 1024),
+                                 smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, kk > 0);
                 }
-                mma_commit(&k_empty[s]);
-                mma_commit(s_full);
-                // wait for the softmax warps to turn S into P, then accumulate P.V
-                if (!mbar_wait(p_full, j & 1, p.status, kTimeoutMma)) { ok = false; break; }
-                if (!mbar_wait(&v_full[s], par, p.status, kTimeoutMma)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(v_smem + s * C::TILE_BYTES);
+                mma_commit(&s_full[g]);
+            };
+            // O of tile g += P (over the tile's S columns) . V_j
+            auto issue_pv = [&](int g, int j) {
+                const uint32_t v_addr = smem_u32(v_smem + (j % ST) * C::TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < kTile / C::UK; ++kk) {
-                    mma_ts<TF32>(tmem_o, tmem_s + kk * 8, smem_desc_mn(v_addr + kk * C::UK * 128, kBoxBytes, TF32),
-                                 idesc_o, j > 0 || kk > 0);
+                    mma_ts<TF32>(tmem_base + C::COL_O + g * HS, tmem_base + g * kTile + kk * 8,
+                                 smem_desc_mn(v_addr + kk * C::UK * 128, kBoxBytes, TF32), idesc_o, j > 0 || kk > 0);
                 }
-                mma_commit(&v_empty[s]);
+            };
+            if (ok && mbar_wait(&k_full[0], 0, p.status, kTimeoutMma)) {
+                tc_fence_after_sync();
+                issue_s(0, 0);
+                if (has_b) issue_s(1, 0);
+                mma_commit(&k_empty[0]);
+            } else {
+                ok = false;
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const uint32_t par = (j / ST) & 1;
+                const bool next = j + 1 < n_kv;
+                const uint32_t par_next = ((j + 1) / ST) & 1;
+                bool v_waited = false, k_waited = false;
+                for (int g = 0; g < 2 && ok; ++g) {
+                    const int n_g = g ? n_b : n_a;
+                    if (j < n_g) {
+                        if (!mbar_wait(&p_full[g], j & 1, p.status, kTimeoutMma)) { ok = false; break; }
+                        if (!v_waited && !mbar_wait(&v_full[j % ST], par, p.status, kTimeoutMma)) { ok = false; break; }
+                        v_waited = true;
+                        tc_fence_after_sync();
+                        issue_pv(g, j);
+                    }
+                    if (j + 1 < n_g) {
+                        if (!k_waited && !mbar_wait(&k_full[(j + 1) % ST], par_next, p.status, kTimeoutMma)) { ok = false; break; }
+                        k_waited = true;
+                        tc_fence_after_sync();
+                        issue_s(g, j + 1);
+                    }
+                }
+                if (!ok) break;
+                mma_commit(&v_empty[j % ST]);                    // both tiles' P.V of this step are issued
+                if (next) mma_commit(&k_empty[(j + 1) % ST]);   // and both S of the next
             }
             if (ok) mma_commit(o_done);
         }
     } else {
-        // ---------------- softmax + epilogue: warps 2..5, thread = query row ----------------
+        // ---------------- softmax + epilogue: warps 2..5 tile A, 6..9 tile B; thread = query row ----------------
+        const int g = (warp - 2) >> 2;
+        const int n_g = g ? n_b : n_a;
+        const int qt = g ? qt_b : qt_a;
         const int lane_group = warp & 3;
         const int r_in_tile = lane_group * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+        const uint32_t tmem_s = tmem_base + g * kTile;
+        const uint32_t tmem_o = tmem_base + C::COL_O + g * HS;
         const float sl2 = p.scale * 1.4426950408889634f;      // scores -> log2 domain
         float m_ref = -FLT_MAX;      // max the exponentials are taken against
         float l = 0.f;               // running sum of exp
         bool ok = true;
-        for (int j = 0; j < n_kv; ++j) {
-            if (!mbar_wait(s_full, j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
+        for (int j = 0; j < n_g; ++j) {
+            if (!mbar_wait(&s_full[g], j & 1, p.status, kTimeoutSoftmax)) { ok = false; break; }
             tc_fence_after_sync();
             const bool diag = p.causal && j == qt;
-            // pass 1: row maximum of the visible scores (the mask only exists on the diagonal tile).
-            // The 32-column chunks are double-buffered in registers: the load of the next chunk is
-            // in flight while this one is reduced, and four running maxima keep the chain short.
+            // The whole row of scores (128 columns) comes into registers with one wait; the maximum and
+            // the exponentials both work from there.
+            uint32_t sc[kTile];
+#pragma unroll
+            for (int c = 0; c < kTile / 32; ++c)
+                tmem_ld32(tmem_s + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(sc + c * 32));
+            tmem_wait_ld();
+            // row maximum of the visible scores (the mask only exists on the diagonal tile)
             float tmax;
             {
-                uint32_t rr[2][32];
-                float t4[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};
-                tmem_ld32(tmem_s + lane_addr, rr[0]);
+                float t8[8];
 #pragma unroll
-                for (int c = 0; c < kTile / 32; ++c) {
-                    tmem_wait_ld();
-                    if (c + 1 < kTile / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, rr[(c + 1) & 1]);
-                    const uint32_t(&r)[32] = rr[c & 1];
-                    if (diag) {
+                for (int i = 0; i < 8; ++i) t8[i] = -FLT_MAX;
+                if (diag) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i <= r_in_tile) t4[i & 3] = fmaxf(t4[i & 3], __uint_as_float(r[i]));
-                    } else {
+                    for (int i = 0; i < kTile; ++i)
+                        t8[i & 7] = fmaxf(t8[i & 7], i <= r_in_tile ? __uint_as_float(sc[i]) : -FLT_MAX);
+                } else {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            t4[(i >> 1) & 3] = fmaxf(t4[(i >> 1) & 3], fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
-                    }
+                    for (int i = 0; i < kTile; i += 2)
+                        t8[(i >> 1) & 7] = max3_f32(t8[(i >> 1) & 7], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]));
                 }
-                tmax = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
+                tmax = fmaxf(max3_f32(t8[0], t8[1], t8[2]), max3_f32(t8[3], t8[4], t8[5]));
+                tmax = max3_f32(tmax, t8[6], t8[7]);
             }
             const float m_new = fmaxf(m_ref, tmax);
             const bool need = (j == 0) || (m_new - m_ref) * sl2 > 8.0f;
@@ -225,74 +319,38 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     l *= alpha;
                 }
                 if (j > 0) {
-                    // S_j is complete, so every earlier P.V has completed too (in-order pipe)
+                    // S_j of this tile is complete, so its earlier P.V have completed too (the MMA
+                    // thread issues S_j behind P.V_(j-1) and the pipe is in order)
 #pragma unroll 1
-                    for (int c = 0; c < HS / 32; ++c) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem_o + lane_addr + c * 32, r);
+                    for (int c = 0; c < HS / 16; ++c) {
+                        uint32_t r[16];
+                        tmem_ld16(tmem_o + lane_addr + c * 16, r);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st32(tmem_o + lane_addr + c * 32, r);
+                        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st16(tmem_o + lane_addr + c * 16, r);
                     }
                     tmem_wait_st();
                 }
             }
-            // pass 2: P = exp2(s*sl2 - m*sl2), written over S; same double buffering.  P of chunk c
-            // lands in columns that belong to chunks already loaded (BF16: [16c, 16c+16), TF32: the
-            // chunk's own), never in those of the chunk in flight.
+            // P = exp2(s*sl2 - m*sl2) in place in the registers (BF16: packed pairs in the first 64),
+            // two elements per FMA-pipe instruction, then written over S
             const float neg_m = -m_ref * sl2;
             float lsum;
             {
-                uint32_t rr[2][32];
-                float l4[4] = {0.f, 0.f, 0.f, 0.f};
-                tmem_ld32(tmem_s + lane_addr, rr[0]);
+                lsum = diag ? exp_row<TF32, true>(sc, sl2, neg_m, r_in_tile) : exp_row<TF32, false>(sc, sl2, neg_m, r_in_tile);
+                constexpr int P_CHUNKS = TF32 ? kTile / 32 : kTile / 64;
 #pragma unroll
-                for (int c = 0; c < kTile / 32; ++c) {
-                    tmem_wait_ld();
-                    if (c + 1 < kTile / 32) tmem_ld32(tmem_s + lane_addr + (c + 1) * 32, rr[(c + 1) & 1]);
-                    uint32_t(&r)[32] = rr[c & 1];
-                    float pv[32];
-                    if (diag) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            float e = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
-                            pv[i] = (c * 32 + i > r_in_tile) ? 0.f : e;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), sl2, neg_m));
-                    }
-                    if (TF32) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            // round to the nearest TF32 value: the MMA would otherwise truncate
-                            uint32_t t32;
-                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(t32) : "f"(pv[i]));
-                            l4[i & 3] += __uint_as_float(t32);
-                            r[i] = t32;
-                        }
-                        tmem_st32(tmem_s + lane_addr + c * 32, r);
-                    } else {
-                        uint32_t h[16];
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(pv[2 * i], pv[2 * i + 1]);
-                            l4[i & 3] += pv[2 * i] + pv[2 * i + 1];
-                            h[i] = *reinterpret_cast<uint32_t*>(&b2);
-                        }
-                        tmem_st16(tmem_s + lane_addr + c * 16, h);
-                    }
-                }
-                lsum = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                for (int c = 0; c < P_CHUNKS; ++c)
+                    tmem_st32(tmem_s + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(sc + c * 32));
             }
             l += lsum;
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[g]);
         }
         // epilogue: O / l -> global, lse = m*scale + ln(l)
-        if (ok && mbar_wait(o_done, 0, p.status, kTimeoutEpilogue)) {
+        if (n_g > 0 && ok && mbar_wait(o_done, 0, p.status, kTimeoutEpilogue)) {
             tc_fence_after_sync();
             const float inv = 1.f / l;
             const int64_t grow = (int64_t)row_base + (int64_t)qt * kTile + r_in_tile;

@@ -30,13 +30,16 @@ int launch_fwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     p.causal = causal;
     p.scale = scale;
     p.status = kernel_status_ptr();
+    // units whose K and V (2 * S * hs elements each) together take about a third of L2
+    const int64_t group = (40ll << 20) / (2 * S * HS * (int64_t)C::ES);
+    p.group = (int)(group < 1 ? 1 : (group > units ? units : group));
     auto kern = attn_fwd_tc_kernel<T, HS>;
     static bool configured = false;
     if (!configured) {
         BOATCU_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
-    const int64_t grid = units * (S / kTile);
+    const int64_t grid = units * ((S / kTile + 1) / 2);      // one CTA per pair of query tiles
     ProfileScope prof("attn_fwd_tc");
     kern<<<(unsigned)grid, kFwdThreads, C::SMEM, stream()>>>(mq, mk, mv, p);
     BOATCU_LAUNCH_OK("attn_fwd_tc");

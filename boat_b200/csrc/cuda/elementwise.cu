@@ -490,13 +490,9 @@ int boat_cuda_colsum_multi(const void* const* X, int x_type, int64_t rows, int64
         t.out[i] = out[s];
         can_vec = can_vec && aligned16(X[s]);
     }
-    for (int i = 0; i < count; ++i) {
-        // outputs that follow one another in memory (the layer's gradient bucket) are cleared together
-        int j = i;
-        while (j + 1 < count && out[j + 1] == out[j] + cols) ++j;
-        BOATCU_CHECK(cudaMemsetAsync(out[i], 0, (size_t)(j - i + 1) * (size_t)cols * sizeof(float), stream()));
-        i = j;
-    }
+    // one clear per output: neighbouring outputs may still be separate allocations, which a single
+    // clear must not span
+    for (int i = 0; i < count; ++i) BOATCU_CHECK(cudaMemsetAsync(out[i], 0, (size_t)cols * sizeof(float), stream()));
     if (rows <= 0) return 0;
     const int cols_per_block = 32 * (can_vec ? vec : 1);
     dim3 grid((unsigned)ceil_div(cols, cols_per_block), 1, (unsigned)count);
