@@ -619,26 +619,35 @@ def main():
             return loss_proxy
 
         es = 2 if bf16 else 4
-        n_e2e = max(2, min(args.steps, 5))
+        n_e2e = max(5, min(args.steps, 20))
         for _ in range(2):               # warm-up: page-locked pool growth, copy streams, first-use set-up
             host_step()
+        check(lib.boat_cuda_sync(), "sync")
         if dist is not None:
             dist.barrier()
-        t0 = time.perf_counter()
+        # Every step is timed on its own (wall clock, synchronised), and the median is reported: on
+        # a shared host single steps now and then stall for tens of milliseconds without using CPU
+        # time; the mean and the slowest step are given beside it.
+        per_step = []
         for _ in range(n_e2e):
+            t0 = time.perf_counter()
             host_step()
-        check(lib.boat_cuda_sync(), "sync")
-        dt = (time.perf_counter() - t0) / n_e2e
-        te = torch.tensor([dt], dtype=torch.float64, device="cuda")
+            check(lib.boat_cuda_sync(), "sync")
+            per_step.append(time.perf_counter() - t0)
+        per_step.sort()
+        dt = per_step[len(per_step) // 2]
+        dt_mean, dt_max = sum(per_step) / len(per_step), per_step[-1]
+        te = torch.tensor([dt, dt_mean, dt_max], dtype=torch.float64, device="cuda")
         if dist is not None:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        dt = float(te.item())
+        dt, dt_mean, dt_max = (float(v) for v in te.tolist())
         wbytes = (4 * d * d + 4 * d) * 4
-        e2e = dict(value=world * T / dt, unit="tokens/s", ms_per_step=dt * 1e3,
+        e2e = dict(value=world * T / dt, unit="tokens/s", ms_per_step=dt * 1e3, steps=n_e2e,
+                   ms_per_step_mean=dt_mean * 1e3, ms_per_step_max=dt_max * 1e3,
                    h2d_bytes_per_step=2 * T * d * es + 2 * wbytes,        # X, dOut, parameters for fwd and bwd
                    d2h_bytes_per_step=4 * T * d * es + wbytes,            # out, dq, dk, dv, parameter gradients
-                   note="host BF16 tensors in and out through boat_attention_forward/backward; wall clock" if bf16
-                   else "host FP32 tensors in and out through boat_attention_forward/backward; wall clock")
+                   note="host BF16 tensors in and out through boat_attention_forward/backward; wall clock, median step" if bf16
+                   else "host FP32 tensors in and out through boat_attention_forward/backward; wall clock, median step")
         host_layer.free()
 
     cpu = None

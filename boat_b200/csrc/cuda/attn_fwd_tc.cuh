@@ -140,11 +140,24 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // CTA order: units in groups of p.group, so that the K and V tiles which the CTAs running at one
     // time stream through shared memory (every CTA of a unit reads all of the unit's K and V) stay
     // in L2; inside a group the tile pair is the slow index, long (late) rows first when causal.
+    // When the units do not divide into whole groups the short group goes first: the launch then ends
+    // with the short CTAs of a full group, which fill the SMs evenly.
     const int per_group = p.group * n_pairs;
-    const int grp = blockIdx.x / per_group;
-    const int rem = blockIdx.x - grp * per_group;
-    const int in_group = min(p.group, p.units - grp * p.group);
-    const int unit = grp * p.group + rem % in_group;
+    const int short_group = p.units % p.group;             // 0: all groups are whole
+    const int short_ctas = short_group * n_pairs;
+    int unit0, in_group, rem;
+    if ((int)blockIdx.x < short_ctas) {
+        unit0 = 0;
+        in_group = short_group;
+        rem = blockIdx.x;
+    } else {
+        const int b = blockIdx.x - short_ctas;
+        const int grp = b / per_group;
+        unit0 = short_group + grp * p.group;
+        in_group = p.group;
+        rem = b - grp * per_group;
+    }
+    const int unit = unit0 + rem % in_group;
     const int pt = n_pairs - 1 - rem / in_group;
     const int qt_a = 2 * pt, qt_b = 2 * pt + 1;
     const bool has_b = qt_b < q_tiles;                     // an odd tile count leaves the last CTA one tile

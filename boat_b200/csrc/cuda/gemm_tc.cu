@@ -68,7 +68,7 @@ struct Params {
 
 template <typename T, bool A_MN, bool B_MN, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ GroupMaps maps, const Params p) {
+gemm_tc_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant__ Params p) {
     using C = Cfg<T, BN>;
     constexpr bool TF32 = sizeof(T) == 4;
     extern __shared__ uint8_t smem_raw[];
