@@ -41,9 +41,6 @@
 // Warp 0: TMA producer (K, V, Q, statistics), warp 1: MMA issuer, warps 2-9: softmax + final dK/dV store
 // (two warps per TMEM lane group, 64 query columns each), warps 10-13: dQ reduction.
 #pragma once
-#ifndef BOAT_BWD_POLY64
-#define BOAT_BWD_POLY64 0
-#endif
 #include <type_traits>
 #include "attn_fwd_tc.cuh"
 
@@ -61,8 +58,6 @@ struct BwdCfg {
     // Q / dO stages: three when they fit (head size 64), so that the dO tile loaded behind a
     // dQ read-out is not needed before the tile after next
     static constexpr int Q_STAGES = HS == 64 ? 3 : 2;
-    // phase A: every POLY_EVERY-th exponential of a thread is a polynomial on the FMA pipe (0: none)
-    static constexpr int POLY_EVERY = HS == 64 ? BOAT_BWD_POLY64 : 0;
     // K,V + Q,dO stages + dS^T + two (lse, delta) buffers + barriers.  With head size 128 this
     // is 231,680 of the 232,448 bytes a CTA may have, so the base must come 1024-byte aligned
     // from the launch (checked at kernel entry) - there is no room for manual alignment slack.
@@ -96,18 +91,6 @@ struct BwdParams {
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-// 2^x for x <= 0 on the FMA pipe: integer part by the magic-number trick, fraction by a cubic
-// (relative error below 1e-3, under the BF16 rounding the result gets next).
-__device__ __forceinline__ float exp2_fma(float x) {
-    x = fmaxf(x, -120.f);
-    const float t = x + 12582912.f;                 // 1.5 * 2^23: the integer part lands in the low mantissa bits
-    const float r = x - (t - 12582912.f);           // fraction in [-0.5, 0.5]
-    float pr = fmaf(r, 0.05550411f, 0.24022651f);
-    pr = fmaf(pr, r, 0.69314718f);
-    pr = fmaf(pr, r, 1.0f);
-    return __int_as_float(__float_as_int(pr) + (__float_as_int(t) << 23));
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -439,14 +422,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s1[x + 2]), __uint_as_float(s1[x + 3])), sl2_2, pack_f32x2(lb.z, lb.w)), b[2], b[3]);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        // one column in POLY_EVERY takes the FMA pipe instead of the special-function unit
-                        if (C::POLY_EVERY > 0 && e % C::POLY_EVERY == C::POLY_EVERY - 1) {
-                            a[e] = exp2_fma(a[e]);
-                            b[e] = exp2_fma(b[e]);
-                        } else {
-                            a[e] = fast_exp2(a[e]);
-                            b[e] = fast_exp2(b[e]);
-                        }
+                        a[e] = fast_exp2(a[e]);
+                        b[e] = fast_exp2(b[e]);
                     }
                     if (kDiag) {                     // query q sees key r only when q >= r
 #pragma unroll
