@@ -484,6 +484,40 @@ def main():
     flops = block_flops(B, S, d, causal) if is_block else algorithmic_flops(B, S, d, causal)
     tflops_per_gpu = flops / (ms_per_step * 1e-3) / 1e12
 
+    # ---- data-parallel block: every parameter gradient summed exactly once?  The local gradients of one
+    # step (no sums started) are added up over the ranks on the side (float64 checksums through
+    # torch.distributed) and compared with what the overlapped, bucketed sums of the library leave.
+    block_grad_check = None
+    if world > 1 and is_block:
+        def grad_checksums():
+            check(lib.boat_cuda_sync(), "sync")
+            arrays = [layer.param("grad_" + n).numpy() for n in ("weight_q", "weight_k", "weight_v", "weight_o",
+                                                                  "bias_q", "bias_k", "bias_v", "bias_o")
+                      if layer.param("grad_" + n) is not None]
+            for part in (block.ln1, block.ln2, block.fc1, block.fc2):
+                arrays += [a for a in part.grads() if a is not None]
+            return torch.tensor([[float(a.astype(np.float64).sum()), float(np.abs(a.astype(np.float64)).sum())] for a in arrays],
+                                dtype=torch.float64, device="cuda")
+        block.zero_dense_grads()
+        layer.set_grad_overlap(0)
+        out, dx = block.step(x, g)                   # local gradients only
+        local = grad_checksums()
+        out.free(); dx.free()
+        block.zero_dense_grads()
+        dist.all_reduce(local, op=dist.ReduceOp.SUM)
+        layer.set_grad_overlap(overlap_mode)
+        out, dx = block.step(x, g)
+        block.allreduce_grads()
+        summed = grad_checksums()
+        out.free(); dx.free()
+        block.zero_dense_grads()
+        err = float(((summed[:, 0] - local[:, 0]).abs() / local[:, 1].clamp_min(1e-30)).max().item())
+        block_grad_check = dict(tensors=int(summed.shape[0]), rel_err=err, tolerance=1e-3,
+                                what="max over the block's gradient tensors of |sum of the summed tensor - sum over ranks of "
+                                     "the local tensor's sum| / sum over ranks of the local tensor's absolute sum")
+        if not err <= 1e-3:
+            raise SystemExit("bench.py: gradient sums of the block differ from the sum of the local gradients: %g" % err)
+
     # ---- strong scaling: the SAME problem (global batch = the per-GPU batch of the weak run) split over the
     # ranks by (batch, head) units, each rank holding only the token rows of its units ----
     strong = None
@@ -663,6 +697,8 @@ def main():
                     tflops_per_gpu=tflops_per_gpu,
                     frac_of_bf16_peak=(tflops_per_gpu / (peaks["bf16"] if ms_per_step * args.steps < 1e3 else peaks["bf16_sustained"])) if bf16 else None,
                     roofline=roofline, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches), clocks=clocks)
+        if block_grad_check is not None:
+            line["grad_sum_check"] = block_grad_check
         if strong:
             line["strong"] = strong
         line["host_affinity"] = affinity

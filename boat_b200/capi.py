@@ -173,6 +173,7 @@ PROTOTYPES = {
     "boat_attention_grad_bucket": (_I, [_P, C.POINTER(C.POINTER(C.c_float)), C.POINTER(_SZ)]),
     "boat_attention_allreduce_grads": (_I, [_P]),
     "boat_attention_set_grad_overlap": (_I, [_P, _I]),
+    "boat_attention_get_grad_overlap": (_I, [_P]),
     "boat_attention_add_to_optimizer": (_I, [_P, _P]),
     "boat_encoder_block_create": (_P, [_P, _P, _P, _P, _P]),
     "boat_encoder_block_forward": (_P, [_P, _P]),

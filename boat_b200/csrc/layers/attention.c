@@ -38,6 +38,8 @@ struct boat_attention_t {
     int            grad_overlap;        /* 0: sums only in allreduce_grads; 1: backward starts both groups
                                            itself; 2: backward starts dWo|dbo, the rest waits for allreduce_grads */
     bool           rest_pending;        /* mode 2: dWq dWk dWv | dbq dbk dbv still to be summed */
+    bool           sums_begun;          /* the last backward started sums of this layer's bucket that nobody
+                                           has joined yet */
 
     /* state of the last forward, consumed by backward */
     boat_tensor_t* cache_in[3];         /* query, key, value - referenced          */
@@ -774,9 +776,13 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     size_t scratch_bytes;
 
     if (!ensure_grads(a)) goto done;
-    /* gradient sums of the previous step still on the communication stream read the bucket
-     * this step is about to overwrite */
-    if (boat_cuda_allreduce_pending() && boat_report("gradient all-reduce", boat_cuda_allreduce_join()) != 0) goto done;
+    /* gradient sums of this layer's previous step still on the communication stream read the bucket
+     * this step is about to overwrite.  (Sums other layers have under way - an encoder block starts
+     * its dense layers' before this call - are not waited for.) */
+    if (a->sums_begun && boat_cuda_allreduce_pending() &&
+        boat_report("gradient all-reduce", boat_cuda_allreduce_join()) != 0)
+        goto done;
+    a->sums_begun = false;
     const bool pipelined = units / a->gran >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) &&
                            on_host(a->cache_in[1]) && on_host(a->cache_in[2]);
     g_async_uploads = pipelined;
@@ -818,6 +824,7 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         float* piece[2] = {d_dw[WO], d_db[WO]};
         const int64_t count[2] = {H * H, bias ? H : 0};
         if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 2)) != 0) goto done;
+        a->sums_begun = true;
     }
 
     /* attention core */
@@ -1119,6 +1126,8 @@ int boat_attention_grad_bucket(const boat_attention_t* a, float** data, size_t* 
     return 0;
 }
 
+int boat_attention_get_grad_overlap(const boat_attention_t* a) { return a ? a->grad_overlap : 0; }
+
 int boat_attention_set_grad_overlap(boat_attention_t* a, int mode) {
     if (!a || mode < 0 || mode > 2) return 1;
     a->grad_overlap = mode;
@@ -1127,23 +1136,27 @@ int boat_attention_set_grad_overlap(boat_attention_t* a, int mode) {
 
 int boat_attention_allreduce_grads(boat_attention_t* a) {
     if (!a || !a->grad_bucket) return 1;
-    /* sums started by the backward itself: the library stream only has to wait for them - after
-     * starting the group the backward left for now (mode 2) */
-    if (a->rest_pending) {
-        const int64_t H = (int64_t)a->config.hidden_size;
-        const bool bias = a->param[BQ] != NULL;
-        float* bucket = (float*)a->grad_bucket->data;
-        float* piece[2] = {bucket, bucket + 4 * H * H};
-        const int64_t count[2] = {3 * H * H, bias ? 3 * H : 0};
-        a->rest_pending = false;
-        if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 2)) != 0) return 3;
-    }
-    if (boat_cuda_allreduce_pending()) return boat_report("gradient all-reduce", boat_cuda_allreduce_join());
     if (boat_cuda_comm_world() <= 1) return 0;
     if (a->device != BOAT_DEVICE_CUDA) {
         fprintf(stderr, "boat: gradient all-reduce needs the layer on BOAT_DEVICE_CUDA\n");
         return 2;
     }
-    return boat_report("gradient all-reduce",
-                       boat_cuda_allreduce_sum_f32((float*)a->grad_bucket->data, (int64_t)a->grad_bucket->nelements));
+    const int64_t H = (int64_t)a->config.hidden_size;
+    const bool bias = a->param[BQ] != NULL;
+    float* bucket = (float*)a->grad_bucket->data;
+    if (a->rest_pending) {
+        /* the backward started dWo|dbo itself and left the other group for now (mode 2) */
+        float* piece[2] = {bucket, bucket + 4 * H * H};
+        const int64_t count[2] = {3 * H * H, bias ? 3 * H : 0};
+        a->rest_pending = false;
+        if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 2)) != 0) return 3;
+    } else if (!a->sums_begun) {
+        /* nothing of this bucket is under way: all of it now, behind whatever other layers started */
+        float* piece[1] = {bucket};
+        const int64_t count[1] = {(int64_t)a->grad_bucket->nelements};
+        if (boat_report("gradient all-reduce", boat_cuda_allreduce_begin(piece, count, 1)) != 0) return 3;
+    }
+    a->sums_begun = false;
+    /* the library stream waits for every sum under way */
+    return boat_report("gradient all-reduce", boat_cuda_allreduce_join());
 }

@@ -21,7 +21,25 @@ struct boat_encoder_block_t {
     boat_dense_layer_t *fc1, *fc2;
     boat_tensor_t* u;                 /* dense1 output before GELU, kept for the backward */
     int64_t shape[3];                 /* [B, S, d] of the last forward */
+    bool sums_begun;                  /* the last backward started the gradient sums of the dense and
+                                         LayerNorm layers itself */
 };
+
+/* In-place sum over the ranks of the gradients of up to four tensors, started on the communication
+ * stream behind what the library stream has queued so far.  false when a tensor is not FP32 on the
+ * GPU or the start fails. */
+static bool begin_sums(boat_tensor_t* const t[], int n) {
+    float* piece[4];
+    int64_t count[4];
+    int k = 0;
+    for (int i = 0; i < n && k < 4; ++i) {
+        if (!t[i]) continue;
+        if (t[i]->device != BOAT_DEVICE_CUDA || t[i]->dtype != BOAT_DTYPE_FLOAT32) return false;
+        piece[k] = (float*)t[i]->data;
+        count[k++] = (int64_t)t[i]->nelements;
+    }
+    return k == 0 || boat_report("block gradient all-reduce", boat_cuda_allreduce_begin(piece, count, k)) == 0;
+}
 
 boat_encoder_block_t* boat_encoder_block_create(boat_layernorm_t* norm1, boat_attention_t* attention,
                                                 boat_layernorm_t* norm2, boat_dense_layer_t* dense1,
@@ -83,11 +101,25 @@ boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* b, const boat_t
     const int64_t flat[2] = {T, d};
     boat_tensor_t *g2 = NULL, *da = NULL, *du = NULL, *dh2 = NULL, *dh2_3 = NULL, *dln2 = NULL, *dr1 = NULL,
                   *gq = NULL, *gk = NULL, *gv = NULL, *s1 = NULL, *dh1 = NULL, *dln1 = NULL, *dx = NULL;
+    /* Data parallel with overlap (the attention layer's setting decides): a layer's gradients are
+     * final when its backward has been issued, long before the step ends - their sums over the ranks
+     * start right there and run under the kernels that follow. */
+    const bool overlap = boat_cuda_comm_world() > 1 && boat_attention_get_grad_overlap(b->attn) != 0;
+    bool begun = overlap;
+    b->sums_begun = false;
     /* MLP branch: out = r1 + dense2(GELU(dense1(LN2(r1)))) */
     g2 = boat_tensor_reshape(grad_output, flat, 2);
     da = g2 ? boat_dense_layer_backward(b->fc2, g2) : NULL;
+    if (da && begun) {
+        boat_tensor_t* const t[2] = {boat_dense_layer_get_grad_weight(b->fc2), boat_dense_layer_get_grad_bias(b->fc2)};
+        begun = begin_sums(t, 2);
+    }
     du = da ? boat_gelu_backward(da, b->u) : NULL;
     dh2 = du ? boat_dense_layer_backward(b->fc1, du) : NULL;
+    if (dh2 && begun) {
+        boat_tensor_t* const t[2] = {boat_dense_layer_get_grad_weight(b->fc1), boat_dense_layer_get_grad_bias(b->fc1)};
+        begun = begin_sums(t, 2);
+    }
     dh2_3 = dh2 ? boat_tensor_reshape(dh2, b->shape, 3) : NULL;
     dln2 = dh2_3 ? boat_layernorm_backward(b->ln2, dh2_3) : NULL;
     dr1 = dln2 ? boat_lincomb(grad_output, 1.0f, dln2, 1.0f) : NULL;
@@ -97,6 +129,13 @@ boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* b, const boat_t
         dh1 = s1 ? boat_lincomb(s1, 1.0f, gv, 1.0f) : NULL;
         dln1 = dh1 ? boat_layernorm_backward(b->ln1, dh1) : NULL;
         dx = dln1 ? boat_lincomb(dr1, 1.0f, dln1, 1.0f) : NULL;
+        if (dx && begun) {
+            /* the four small LayerNorm gradients as one group */
+            boat_tensor_t* const t[4] = {boat_layernorm_get_grad_weight(b->ln1), boat_layernorm_get_grad_bias(b->ln1),
+                                         boat_layernorm_get_grad_weight(b->ln2), boat_layernorm_get_grad_bias(b->ln2)};
+            begun = begin_sums(t, 4);
+            b->sums_begun = begun;
+        }
     }
     drop(g2, NULL); drop(da, NULL); drop(du, NULL); drop(dh2_3, NULL); drop(dh2, NULL); drop(dln2, NULL);
     drop(dr1, NULL); drop(gq, NULL); drop(gk, NULL); drop(gv, NULL); drop(s1, NULL); drop(dh1, NULL); drop(dln1, NULL);
@@ -110,7 +149,12 @@ boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* b, const boat_t
 int boat_encoder_block_allreduce_grads(boat_encoder_block_t* b) {
     if (!b) return 1;
     if (boat_cuda_comm_world() <= 1) return 0;
-    /* sums the attention backward started itself are joined with the rest below */
+    if (b->sums_begun) {
+        /* the backward started the dense and LayerNorm sums; the attention layer starts what it still
+         * owes and makes the library stream wait for all of them */
+        b->sums_begun = false;
+        return boat_attention_allreduce_grads(b->attn);
+    }
     boat_tensor_t* t[8] = {boat_layernorm_get_grad_weight(b->ln1), boat_layernorm_get_grad_bias(b->ln1),
                            boat_layernorm_get_grad_weight(b->ln2), boat_layernorm_get_grad_bias(b->ln2),
                            boat_dense_layer_get_grad_weight(b->fc1), boat_dense_layer_get_grad_bias(b->fc1),
@@ -127,12 +171,8 @@ int boat_encoder_block_allreduce_grads(boat_encoder_block_t* b) {
         piece[n] = (float*)t[i]->data;
         count[n++] = (int64_t)t[i]->nelements;
     }
-    /* the attention bucket: already on its way when the backward started the sums itself,
-     * otherwise summed now on the library stream (which also checks that the layer is on CUDA) */
-    if (!boat_cuda_allreduce_pending()) {
-        int rc = boat_attention_allreduce_grads(b->attn);
-        if (rc != 0) return rc;
-    }
     if (boat_report("block gradient all-reduce", boat_cuda_allreduce_begin(piece, count, n)) != 0) return 3;
-    return boat_report("block gradient all-reduce", boat_cuda_allreduce_join());
+    /* the attention bucket: what its backward has not started yet; then the library stream waits for
+     * every sum under way */
+    return boat_attention_allreduce_grads(b->attn);
 }

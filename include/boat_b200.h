@@ -68,6 +68,7 @@ BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
  * share the SMs with a running collective lose more than the collective costs alone).  In modes 1
  * and 2 boat_attention_allreduce_grads joins the sums: call it, as before, after the backward and
  * before anything reads or updates the gradients. */
+BOAT_API int boat_attention_get_grad_overlap(const boat_attention_t* attention);
 BOAT_API int boat_attention_set_grad_overlap(boat_attention_t* attention, int mode);
 
 /* Register the layer's parameters with an optimizer (boat/optimizers.h), each with its
