@@ -589,9 +589,14 @@ def main():
         name, n, ms = line.split()
         kern[name] = (int(n), float(ms))
     core_c = 0.5 if causal else 1.0
-    kflops = {   # algorithmic FLOPs per launch scope
-        "gemm_tc_nn": 2.0 * T * d * d, "gemm_tc_nt": 2.0 * T * d * d, "gemm_tc_tn": 2.0 * T * d * d,
-        "gemm_simt": 2.0 * T * d * d,
+    # Algorithmic FLOPs per STEP and kernel family.  A GEMM scope may hold several problems (the Q, K, V
+    # projections, their weight and their input gradients run as one launch each), so the families are
+    # counted per step: attention has four products of 2*T*d*d in each orientation, the encoder block
+    # adds two dense products of 8*T*d*d in each.
+    gemm_step = 8.0 * T * d * d + (16.0 * T * d * d if is_block else 0.0)
+    kflops = {
+        "gemm_tc_nn": gemm_step, "gemm_tc_nt": gemm_step, "gemm_tc_tn": gemm_step,
+        "gemm_simt": gemm_step,
         "attn_fwd_tc": 4.0 * core_c * B * S * S * d, "attn_fwd_simt": 4.0 * core_c * B * S * S * d,
         "attn_bwd_tc": 8.0 * core_c * B * S * S * d, "attn_bwd_simt": 8.0 * core_c * B * S * S * d,
     }
@@ -601,7 +606,7 @@ def main():
         top = max((k for k in kern if k in kflops), key=lambda k: kern[k][1], default=None)
         if top:
             n, ms = kern[top]
-            achieved = kflops[top] / (ms / n * 1e-3) / 1e12
+            achieved = kflops[top] * args.steps / (ms * 1e-3) / 1e12
             # Denominator: the measured burst figure when the timed region is shorter than a second
             # (clocks have not settled under the power cap yet), the sustained one otherwise; both
             # fractions are on the line.  TF32 has no entry in MEASURED_PEAKS.json: it is measured
