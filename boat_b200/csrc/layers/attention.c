@@ -82,19 +82,6 @@ static void dev_free(void* p) {
     if (p) boat_report("device free", boat_cuda_free(p));
 }
 
-/* When set, host tensors are uploaded on the upload stream (ordered before later launches by an
- * event) instead of by a copy that blocks the host.  Only the chunked host-tensor paths set it:
- * they end with boat_cuda_sync(), so the host buffers are no longer read when the call returns. */
-static bool g_async_uploads = false;
-
-static int upload(void* dst, const void* src, size_t bytes) {
-    if (!g_async_uploads) return boat_cuda_memcpy_h2d(dst, src, bytes);
-    int rc = boat_cuda_copies_after_compute();           /* dst was just allocated on the library stream */
-    if (rc == 0) rc = boat_cuda_upload_async(dst, src, bytes);
-    if (rc == 0) rc = boat_cuda_join_uploads();
-    return rc;
-}
-
 /* Device buffer holding tensor `t` in storage type `type`.  *owned says whether the caller
  * must release it (false: it is the tensor's own HBM). */
 static void* stage_in(const boat_tensor_t* t, int type, bool* owned) {
@@ -108,7 +95,7 @@ static void* stage_in(const boat_tensor_t* t, int type, bool* owned) {
     if (t->device != BOAT_DEVICE_CUDA) {
         tmp = dev_alloc(n * storage_size(have));
         if (!tmp) return NULL;
-        if (boat_report("upload", upload(tmp, t->data, n * storage_size(have))) != 0) {
+        if (boat_report("upload", boat_cuda_memcpy_h2d(tmp, t->data, n * storage_size(have))) != 0) {
             dev_free(tmp);
             return NULL;
         }
@@ -221,12 +208,15 @@ typedef struct {
     void* w[4];
     float* b[4];
     bool w_owned[4], b_owned[4];
+    void* raw_w[4];             /* chunked host paths: where a weight lands before its conversion */
+    bool late[4];               /* ... and whether it still has to be brought up */
 } staged_params_t;
 
 static void release_params(staged_params_t* p) {
     for (int i = 0; i < 4; ++i) {
         if (p->w_owned[i]) dev_free(p->w[i]);
         if (p->b_owned[i]) dev_free(p->b[i]);
+        dev_free(p->raw_w[i]);
     }
     memset(p, 0, sizeof *p);
 }
@@ -286,6 +276,58 @@ fail:
 }
 
 
+/* The chunked host-tensor paths bring a host layer's parameters up on the upload stream, behind the
+ * first chunk of input and each group just before the first kernel that reads it, so that this
+ * kernel waits for nothing else.  The device buffers are allocated up front, before the copy
+ * streams are tied to the library stream: a buffer allocated later could only be written once the
+ * kernels queued before its allocation have run, which would hold up every later upload. */
+static bool prepare_late_params(boat_attention_t* a, int mma, int type, bool with_bias, staged_params_t* p) {
+    memset(p, 0, sizeof *p);
+    const size_t n = a->config.hidden_size * a->config.hidden_size;
+    const bool convert = type == BOAT_CUDA_BF16 || mma == BOAT_MMA_TF32;
+    for (int i = 0; i < 4; ++i) {
+        const boat_tensor_t* w = a->param[WQ + i];
+        if (w->device == BOAT_DEVICE_CUDA || w->dtype != BOAT_DTYPE_FLOAT32 || w->nelements != n) goto fail;
+        p->w[i] = dev_alloc(n * storage_size(type));
+        p->w_owned[i] = p->w[i] != NULL;
+        if (!p->w[i]) goto fail;
+        if (convert) {
+            p->raw_w[i] = dev_alloc(n * sizeof(float));
+            if (!p->raw_w[i]) goto fail;
+        }
+        p->late[i] = true;
+        const boat_tensor_t* b = a->param[BQ + i];
+        if (with_bias && b) {
+            if (b->device == BOAT_DEVICE_CUDA || b->dtype != BOAT_DTYPE_FLOAT32) goto fail;
+            p->b[i] = (float*)dev_alloc(b->nelements * sizeof(float));
+            p->b_owned[i] = p->b[i] != NULL;
+            if (!p->b[i]) goto fail;
+        }
+    }
+    return true;
+fail:
+    release_params(p);
+    return false;
+}
+
+/* Uploads and converts weights lo..hi (with their biases) prepared by prepare_late_params; a no-op
+ * for parameters that were staged up front. */
+static bool stage_param_range(boat_attention_t* a, int type, staged_params_t* p, int lo, int hi) {
+    const int64_t n = (int64_t)(a->config.hidden_size * a->config.hidden_size);
+    for (int i = lo; i <= hi; ++i) {
+        if (!p->late[i]) continue;
+        p->late[i] = false;
+        void* land = p->raw_w[i] ? p->raw_w[i] : p->w[i];
+        int rc = boat_cuda_upload_async(land, a->param[WQ + i]->data, (size_t)n * sizeof(float));
+        if (rc == 0 && p->b[i]) rc = boat_cuda_upload_async(p->b[i], a->param[BQ + i]->data, a->param[BQ + i]->nbytes);
+        if (rc == 0) rc = boat_cuda_join_uploads();
+        if (rc == 0 && type == BOAT_CUDA_BF16) rc = boat_cuda_cast(p->w[i], BOAT_CUDA_BF16, land, BOAT_CUDA_F32, n);
+        else if (rc == 0 && p->raw_w[i]) rc = boat_cuda_round_tf32((float*)p->w[i], (const float*)land, n);
+        if (boat_report("parameter upload", rc) != 0) return false;
+    }
+    return true;
+}
+
 /* ---- host tensors: transfers overlapped with the arithmetic ------------------------------------
  * With host tensors a step moves about a gigabyte over PCIe (inputs and parameters up, outputs
  * and gradients down), more time than the kernels take.  Everything that is computed per token
@@ -293,7 +335,8 @@ fail:
  * done in chunks of whole batch entries: while chunk c is computed, chunk c+1 is uploaded and
  * chunk c-1 downloaded, on the copy streams of boat_cuda_upload_async / _download_async.  Only
  * the weight and bias gradients, which sum over all rows, run once at the end.  The arithmetic
- * per row is the same as in the one-piece path. */
+ * per row is the same as in the one-piece path.  A host layer's parameters go up on the upload
+ * stream as well, behind the first chunk and in the order the kernels need them. */
 enum { MAX_CHUNKS = 8 };
 
 static bool on_host(const boat_tensor_t* t) { return t->device != BOAT_DEVICE_CUDA; }
@@ -339,7 +382,7 @@ static int stage_rows(const boat_tensor_t* t, int mma, int type, void* dst, void
 /* Forward for host inputs cut into at least two chunks.  Fills the layer's forward state like the
  * one-piece path.  A chunk is a run of whole pieces of a->gran units, i.e. of gran*S/nh token rows. */
 static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t* const in[3], int mma, int type,
-                                        const staged_params_t* p) {
+                                        staged_params_t* p) {
     const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
     const int64_t hs = (int64_t)a->config.head_size, S = a->S, T = a->T;
     const int64_t G = a->units / a->gran, grows = a->gran * S / nh;      /* pieces, token rows per piece */
@@ -386,6 +429,7 @@ static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t
         const size_t off = (size_t)(r0 * H) * tsz, ooff = (size_t)(r0 * H) * osz;
         for (int i = 0; i < 3; ++i)
             if (a->d_in_owned[i] && stage_rows(in[i], mma, type, a->d_in[i], raw[i], r0, nr, H) != 0) goto done;
+        if (c == 0 && !stage_param_range(a, type, p, WQ, WV)) goto done;
         for (int i = 0; i < 3; ++i) {
             if (boat_report("projection", boat_cuda_gemm(mma, 0, 0, nr, H, H, (char*)a->d_in[i] + off, H, p->w[i], H, type,
                                                          (char*)a->d_proj[i] + off, H, feed_type(mma, type), p->b[i])) != 0)
@@ -396,6 +440,7 @@ static boat_tensor_t* forward_pipelined(boat_attention_t* a, const boat_tensor_t
                                            (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
                                            type, (char*)a->d_ctx + off, a->d_lse + b0 * a->gran * S)) != 0)
             goto done;
+        if (c == 0 && !stage_param_range(a, type, p, WO, WO)) goto done;
         if (boat_report("output projection", boat_cuda_gemm(mma, 0, 0, nr, H, H, (char*)a->d_ctx + off, H, p->w[WO], H, type,
                                                             (char*)d_out + ooff, H, out_type, p->b[WO])) != 0)
             goto done;
@@ -420,11 +465,17 @@ done:
  * attention core and the three input gradients per chunk, input gradients down while the next
  * chunk is computed; weight and bias gradients over all rows at the end. */
 static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_output, int mma, int type,
-                               const staged_params_t* p, float* const d_dw[4], float* const d_db[4],
+                               staged_params_t* p, float* const d_dw[4], float* const d_db[4],
                                boat_tensor_t* gin[3]) {
     const int64_t H = (int64_t)a->config.hidden_size, nh = (int64_t)a->config.num_heads;
     const int64_t hs = (int64_t)a->config.head_size, S = a->S, T = a->T;
-    const int64_t G = a->units / a->gran, grows = a->gran * S / nh;
+    /* The backward moves three times as much down as up and its kernels have time to spare, so its
+     * pieces may be finer than the forward's: halves of a piece as long as those are still whole
+     * units owning whole token rows, until there are MAX_CHUNKS chunks - a shorter wait for the first
+     * download and a shorter last one. */
+    int64_t gran = a->gran;
+    while (a->units / gran < MAX_CHUNKS && gran % 2 == 0 && ((gran / 2) * S) % nh == 0) gran /= 2;
+    const int64_t G = a->units / gran, grows = gran * S / nh;
     const size_t tsz = storage_size(type), act_bytes = (size_t)T * (size_t)H * tsz;
     const bool bias = a->param[BQ] != NULL;
     const int nchunk = (int)(G < MAX_CHUNKS ? G : MAX_CHUNKS);
@@ -451,7 +502,7 @@ static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_ou
     }
     for (int c = 0; c < nchunk; ++c) {              /* the largest chunk decides the scratch size */
         const int64_t nb = chunk_begin(G, nchunk, c + 1) - chunk_begin(G, nchunk, c);
-        const size_t need = boat_cuda_attn_bwd_scratch_bytes(mma, nb * a->gran, S, hs);
+        const size_t need = boat_cuda_attn_bwd_scratch_bytes(mma, nb * gran, S, hs);
         if (need > scratch_bytes) scratch_bytes = need;
     }
     scratch = dev_alloc(scratch_bytes ? scratch_bytes : 256);
@@ -463,17 +514,21 @@ static bool backward_pipelined(boat_attention_t* a, const boat_tensor_t* grad_ou
         const int64_t r0 = b0 * grows, nr = (b1 - b0) * grows;
         const size_t off = (size_t)(r0 * H) * tsz;
         if (stage_rows(grad_output, mma, type, d_go, raw_go, r0, nr, H) != 0) goto done;
+        /* Wo behind the first chunk of dOut; the other weights behind it, needed only after the
+         * attention-core backward of that chunk */
+        if (c == 0 && !stage_param_range(a, type, p, WO, WO)) goto done;
         /* d(ctx) = dOut . Wo^T */
         if (boat_report("dOut.Wo^T", boat_cuda_gemm(mma, 0, 1, nr, H, H, (char*)d_go + off, H, p->w[WO], H, type,
                                                     (char*)d_dctx + off, H, feed_type(mma, type), NULL)) != 0)
             goto done;
         if (boat_report("attention core backward",
-                        boat_cuda_attn_bwd(mma, (b1 - b0) * a->gran, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
+                        boat_cuda_attn_bwd(mma, (b1 - b0) * gran, S, hs, a->config.causal_mask, 1.0f / sqrtf((float)hs),
                                            (char*)a->d_proj[0] + off, (char*)a->d_proj[1] + off, (char*)a->d_proj[2] + off,
-                                           (char*)a->d_ctx + off, (char*)d_dctx + off, a->d_lse + b0 * a->gran * S, type,
+                                           (char*)a->d_ctx + off, (char*)d_dctx + off, a->d_lse + b0 * gran * S, type,
                                            (char*)d_dproj[0] + off, (char*)d_dproj[1] + off, (char*)d_dproj[2] + off,
                                            scratch, scratch_bytes)) != 0)
             goto done;
+        if (c == 0 && !stage_param_range(a, type, p, WQ, WV)) goto done;
         for (int i = 0; i < 3; ++i) {
             const size_t osz = storage_size(out_type[i]), ooff = (size_t)(r0 * H) * osz;
             /* dX = dP . W^T */
@@ -598,15 +653,10 @@ static boat_tensor_t* forward_rows(boat_attention_t* a, const boat_tensor_t* que
     void* d_out = NULL;
     boat_tensor_t* result = NULL;
     const bool pipelined = units / gran >= 2 && pipeline_enabled() && on_host(query) && on_host(key) && on_host(value);
-    /* host parameters of a chunked call go up on the upload stream, ahead of the first chunk,
-     * without blocking the host between them */
-    g_async_uploads = pipelined;
-    const bool staged = stage_params(a, mma, type, false, &p);
-    g_async_uploads = false;
-    if (!staged) {
-        if (pipelined) boat_cuda_sync();        /* uploads already under way still read host memory */
+    /* a host layer's parameters of a chunked call are brought up inside it, behind the first chunk */
+    if (!(pipelined && a->device != BOAT_DEVICE_CUDA && prepare_late_params(a, mma, type, true, &p)) &&
+        !stage_params(a, mma, type, false, &p))
         goto done;
-    }
     if (pipelined) {
         result = forward_pipelined(a, in, mma, type, &p);
         if (result) a->cached = true;
@@ -785,13 +835,11 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     a->sums_begun = false;
     const bool pipelined = units / a->gran >= 2 && pipeline_enabled() && on_host(grad_output) && on_host(a->cache_in[0]) &&
                            on_host(a->cache_in[1]) && on_host(a->cache_in[2]);
-    g_async_uploads = pipelined;
-    const bool staged = stage_params(a, mma, type, true, &p);
-    a->shadow_fresh = false;                    /* one backward per forward may trust the forward's copies */
-    g_async_uploads = false;
-    if (!staged) {
-        if (pipelined) boat_cuda_sync();        /* uploads already under way still read host memory */
-        goto done;
+    if (!(pipelined && a->device != BOAT_DEVICE_CUDA && prepare_late_params(a, mma, type, false, &p))) {
+        /* (a host layer's parameters of a chunked call are brought up inside it, behind the first chunk) */
+        const bool staged = stage_params(a, mma, type, true, &p);
+        a->shadow_fresh = false;                /* one backward per forward may trust the forward's copies */
+        if (!staged) goto done;
     }
     /* gradients are produced in HBM; a host layer receives them with one copy at the end */
     d_bucket = a->device == BOAT_DEVICE_CUDA ? (float*)a->grad_bucket->data
