@@ -571,7 +571,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
         }
-        if (tid128 == 0) tma_wait_group0();                 // all adds have landed before the CTA ends
+        // The CTA may end once the reductions have read their shared-memory source; that they have
+        // landed in global memory by the time the next kernel runs is the grid's completion.
+        if (tid128 == 0) tma_wait_group_read0();
     }
     tc_fence_before_sync();
     __syncthreads();
