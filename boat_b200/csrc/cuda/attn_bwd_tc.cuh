@@ -192,6 +192,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_prefetch_desc(&map_v);
         tma_prefetch_desc(&map_do);
         tma_prefetch_desc(&map_dq);
+        // This thread is also the producer: the loads that wait for nothing - K and V of the first
+        // walk, dO of the first Q_STAGES query tiles (later ones are loaded by the dQ warps, which
+        // stage dQ through the dO buffers and know when one is free again) - start here, under the
+        // tensor-memory allocation and the CTA's first barrier.
+        mbar_arrive_expect_tx(kv_full, 2 * C::TILE_BYTES);
+        for (int b = 0; b < C::NBOX; ++b) {
+            tma_load_2d(k_smem + b * kBoxBytes, &map_k, kv_full, b * 64, row_base + jtA * kTile);
+            tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jtA * kTile);
+        }
+        for (int t = 0; t < n_q && t < C::Q_STAGES; ++t) {
+            mbar_arrive_expect_tx(&do_full[t], C::TILE_BYTES);
+            for (int b = 0; b < C::NBOX; ++b)
+                tma_load_2d(do_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_do, &do_full[t], b * 64,
+                            row_base + qtile(t) * kTile);
+        }
     }
     if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
     tc_fence_before_sync();
@@ -209,15 +224,6 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tma_load_2d(v_smem + b * kBoxBytes, &map_v, kv_full, b * 64, row_base + jt * kTile);
                 }
             };
-            load_kv(jtA);
-            // dO of the first Q_STAGES query tiles; later ones are loaded by the dQ warps, which stage
-            // dQ through the dO buffers and know when one is free again
-            for (int t = 0; t < n_q && t < C::Q_STAGES; ++t) {
-                mbar_arrive_expect_tx(&do_full[t], C::TILE_BYTES);
-                for (int b = 0; b < C::NBOX; ++b)
-                    tma_load_2d(do_smem + t * C::TILE_BYTES + b * kBoxBytes, &map_do, &do_full[t], b * 64,
-                                row_base + qtile(t) * kTile);
-            }
             for (int t = 0; t < n_q; ++t) {
                 if (t == nA) {                  // second walk: its K and V, once the first walk's MMAs are done
                     if (!mbar_wait(kv_empty, 0, p.status, kTimeoutProducer)) break;

@@ -183,6 +183,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
+        // This thread is also the producer: the loads that wait for nothing - both query tiles and the
+        // first ring-full of key and value tiles - start here, under the tensor-memory allocation
+        // and the CTA's first barrier.
+        mbar_arrive_expect_tx(q_full, (has_b ? 2 : 1) * C::TILE_BYTES);
+        for (int g = 0; g < (has_b ? 2 : 1); ++g)
+            for (int b = 0; b < C::NBOX; ++b)
+                tma_load_2d(q_smem + g * C::TILE_BYTES + b * kBoxBytes, &map_q, q_full, b * C::BOXC,
+                            row_base + (qt_a + g) * kTile);
+        for (int j = 0; j < n_kv && j < ST; ++j) {
+            const int y = row_base + j * kTile;
+            mbar_arrive_expect_tx(&k_full[j], C::TILE_BYTES);
+            for (int b = 0; b < C::NBOX; ++b)
+                tma_load_2d(k_smem + j * C::TILE_BYTES + b * kBoxBytes, &map_k, &k_full[j], b * C::BOXC, y);
+            mbar_arrive_expect_tx(&v_full[j], C::TILE_BYTES);
+            for (int b = 0; b < C::NBOX; ++b)
+                tma_load_2d(v_smem + j * C::TILE_BYTES + b * kBoxBytes, &map_v, &v_full[j], b * C::BOXC, y);
+        }
     }
     if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
     tc_fence_before_sync();
@@ -194,12 +211,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             bool ok = true;
-            mbar_arrive_expect_tx(q_full, (has_b ? 2 : 1) * C::TILE_BYTES);
-            for (int g = 0; g < (has_b ? 2 : 1); ++g)
-                for (int b = 0; b < C::NBOX; ++b)
-                    tma_load_2d(q_smem + g * C::TILE_BYTES + b * kBoxBytes, &map_q, q_full, b * C::BOXC,
-                                row_base + (qt_a + g) * kTile);
-            for (int j = 0; j < n_kv && ok; ++j) {
+            for (int j = ST; j < n_kv && ok; ++j) {               // the first ST tiles are on their way
                 const int s = j % ST;
                 const uint32_t par = ((j / ST) & 1) ^ 1;
                 const int y = row_base + j * kTile;
