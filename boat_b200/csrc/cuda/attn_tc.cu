@@ -33,6 +33,13 @@ int launch_fwd(int64_t units, int64_t S, int causal, float scale, const void* Q,
     // units whose K and V (2 * S * hs elements each) together take about a third of L2
     const int64_t group = (40ll << 20) / (2 * S * HS * (int64_t)C::ES);
     p.group = (int)(group < 1 ? 1 : (group > units ? units : group));
+    {
+        // BOAT_FWD_GROUP=n in the environment overrides the group size; it is read at every launch so
+        // that a test can run a small problem in several groups, the first of them short
+        const char* e = getenv("BOAT_FWD_GROUP");
+        const int n = e ? atoi(e) : 0;
+        if (n >= 1) p.group = n > (int)units ? (int)units : n;
+    }
     auto kern = attn_fwd_tc_kernel<T, HS>;
     static bool configured = false;
     if (!configured) {

@@ -96,6 +96,20 @@ def test_attention_core_slice_of_benchmarked_config(gpu_lib, name, pair):
             assert err <= TOL_BF16, (name, key, "unit %d" % u, err)
 
 
+@pytest.mark.parametrize("group", ["1", "4", "5"])
+def test_forward_unit_groups(gpu_lib, monkeypatch, group):
+    """The forward schedules the CTAs of a few units at a time (their K and V share L2) and puts a
+    short group first when the units do not divide; BOAT_FWD_GROUP forces small groups on the
+    6-unit slice of config 4: six groups of one, a short group of 2 before one of 4, 1 before 5."""
+    monkeypatch.setenv("BOAT_FWD_GROUP", group)
+    name = "c4_S8192_hs128"
+    q, k, v, go, ref = core_problem(name)
+    got = run_core_bf16(gpu_lib, q, k, v, go, True)
+    for u in range(q.shape[0]):
+        assert cases.rel_err(got["o"][u], ref["o"][u]) <= TOL_BF16, (group, u)
+        assert cases.rel_err(got["dq"][u], ref["dq"][u]) <= TOL_BF16, (group, u)      # through the saved lse
+
+
 def test_schedule_default_matches_forced_choice(gpu_lib):
     """Without BOAT_BWD_PAIR the launcher picks a schedule by problem size; whatever it picks
     must give the numbers of that schedule when forced."""
