@@ -22,7 +22,8 @@ struct boat_encoder_block_t {
     boat_tensor_t* u;                 /* dense1 output before GELU, kept for the backward */
     int64_t shape[3];                 /* [B, S, d] of the last forward */
     bool sums_begun;                  /* the last backward started the gradient sums of the dense and
-                                         LayerNorm layers itself */
+                                         LayerNorm layers itself, all of them */
+    bool sums_in_flight;              /* some were started and nobody has waited for them yet */
 };
 
 /* In-place sum over the ranks of the gradients of up to four tensors, started on the communication
@@ -106,6 +107,12 @@ boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* b, const boat_t
      * start right there and run under the kernels that follow. */
     const bool overlap = boat_cuda_comm_world() > 1 && boat_attention_get_grad_overlap(b->attn) != 0;
     bool begun = overlap;
+    if (b->sums_in_flight) {
+        /* sums of a step whose boat_encoder_block_allreduce_grads never came still read and write the
+         * gradients this backward is about to add to */
+        b->sums_in_flight = false;
+        if (boat_report("block gradient all-reduce", boat_cuda_allreduce_join()) != 0) return NULL;
+    }
     b->sums_begun = false;
     /* MLP branch: out = r1 + dense2(GELU(dense1(LN2(r1)))) */
     g2 = boat_tensor_reshape(grad_output, flat, 2);
@@ -113,6 +120,7 @@ boat_tensor_t* boat_encoder_block_backward(boat_encoder_block_t* b, const boat_t
     if (da && begun) {
         boat_tensor_t* const t[2] = {boat_dense_layer_get_grad_weight(b->fc2), boat_dense_layer_get_grad_bias(b->fc2)};
         begun = begin_sums(t, 2);
+        b->sums_in_flight = begun;
     }
     du = da ? boat_gelu_backward(da, b->u) : NULL;
     dh2 = du ? boat_dense_layer_backward(b->fc1, du) : NULL;
@@ -153,7 +161,15 @@ int boat_encoder_block_allreduce_grads(boat_encoder_block_t* b) {
         /* the backward started the dense and LayerNorm sums; the attention layer starts what it still
          * owes and makes the library stream wait for all of them */
         b->sums_begun = false;
+        b->sums_in_flight = false;
         return boat_attention_allreduce_grads(b->attn);
+    }
+    if (b->sums_in_flight) {
+        /* a backward that failed half-way started some sums: wait for them, report the step as lost */
+        b->sums_in_flight = false;
+        boat_report("block gradient all-reduce", boat_cuda_allreduce_join());
+        fprintf(stderr, "boat: the block's last backward did not complete; its gradients are not summed\n");
+        return 4;
     }
     boat_tensor_t* t[8] = {boat_layernorm_get_grad_weight(b->ln1), boat_layernorm_get_grad_bias(b->ln1),
                            boat_layernorm_get_grad_weight(b->ln2), boat_layernorm_get_grad_bias(b->ln2),
