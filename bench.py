@@ -398,11 +398,12 @@ def main():
         layer.to_device(capi.DEVICE_CUDA)
         layer.set_precision(mma)
     if world > 1:
-        # the backward itself starts the sum of dWo | dbo (it runs under the attention-core backward);
-        # allreduce_grads() starts the rest and joins.  BOAT_GRAD_OVERLAP=1 also starts the rest from the
-        # backward, under the persistent input-gradient GEMMs (measured no better: those lose to a
-        # co-running collective about what the overlap saves); 0 sums everything at the end.
-        overlap_mode = int(os.environ.get("BOAT_GRAD_OVERLAP", "2"))
+        # The backward itself starts the sum of dWo | dbo (it runs under the attention-core backward).  From
+        # four ranks on it also starts the sum of the rest (mode 1), beside the input-gradient GEMMs, which are
+        # then launched with one CTA per tile so that the collective's CTAs get SMs while they run: at N=4
+        # 7.38-7.41 ms per step against 7.45-7.48 ms, the split problem 1.82 against 1.91 ms.  With two ranks
+        # the sum is short and allreduce_grads() starts the rest and joins (mode 2); 0 sums everything at the end.
+        overlap_mode = int(os.environ.get("BOAT_GRAD_OVERLAP", "1" if world >= 4 else "2"))
         layer.set_grad_overlap(overlap_mode)
     adam = None
     if args.optimizer == "adam":

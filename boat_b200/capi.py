@@ -223,6 +223,7 @@ PROTOTYPES = {
     "boat_cuda_attn_bwd": (_I, [_I, _I64, _I64, _I64, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _SZ]),
     "boat_cuda_attn_bwd_static_capacity": (_SZ, []),
     "boat_cuda_attn_bwd_static": (_I, [_I, _I64, _I64, _I64, _I, _F, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P]),
+    "boat_cuda_gemm_set_yielding": (_I, [_I]),
     "boat_cuda_gemm_grouped": (_I, [_I, _I, _I, _I, _I64, _I64, _I64, _P, _I64, _P, _I64, _I, _P, _I64, _I, _P]),
     "boat_cuda_colsum": (_I, [_P, _I, _I64, _I64, _P]),
     "boat_cuda_colsum_multi": (_I, [_P, _I, _I64, _I64, _P, _I]),

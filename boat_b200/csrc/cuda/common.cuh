@@ -88,6 +88,7 @@ bool gemm_tc_supported(int mma, int trans_a, int trans_b, int64_t M, int64_t N, 
                        int out_type);
 int gemm_tc(int mma, int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
             const void* B, int64_t ldb, int in_type, void* C, int64_t ldc, int out_type, const float* bias);
+void gemm_tc_set_yielding(bool on);
 // `groups` (1..4) problems of one shape, layout and type in one launch; bias may be NULL or hold NULLs.
 int gemm_tc_grouped(int mma, int trans_a, int trans_b, int groups, int64_t M, int64_t N, int64_t K,
                     const void* const* A, int64_t lda, const void* const* B, int64_t ldb, void* const* C,

@@ -47,6 +47,11 @@ int boat_cuda_gemm(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, con
     return gemm_simt(ta, tb, M, N, K, A, lda, B, ldb, in_type, C, ldc, out_type, bias);
 }
 
+int boat_cuda_gemm_set_yielding(int on) {
+    gemm_tc_set_yielding(on != 0);
+    return 0;
+}
+
 int boat_cuda_gemm_grouped(int mma, int ta, int tb, int groups, int64_t M, int64_t N, int64_t K, const void* const* A,
                            int64_t lda, const void* const* B, int64_t ldb, int in_type, void* const* C, int64_t ldc,
                            int out_type, const float* const* bias) {

@@ -259,6 +259,8 @@ gemm_tc_kernel(const __grid_constant__ GroupMaps maps, const __grid_constant__ P
     }
 }
 
+bool g_yielding = false;
+
 template <typename T, bool A_MN, bool B_MN, int BN>
 int launch(int groups, int64_t M, int64_t N, int64_t K, const void* const* A, int64_t lda, const void* const* B,
            int64_t ldb, void* const* Cp, int64_t ldc, int out_type, const float* const* bias, int split_k) {
@@ -302,7 +304,10 @@ int launch(int groups, int64_t M, int64_t N, int64_t K, const void* const* A, in
         configured = true;
     }
     const int work = tiles * split_k;
-    const int grid = work < sm_count() ? work : sm_count();
+    // Persistent by default: one CTA per SM walks the tiles.  A yielding launch has one CTA per tile
+    // instead, so that SMs come free all along and the CTAs of a collective started beside it (whose
+    // stream has priority) get placed while the GEMM runs, not after it.
+    const int grid = (g_yielding || work < sm_count()) ? work : sm_count();
     ProfileScope prof(A_MN ? "gemm_tc_tn" : (B_MN ? "gemm_tc_nn" : "gemm_tc_nt"));
     kern<<<grid, kThreads, C::SMEM, stream()>>>(maps, p);
     BOATCU_LAUNCH_OK("gemm_tc");
@@ -371,6 +376,8 @@ int gemm_tc_grouped(int mma, int ta, int tb, int groups, int64_t M, int64_t N, i
         return dispatch_layout<__nv_bfloat16>(ta, tb, groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
     return dispatch_layout<float>(ta, tb, groups, M, N, K, A, lda, B, ldb, C, ldc, out_type, bias);
 }
+
+void gemm_tc_set_yielding(bool on) { g_yielding = on; }
 
 int gemm_tc(int mma, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
             int64_t ldb, int in_type, void* C, int64_t ldc, int out_type, const float* bias) {

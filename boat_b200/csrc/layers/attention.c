@@ -903,6 +903,8 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
     } else if (overlap) {
         a->rest_pending = true;
     }
+    const bool yield = overlap && a->grad_overlap == 1;      /* a sum was just started beside these GEMMs */
+    if (yield) boat_cuda_gemm_set_yielding(1);
     {
         /* dX = dP . W^T for the three inputs: one launch when they share device and dtype */
         const boat_tensor_t* x0 = a->cache_in[0];
@@ -951,6 +953,7 @@ bool boat_attention_backward(boat_attention_t* a, const boat_tensor_t* grad_outp
         goto done;
     ok = true;
 done:
+    boat_cuda_gemm_set_yielding(0);
     dev_free(d_dx);
     dev_free(scratch);
     for (int i = 0; i < 3; ++i) dev_free(d_dproj[i]);

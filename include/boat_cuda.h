@@ -92,6 +92,12 @@ int boat_cuda_gemm(int mma, int trans_a, int trans_b, int64_t M, int64_t N, int6
                    const void* A, int64_t lda, const void* B, int64_t ldb, int in_type,
                    void* C, int64_t ldc, int out_type, const float* bias);
 
+/* While on, tensor-core GEMM launches use one CTA per output tile instead of one persistent CTA per
+ * SM: SMs come free all along the launch, so a collective started beside it on another stream gets
+ * placed while the GEMM runs.  The attention backward switches it on around the input-gradient GEMMs
+ * when it has just started a gradient sum (overlap mode 1). */
+int boat_cuda_gemm_set_yielding(int on);
+
 /* `groups` (1 to 4) contractions of one shape, layout and type as one launch: the Q, K and V
  * projections of a layer (attention.c:363-365 makes three linear_projection calls), their three
  * weight gradients, their three input gradients.  A, B, C are tables of `groups` pointers (entries
