@@ -65,8 +65,8 @@ BOAT_API int boat_attention_allreduce_grads(boat_attention_t* attention);
  * final - it then runs under the attention-core backward - and the sum of dWq dWk dWv | dbq dbk dbv
  * before the three input-gradient GEMMs, which are then launched with one CTA per tile so that the
  * collective's CTAs are placed while they run.  mode 2: only the first of these is started by the
- * backward; the second is started by boat_attention_allreduce_grads (persistent GEMM kernels that
- * share the SMs with a running collective lose more than the collective costs alone).  In modes 1
+ * backward; the second is started by boat_attention_allreduce_grads (with two ranks the sum is short
+ * and the one-CTA-per-tile GEMMs of mode 1 cost about what hiding it saves).  In modes 1
  * and 2 boat_attention_allreduce_grads joins the sums: call it, as before, after the backward and
  * before anything reads or updates the gradients. */
 BOAT_API int boat_attention_get_grad_overlap(const boat_attention_t* attention);
