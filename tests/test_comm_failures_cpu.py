@@ -87,6 +87,15 @@ def test_healthy_exchange_then_a_peer_with_another_bucket_size(fake_lib):
         assert lib.boat_cuda_allreduce_pending() == 1
         assert lib.boat_cuda_allreduce_join() == 0 and lib.boat_cuda_allreduce_pending() == 0
         assert list(a) == [2, 2, 2] and list(b) == [10, 10]
+        # several starts before one join, as an encoder block's backward issues them (one per layer)
+        c, d, e = (C.c_float * 4)(1, 2, 3, 4), (C.c_float * 1)(7), (C.c_float * 2)(0.5, -0.5)
+        for arr in (c, d, e):
+            one = (C.c_void_p * 1)(C.addressof(arr))
+            assert lib.boat_cuda_allreduce_begin(one, (C.c_int64 * 1)(len(arr)), 1) == 0, err()
+            assert lib.boat_cuda_allreduce_pending() == 1
+        assert lib.boat_cuda_allreduce_join() == 0 and lib.boat_cuda_allreduce_pending() == 0
+        assert list(c) == [2, 4, 6, 8] and list(d) == [14] and list(e) == [1.0, -1.0]
+        assert lib.boat_cuda_allreduce_join() == 0                      # nothing under way: a no-op
         # from now on the peer claims 7 elements where this rank brings 8
         os.environ["FAKE_NCCL_PEER_COUNT"] = "7"
         big = (C.c_float * 8)(*([1.0] * 8))
