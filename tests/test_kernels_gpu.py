@@ -383,3 +383,21 @@ def test_convert_multi_equals_single_conversions(gpu_lib, sizes):
             bf = dst_type == capi.CUDA_BF16
             assert np.array_equal(many[i].numpy((n,), bf16=bf), one[i].numpy((n,), bf16=bf)), (dst_type, i)
     assert lib.boat_cuda_convert_multi(_ptr_table(dx), capi.CUDA_F32, _ptr_table(dx), counts, len(sizes)) != 0
+
+
+@pytest.mark.parametrize("mma", [capi.MMA_BF16, capi.MMA_TF32], ids=["bf16", "tf32"])
+@pytest.mark.parametrize("layout", LAYOUTS, ids=["nn", "nt", "tn"])
+def test_gemm_one_cta_per_tile_gives_the_same_bits(gpu_lib, mma, layout):
+    """boat_cuda_gemm_set_yielding(1): one CTA per output tile instead of one persistent CTA per SM
+    (the attention backward uses it beside a running gradient sum) - the same tiles, the same
+    accumulation order, the same bits; more tiles than SMs so that the two launches really differ."""
+    lib = gpu_lib
+    M, N, K = 4096, 2048, 512          # 256 tiles of 128 x 256
+    try:
+        got_persistent, ref = run_gemm(lib, mma, layout[0], layout[1], M, N, K, out_bf16=mma == capi.MMA_BF16)
+        check(lib.boat_cuda_gemm_set_yielding(1), "set_yielding")
+        got_yielding, _ = run_gemm(lib, mma, layout[0], layout[1], M, N, K, out_bf16=mma == capi.MMA_BF16)
+    finally:
+        check(lib.boat_cuda_gemm_set_yielding(0), "set_yielding")
+    assert rel(got_persistent, ref) <= TOL[mma]
+    assert np.array_equal(got_persistent, got_yielding)
