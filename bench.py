@@ -282,8 +282,10 @@ def l2_policy(cfg):
 
 
 def workload_config(name, cfg, world):
-    return dict(workload="%s: attention fwd+bwd, batch=%d per GPU, seq=%d, d_model=%d, heads=%d (head_dim %d), %s, %s" %
-                (name, cfg["B"], cfg["S"], cfg["d"], cfg["nh"], cfg["d"] // cfg["nh"],
+    what = "pre-LN encoder block step (LayerNorm, attention, residual, LayerNorm, dense 4d, GELU, dense, residual; MSE)" \
+        if cfg.get("block") else "attention fwd+bwd"
+    return dict(workload="%s: %s, batch=%d per GPU, seq=%d, d_model=%d, heads=%d (head_dim %d), %s, %s" %
+                (name, what, cfg["B"], cfg["S"], cfg["d"], cfg["nh"], cfg["d"] // cfg["nh"],
                  "causal" if cfg["causal"] else "non-causal",
                  "BF16 storage, FP32 accumulate" if cfg["mma"] == "bf16" else "FP32 storage, TF32 MMA"),
                 batch_per_gpu=cfg["B"], global_batch=cfg["B"] * world, seq_len=cfg["S"], d_model=cfg["d"],
